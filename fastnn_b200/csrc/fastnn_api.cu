@@ -1,0 +1,501 @@
+// C ABI of libfastnn_b200.so (declared in include/fastnn_b200_kernels.h).
+//
+// Host side of the GEMM path: per-device state, argument checks, the tile / split-K
+// planner, tensor-map encoding and kernel launches.  No cuBLAS, no CPU fallback.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <utility>
+
+#include "../../include/fastnn_b200_kernels.h"
+#include "gemm_simt.cuh"
+#include "gemm_tcgen05.cuh"
+
+namespace {
+
+using fnn::GemmParams;
+
+constexpr int kMaxDevices = 16;
+constexpr size_t kMaxDynSmem = 232448;   // 227 KiB, the sm_100 per-CTA limit
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct Workspace {
+  float* ptr = nullptr;
+  size_t bytes = 0;
+};
+
+struct DeviceState {
+  bool ready = false;
+  int num_sms = 0;
+  unsigned int* status = nullptr;   // device word written by a kernel whose wait ran out
+  long long spin_budget = 0;        // clock ticks one wait may last
+  std::map<cudaStream_t, Workspace> workspaces;   // split-K partials, one per stream
+};
+
+std::mutex g_mutex;
+DeviceState g_dev[kMaxDevices];
+EncodeTiledFn g_encode = nullptr;
+std::atomic<unsigned long long> g_launches{0};
+
+struct Policy {
+  int policy = 0, block_n = 0, split_k = 0;
+};
+Policy g_policy;
+
+struct LastCall {
+  int path = 0, block_n = 0, split_k = 0, num_ctas = 0;
+};
+thread_local LastCall t_last;
+
+#define FNN_CUDA_OK(call)                      \
+  do {                                         \
+    if ((call) != cudaSuccess) {               \
+      (void)cudaGetLastError();                \
+      return -1;                               \
+    }                                          \
+  } while (0)
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+DeviceState* current_state() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  DeviceState* st = &g_dev[dev];
+  return st->ready ? st : nullptr;
+}
+
+// 3-D FP32 tensor map, 128-byte swizzle, zero fill outside the tensor.
+bool encode_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1) {
+  if (g_encode == nullptr) return false;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {box0, box1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+struct Plan {
+  int block_n, split_k, stages;
+};
+
+// Cycle model used to pick the tile width and the K split.  Per 32-deep k-block a CTA is
+// bound either by the tensor pipe (block_n / 2 cycles at 4096 dense TF32 flop/clk/SM) or by
+// reading A (4 KiB) and B (block_n * 32 B) from shared memory at 128 B/clk.
+Plan choose_plan(int m, int n, int k, int batch, int num_sms) {
+  const int tiles_m = ceil_div(m, fnn::kBlockM);
+  const int num_kb = ceil_div(k, fnn::kBlockK);
+  const int n32 = ceil_div(n, 32) * 32;
+  const double out_bytes = 4.0 * m * n * batch;
+  const double hbm_per_clk = 3000.0;
+  const double floor_cycles = (4.0 * batch * (1.0 * m * k + 1.0 * k * n) + out_bytes) / hbm_per_clk;
+  Plan best{32, 1, 4};
+  double best_cost = 1e300;
+  static const int splits[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
+  for (int bn = 32; bn <= fnn::kMaxBlockN; bn += 32) {
+    if (bn > n32) break;
+    const int tiles_n = ceil_div(n, bn);
+    const double t_kb = bn / 2.0 > 32.0 + bn / 4.0 ? bn / 2.0 : 32.0 + bn / 4.0;
+    for (int s : splits) {
+      if (s > 1 && num_kb / s < 4) break;
+      const int kbps = ceil_div(num_kb, s);
+      const int real_split = ceil_div(num_kb, kbps);
+      const long long units = 1ll * batch * tiles_m * tiles_n * real_split;
+      const double waves = static_cast<double>((units + num_sms - 1) / num_sms);
+      double cycles = waves * (kbps * t_kb + 1200.0);
+      if (real_split > 1) cycles += (2.0 * real_split + 1.0) * out_bytes / hbm_per_clk + 6000.0;
+      if (cycles < floor_cycles) cycles = floor_cycles;
+      // prefer wider tiles and fewer splits on ties
+      cycles *= 1.0 + 1e-4 * (8 - bn / 32) + 1e-3 * (real_split - 1);
+      if (cycles < best_cost) {
+        best_cost = cycles;
+        best.block_n = bn;
+        best.split_k = real_split;
+      }
+    }
+  }
+  return best;
+}
+
+int stages_for(int block_n) {
+  const size_t stage = fnn::kStageABytes + static_cast<size_t>(block_n) * fnn::kBlockK * 4;
+  const size_t avail = kMaxDynSmem - 1024 - fnn::kStagingBytes - fnn::kBarrierBytes;
+  int s = static_cast<int>(avail / stage);
+  if (s > fnn::kMaxStages) s = fnn::kMaxStages;
+  return s;
+}
+
+struct GemmArgs {
+  int layout;
+  const float *a, *b;
+  float* c;
+  int m, n, k, batch;
+  long long lda, ldb, ldc, sa, sb, sc;
+  float alpha, beta;
+  const float* bias;
+  int act;
+  cudaStream_t stream;
+};
+
+bool tma_operands_ok(const GemmArgs& g) {
+  if (g.k < 1) return false;
+  if (!aligned16(g.a) || !aligned16(g.b)) return false;
+  if ((g.lda & 3) || (g.ldb & 3)) return false;
+  if (g.batch > 1 && ((g.sa & 3) || (g.sb & 3))) return false;
+  // tensor-map limits: strides below 2^40 bytes
+  const long long lim = (1ll << 40) / 4;
+  if (g.lda >= lim || g.ldb >= lim || g.sa >= lim || g.sb >= lim) return false;
+  return true;
+}
+
+int launch_simt(const GemmArgs& g) {
+  fnn::SimtParams p;
+  p.a = g.a; p.b = g.b; p.c = g.c; p.bias = g.bias;
+  p.m = g.m; p.n = g.n; p.k = g.k; p.batch = g.batch;
+  p.a_bs = g.sa; p.b_bs = g.sb; p.c_bs = g.sc; p.ldc = g.ldc;
+  if (g.layout == FASTNN_B200_TN) { p.a_rs = 1; p.a_cs = g.lda; } else { p.a_rs = g.lda; p.a_cs = 1; }
+  if (g.layout == FASTNN_B200_NT) { p.b_rs = 1; p.b_cs = g.ldb; } else { p.b_rs = g.ldb; p.b_cs = 1; }
+  p.alpha = g.alpha; p.beta = g.beta; p.act = g.act;
+  const int gx = ceil_div(g.n, fnn::kSimtTile), gy = ceil_div(g.m, fnn::kSimtTile);
+  if (gy > 65535) return -1;
+  for (int b0 = 0; b0 < g.batch; b0 += 65535) {
+    fnn::SimtParams q = p;
+    q.a += b0 * p.a_bs; q.b += b0 * p.b_bs; q.c += b0 * p.c_bs;
+    const int nb = g.batch - b0 < 65535 ? g.batch - b0 : 65535;
+    fnn::gemm_simt_kernel<<<dim3(gx, gy, nb), 256, 0, g.stream>>>(q);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
+  FNN_CUDA_OK(cudaGetLastError());
+  t_last = LastCall{1, 0, 1, gx * gy * g.batch};
+  return 0;
+}
+
+int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
+  Plan plan = choose_plan(g.m, g.n, g.k, g.batch, st->num_sms);
+  if (pol.block_n > 0) plan.block_n = pol.block_n;
+  if (pol.split_k > 0) plan.split_k = pol.split_k;
+  const int num_kb = ceil_div(g.k, fnn::kBlockK);
+  if (plan.split_k > num_kb) plan.split_k = num_kb;
+  const int kbps = ceil_div(num_kb, plan.split_k);
+  plan.split_k = ceil_div(num_kb, kbps);
+  plan.stages = stages_for(plan.block_n);
+
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.m = g.m; p.n = g.n; p.k = g.k; p.batch = g.batch;
+  p.block_n = plan.block_n;
+  p.num_stages = plan.stages;
+  p.tiles_m = ceil_div(g.m, fnn::kBlockM);
+  p.tiles_n = ceil_div(g.n, plan.block_n);
+  p.num_kb = num_kb;
+  p.split_k = plan.split_k;
+  p.kb_per_split = kbps;
+  const long long units = 1ll * g.batch * p.tiles_m * p.tiles_n * plan.split_k;
+  if (units > 0x7fffffffll) return -1;
+  p.total_units = static_cast<int>(units);
+  p.a_mn_major = (g.layout == FASTNN_B200_TN) ? 1 : 0;
+  p.b_mn_major = (g.layout == FASTNN_B200_NT) ? 0 : 1;
+  p.alpha = g.alpha; p.beta = g.beta; p.bias = g.bias; p.act = g.act;
+  p.status = st->status;
+  p.spin_budget = st->spin_budget;
+
+  // output target: C itself, or the split-K workspace
+  float* out = g.c;
+  long long out_ld = g.ldc, out_bs = g.sc;
+  long long out_z = g.batch;
+  if (plan.split_k > 1) {
+    const size_t need = sizeof(float) * static_cast<size_t>(g.m) * g.n * g.batch * plan.split_k;
+    Workspace& ws = st->workspaces[g.stream];
+    if (ws.bytes < need) {
+      if (ws.ptr) FNN_CUDA_OK(cudaFree(ws.ptr));
+      ws.ptr = nullptr; ws.bytes = 0;
+      FNN_CUDA_OK(cudaMalloc(&ws.ptr, need));
+      ws.bytes = need;
+    }
+    out = ws.ptr;
+    out_ld = g.n;
+    out_bs = static_cast<long long>(g.m) * g.n;
+    out_z = static_cast<long long>(g.batch) * plan.split_k;
+    p.bias = nullptr;
+  }
+  const bool tma_store = aligned16(out) && (out_ld & 3) == 0 && (out_z == 1 || (out_bs & 3) == 0) &&
+                         (plan.split_k > 1 || g.beta == 0.0f) && out_ld < (1ll << 38) &&
+                         out_bs < (1ll << 38);
+  p.store_mode = tma_store ? 0 : 1;
+  p.c = out; p.ldc = out_ld; p.c_batch_stride = out_bs;
+
+  CUtensorMap tmA, tmB, tmC;
+  const uint64_t B = static_cast<uint64_t>(g.batch);
+  const uint64_t sa_bytes = (g.batch > 1 ? g.sa : g.lda * (p.a_mn_major ? g.k : g.m)) * 4ull;
+  const uint64_t sb_bytes = (g.batch > 1 ? g.sb : g.ldb * (p.b_mn_major ? g.k : g.n)) * 4ull;
+  bool ok;
+  if (!p.a_mn_major)
+    ok = encode_map(&tmA, g.a, g.k, g.m, B, g.lda * 4ull, sa_bytes, fnn::kBlockK, fnn::kBlockM);
+  else
+    ok = encode_map(&tmA, g.a, g.m, g.k, B, g.lda * 4ull, sa_bytes, 32, fnn::kBlockK);
+  if (!p.b_mn_major)
+    ok = ok && encode_map(&tmB, g.b, g.k, g.n, B, g.ldb * 4ull, sb_bytes, fnn::kBlockK, plan.block_n);
+  else
+    ok = ok && encode_map(&tmB, g.b, g.n, g.k, B, g.ldb * 4ull, sb_bytes, 32, fnn::kBlockK);
+  if (tma_store) {
+    const uint64_t sc_bytes = (out_z > 1 ? out_bs : out_ld * g.m) * 4ull;
+    ok = ok && encode_map(&tmC, out, g.n, g.m, static_cast<uint64_t>(out_z), out_ld * 4ull,
+                          sc_bytes, 32, 32);
+  } else {
+    std::memset(&tmC, 0, sizeof(tmC));
+  }
+  if (!ok) return -1;
+
+  const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
+  const size_t smem = fnn::gemm_smem_bytes(plan.block_n, plan.stages);
+  fnn::gemm_tf32_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  FNN_CUDA_OK(cudaGetLastError());
+
+  if (plan.split_k > 1) {
+    const long long total = 1ll * g.m * g.n * g.batch;
+    const bool vec = (g.n & 3) == 0 && aligned16(g.c) && (g.ldc & 3) == 0 && (g.sc & 3) == 0 &&
+                     (g.bias == nullptr || aligned16(g.bias));
+    long long work = vec ? total / 4 : total;
+    long long blocks = (work + 255) / 256;
+    const long long cap = 8ll * st->num_sms;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    if (vec)
+      fnn::splitk_reduce_vec4_kernel<<<static_cast<unsigned>(blocks), 256, 0, g.stream>>>(
+          reinterpret_cast<const float4*>(out), g.c, g.bias, g.m, g.n, g.batch, plan.split_k, g.ldc,
+          g.sc, g.alpha, g.beta, g.act);
+    else
+      fnn::splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, g.stream>>>(
+          out, g.c, g.bias, g.m, g.n, g.batch, plan.split_k, g.ldc, g.sc, g.alpha, g.beta, g.act);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    FNN_CUDA_OK(cudaGetLastError());
+  }
+  t_last = LastCall{2, plan.block_n, plan.split_k, grid};
+  return 0;
+}
+
+int gemm_dispatch(const GemmArgs& g) {
+  if (g.layout < 0 || g.layout > 2) return -1;
+  if (g.m < 0 || g.n < 0 || g.k < 0 || g.batch < 0) return -1;
+  if (g.act < 0 || g.act > 2) return -1;
+  if (g.m == 0 || g.n == 0 || g.batch == 0) return 0;          // nothing to write
+  if (g.c == nullptr || (g.k > 0 && (g.a == nullptr || g.b == nullptr))) return -1;
+  // leading dimensions must cover a row
+  const long long a_row = (g.layout == FASTNN_B200_TN) ? g.m : g.k;
+  const long long b_row = (g.layout == FASTNN_B200_NT) ? g.k : g.n;
+  if (g.lda < a_row || g.ldb < b_row || g.ldc < g.n) return -1;
+
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState* st = current_state();
+  if (st == nullptr) return -1;                                   // fastnn_cuda_init not called
+  const Policy pol = g_policy;
+  const bool can_tma = tma_operands_ok(g);
+  if (pol.policy == 2 && !can_tma) return -1;
+  if (pol.policy == 1 || !can_tma) return launch_simt(g);
+  return launch_tcgen05(st, g, pol);
+}
+
+}  // namespace
+
+// ============================================================ drop-in symbols ===
+
+extern "C" int fastnn_cuda_init(int device_id) {
+  if (device_id < 0 || device_id >= kMaxDevices) return -1;
+  FNN_CUDA_OK(cudaSetDevice(device_id));
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState& st = g_dev[device_id];
+  if (st.ready) return 0;
+  cudaDeviceProp prop;
+  FNN_CUDA_OK(cudaGetDeviceProperties(&prop, device_id));
+  if (prop.major != 10) {
+    std::fprintf(stderr, "fastnn_b200: device %d is sm_%d%d; this library carries sm_100a code only\n",
+                 device_id, prop.major, prop.minor);
+    return -1;
+  }
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    FNN_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return -1;
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kMaxDynSmem)));
+  st.num_sms = prop.multiProcessorCount;
+  FNN_CUDA_OK(cudaMalloc(&st.status, sizeof(unsigned int)));
+  FNN_CUDA_OK(cudaMemset(st.status, 0, sizeof(unsigned int)));
+  // about two seconds at the maximum SM clock (clockRate is in kHz)
+  int khz = 0;
+  if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device_id) != cudaSuccess || khz <= 0) {
+    (void)cudaGetLastError();
+    khz = 2000000;
+  }
+  st.spin_budget = 2000ll * khz;
+  if (const char* e = std::getenv("FASTNN_B200_SPIN_MS")) {
+    const long long ms = std::atoll(e);
+    if (ms > 0) st.spin_budget = ms * khz;
+  }
+  st.ready = true;
+  return 0;
+}
+
+extern "C" int fastnn_cuda_device_count(void) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return count;
+}
+
+extern "C" int fastnn_cuda_synchronize(void) {
+  FNN_CUDA_OK(cudaDeviceSynchronize());
+  return 0;
+}
+
+extern "C" void fastnn_cuda_get_memory_info(size_t* free_mem, size_t* total_mem) {
+  size_t f = 0, t = 0;
+  if (cudaMemGetInfo(&f, &t) != cudaSuccess) (void)cudaGetLastError();
+  if (free_mem) *free_mem = f;
+  if (total_mem) *total_mem = t;
+}
+
+extern "C" int fastnn_cuda_malloc(float** ptr, size_t size) {
+  if (ptr == nullptr) return -1;
+  FNN_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(ptr), size));
+  return 0;
+}
+extern "C" int fastnn_cuda_free(float* ptr) {
+  FNN_CUDA_OK(cudaFree(ptr));
+  return 0;
+}
+extern "C" int fastnn_cuda_memcpy_h2d(float* dst, const float* src, size_t size) {
+  FNN_CUDA_OK(cudaMemcpy(dst, src, size, cudaMemcpyHostToDevice));
+  return 0;
+}
+extern "C" int fastnn_cuda_memcpy_d2h(float* dst, const float* src, size_t size) {
+  FNN_CUDA_OK(cudaMemcpy(dst, src, size, cudaMemcpyDeviceToHost));
+  return 0;
+}
+extern "C" int fastnn_cuda_memcpy_d2d(float* dst, const float* src, size_t size) {
+  FNN_CUDA_OK(cudaMemcpy(dst, src, size, cudaMemcpyDeviceToDevice));
+  return 0;
+}
+extern "C" int fastnn_cuda_memset(float* ptr, int value, size_t size) {
+  FNN_CUDA_OK(cudaMemset(ptr, value, size));
+  return 0;
+}
+
+extern "C" int fastnn_cuda_matmul(const float* a, const float* b, float* c, int m, int n, int k,
+                                  int lda, int ldb, int ldc, float alpha, float beta) {
+  GemmArgs g{FASTNN_B200_NN, a, b, c, m, n, k, 1, lda, ldb, ldc,
+             1ll * m * lda, 1ll * k * ldb, 1ll * m * ldc, alpha, beta, nullptr, 0, nullptr};
+  return gemm_dispatch(g);
+}
+extern "C" int fastnn_cuda_matmul_batched(const float* a, const float* b, float* c, int m, int n,
+                                          int k, int batch_size, float alpha, float beta) {
+  GemmArgs g{FASTNN_B200_NN, a, b, c, m, n, k, batch_size, k, n, n,
+             1ll * m * k, 1ll * k * n, 1ll * m * n, alpha, beta, nullptr, 0, nullptr};
+  return gemm_dispatch(g);
+}
+extern "C" int fastnn_cuda_matmul_nt(const float* a, const float* b, float* c, int m, int n, int k) {
+  GemmArgs g{FASTNN_B200_NT, a, b, c, m, n, k, 1, k, k, n,
+             1ll * m * k, 1ll * n * k, 1ll * m * n, 1.0f, 0.0f, nullptr, 0, nullptr};
+  return gemm_dispatch(g);
+}
+extern "C" int fastnn_cuda_matmul_tn(const float* a, const float* b, float* c, int m, int n, int k) {
+  GemmArgs g{FASTNN_B200_TN, a, b, c, m, n, k, 1, m, n, n,
+             1ll * k * m, 1ll * k * n, 1ll * m * n, 1.0f, 0.0f, nullptr, 0, nullptr};
+  return gemm_dispatch(g);
+}
+extern "C" int fastnn_cuda_matmul_batched_nt(const float* a, const float* b, float* c, int m, int n,
+                                             int k, int batch_size) {
+  GemmArgs g{FASTNN_B200_NT, a, b, c, m, n, k, batch_size, k, k, n,
+             1ll * m * k, 1ll * n * k, 1ll * m * n, 1.0f, 0.0f, nullptr, 0, nullptr};
+  return gemm_dispatch(g);
+}
+extern "C" int fastnn_cuda_matmul_batched_tn(const float* a, const float* b, float* c, int m, int n,
+                                             int k, int batch_size) {
+  GemmArgs g{FASTNN_B200_TN, a, b, c, m, n, k, batch_size, m, n, n,
+             1ll * k * m, 1ll * k * n, 1ll * m * n, 1.0f, 0.0f, nullptr, 0, nullptr};
+  return gemm_dispatch(g);
+}
+
+// ================================================================== additions ===
+
+extern "C" int fastnn_b200_gemm_ex(int layout, const float* a, const float* b, float* c, int m,
+                                   int n, int k, int batch, long long lda, long long ldb,
+                                   long long ldc, long long stride_a, long long stride_b,
+                                   long long stride_c, float alpha, float beta, const float* bias,
+                                   int act, void* stream) {
+  GemmArgs g{layout, a, b, c, m, n, k, batch, lda, ldb, ldc, stride_a, stride_b, stride_c,
+             alpha, beta, bias, act, static_cast<cudaStream_t>(stream)};
+  return gemm_dispatch(g);
+}
+
+extern "C" int fastnn_b200_linear_forward(int layout, const float* x, const float* w,
+                                          const float* bias, float* y, int rows, int in_features,
+                                          int out_features, int act) {
+  if (layout != FASTNN_B200_NT && layout != FASTNN_B200_NN) return -1;
+  const long long ldw = (layout == FASTNN_B200_NT) ? in_features : out_features;
+  GemmArgs g{layout, x, w, y, rows, out_features, in_features, 1, in_features, ldw, out_features,
+             1ll * rows * in_features, 1ll * in_features * out_features, 1ll * rows * out_features,
+             1.0f, 0.0f, bias, act, nullptr};
+  return gemm_dispatch(g);
+}
+
+extern "C" int fastnn_b200_set_policy(int policy, int block_n, int split_k) {
+  if (policy < 0 || policy > 2) return -1;
+  if (block_n < 0 || block_n > fnn::kMaxBlockN || (block_n % 32) != 0) return -1;
+  if (split_k < 0) return -1;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_policy.policy = policy;
+  g_policy.block_n = block_n;
+  g_policy.split_k = split_k;
+  return 0;
+}
+
+extern "C" int fastnn_b200_last_path(int* block_n, int* split_k, int* num_ctas) {
+  if (block_n) *block_n = t_last.block_n;
+  if (split_k) *split_k = t_last.split_k;
+  if (num_ctas) *num_ctas = t_last.num_ctas;
+  return t_last.path;
+}
+
+extern "C" int fastnn_b200_device_status(unsigned int* status) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState* st = current_state();
+  if (st == nullptr) return -1;
+  FNN_CUDA_OK(cudaDeviceSynchronize());
+  unsigned int v = 0;
+  FNN_CUDA_OK(cudaMemcpy(&v, st->status, sizeof(v), cudaMemcpyDeviceToHost));
+  if (v != 0) FNN_CUDA_OK(cudaMemset(st->status, 0, sizeof(v)));
+  if (status) *status = v;
+  return 0;
+}
+
+extern "C" unsigned long long fastnn_b200_launch_count(void) {
+  return g_launches.load(std::memory_order_relaxed);
+}
+
+extern "C" const char* fastnn_b200_version(void) { return "fastnn_b200 0.1 (sm_100a)"; }

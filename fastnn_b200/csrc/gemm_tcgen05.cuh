@@ -1,0 +1,361 @@
+// Persistent, warp-specialised TF32 GEMM for sm_100a.
+//
+//   C[b] = epilogue( A[b] (m x k) . B[b] (k x n) ),  FP32 in memory, TF32 multiply,
+//   FP32 accumulate in tensor memory.
+//
+// One CTA owns one SM and walks a static list of work units (batch, k-split, tile).
+//   warp 0     TMA producer: fills a ring of shared-memory stages (A 128 x 32, B block_n x 32).
+//   warp 1     allocates TMEM; one lane issues tcgen05.mma kind::tf32 (M=128, N=block_n, K=8),
+//              four per stage, into one of two TMEM accumulators.
+//   warps 2-5  epilogue: tcgen05.ld 32 lanes x 32 columns, scale / bias / activation, then
+//              either a 128B-swizzled staging tile + TMA store, or predicated global stores.
+// The transposed layouts never materialise a transpose: an operand whose contiguous
+// dimension is M or N is loaded as 32 x 32 boxes (inner dimension M/N) and handed to the
+// tensor core through an MN-major shared-memory descriptor.
+//
+// Every wait on an mbarrier is bounded: when the budget runs out the waiting role records
+// a code in the status word, raises a CTA-wide abort flag and every role falls through to
+// the common teardown (which frees TMEM), so a bad launch ends with an error, not a hang.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx_sm100.cuh"
+
+namespace fnn {
+
+constexpr int kBlockM = 128;          // rows of C per tile = UMMA M = TMEM lanes
+constexpr int kBlockK = 32;           // floats per stage along K = one 128-byte swizzle row
+constexpr int kUmmaK = 8;             // K of one tcgen05.mma kind::tf32
+constexpr int kMaxBlockN = 256;       // columns of one accumulator
+constexpr int kTmemCols = 512;        // two accumulators
+constexpr int kNumThreads = 192;      // 6 warps
+constexpr int kEpilogueWarp0 = 2;
+constexpr int kStageABytes = kBlockM * kBlockK * 4;            // 16 KiB
+constexpr int kChunkBytes = 32 * kBlockK * 4;                  // one 32 x 32 MN-major box, 4 KiB
+constexpr int kStagingBytesPerWarp = 2 * 32 * 32 * 4;          // two 32 x 32 output tiles
+constexpr int kStagingBytes = 4 * kStagingBytesPerWarp;        // 32 KiB
+constexpr int kMaxStages = 8;
+constexpr int kGroupM = 16;           // tile rows per rasterisation group
+constexpr int kBarrierBytes = 256;
+
+// status codes written by a role whose wait ran out
+enum : unsigned int {
+  kStatusOk = 0,
+  kStatusProducerTimeout = 0x101,
+  kStatusMmaTimeout = 0x102,
+  kStatusEpilogueTimeout = 0x103,
+  kStatusMmaTmemTimeout = 0x104,
+};
+
+enum : int { kActNone = 0, kActRelu = 1, kActGelu = 2 };
+
+struct GemmParams {
+  int m, n, k, batch;
+  int block_n;         // 32..256, multiple of 32
+  int num_stages;
+  int tiles_m, tiles_n;
+  int num_kb;          // ceil(k / 32)
+  int split_k;         // >= 1
+  int kb_per_split;
+  int total_units;     // batch * tiles_m * tiles_n * split_k
+  int a_mn_major;      // A stored [k, m]
+  int b_mn_major;      // B stored [k, n]
+  int store_mode;      // 0: TMA store through tmC, 1: predicated global stores
+  float alpha, beta;
+  const float* bias;   // [n] or null (ignored when split_k > 1: applied by the reduce pass)
+  int act;
+  float* c;            // direct-store target
+  long long ldc, c_batch_stride;   // elements
+  unsigned int* status;
+  long long spin_budget;           // clock64 ticks a single wait may last
+};
+
+struct Unit {
+  int b, s, mt, nt;
+};
+
+__device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u) {
+  Unit w;
+  w.s = u % p.split_k;
+  int t = u / p.split_k;
+  const int tiles = p.tiles_m * p.tiles_n;
+  w.b = t / tiles;
+  t -= w.b * tiles;
+  const int group_sz = kGroupM * p.tiles_n;
+  const int g = t / group_sz;
+  const int first_m = g * kGroupM;
+  const int gm = min(p.tiles_m - first_m, kGroupM);
+  const int r = t - g * group_sz;
+  w.mt = first_m + r % gm;
+  w.nt = r / gm;
+  return w;
+}
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  if (act == kActRelu) return fmaxf(x, 0.0f);
+  if (act == kActGelu) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+  return x;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this role's budget ran out, or
+// another role's did).
+__device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                             const GemmParams& p, unsigned int code) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int it = 0;
+  while (true) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if ((++it & 63) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > p.spin_budget) {
+        atomicCAS(p.status, 0u, code);
+        *abort_flag = 1;
+        __threadfence_block();
+        return false;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 B.
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t stage_b_bytes = static_cast<uint32_t>(p.block_n) * kBlockK * 4;
+  const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
+  const uint32_t staging_base = smem_base + p.num_stages * stage_bytes;
+  const uint32_t bar_base = staging_base + kStagingBytes;
+  // barrier layout: full[8] empty[8] tmem_full[2] tmem_empty[2] | tmem address | abort flag
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 64u + 8u * s; };
+  auto tfull_bar = [&](int a) { return bar_base + 128u + 8u * a; };
+  auto tempty_bar = [&](int a) { return bar_base + 144u + 8u * a; };
+  const uint32_t tmem_slot = bar_base + 160u;
+  uint8_t* bar_gen = smem_gen + (bar_base - smem_base);
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(bar_gen + 160);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 168);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.num_stages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+    ptx::prefetch_tensormap(&tmA);
+    ptx::prefetch_tensormap(&tmB);
+    if (p.store_mode == 0) ptx::prefetch_tensormap(&tmC);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_1cta(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish_1cta();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer ---
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+        const Unit w = decode_unit(p, u);
+        const int m0 = w.mt * kBlockM;
+        const int n0 = w.nt * p.block_n;
+        const int kb0 = w.s * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = wait_barrier(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
+          if (!ok) break;
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint32_t sb = sa + kStageABytes;
+          const uint32_t fb = full_bar(stage);
+          ptx::mbar_expect_tx(fb, stage_bytes);
+          const int k0 = kb * kBlockK;
+          if (!p.a_mn_major) {
+            ptx::tma_load_3d(sa, &tmA, fb, k0, m0, w.b);                       // 32 x 128 box
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBlockM / 32; ++c)
+              ptx::tma_load_3d(sa + c * kChunkBytes, &tmA, fb, m0 + 32 * c, k0, w.b);
+          }
+          if (!p.b_mn_major) {
+            ptx::tma_load_3d(sb, &tmB, fb, k0, n0, w.b);                       // 32 x block_n box
+          } else {
+            for (int c = 0; c < p.block_n / 32; ++c)
+              ptx::tma_load_3d(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b);
+          }
+          if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------------------- MMA issuer ---
+    if (lane == 0) {
+      const uint32_t idesc = ptx::idesc_tf32(kBlockM, p.block_n, p.a_mn_major, p.b_mn_major);
+      // K-major: rows of 128 B, 8-row groups 1024 B apart; one MMA advances 32 B along K.
+      // MN-major: 32-element chunks, each [32 k-rows][128 B]; chunks kBlockK*128 B apart,
+      //           8-k-row groups 1024 B apart; one MMA advances one 8-row group.
+      const uint32_t a_lbo = p.a_mn_major ? kChunkBytes : 16u;
+      const uint32_t b_lbo = p.b_mn_major ? kChunkBytes : 16u;
+      const uint32_t a_kstep = p.a_mn_major ? 1024u : kUmmaK * 4u;
+      const uint32_t b_kstep = p.b_mn_major ? 1024u : kUmmaK * 4u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+        const Unit w = decode_unit(p, u);
+        const int kb0 = w.s * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        ok = wait_barrier(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBlockN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = wait_barrier(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint32_t sb = sa + kStageABytes;
+#pragma unroll
+          for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
+            const uint64_t da = ptx::smem_desc_sw128(sa + ks * a_kstep, a_lbo, 1024u);
+            const uint64_t db = ptx::smem_desc_sw128(sb + ks * b_kstep, b_lbo, 1024u);
+            ptx::mma_tf32_1cta(tmem_d, da, db, idesc, (kb > kb0 || ks > 0) ? 1u : 0u);
+          }
+          ptx::mma_commit_1cta(empty_bar(stage));   // stage reusable once these MMAs retire
+          if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::mma_commit_1cta(tfull_bar(acc));       // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue ---
+    const int q = warp & 3;                          // TMEM lane quadrant this warp may read
+    const uint32_t staging = staging_base + (warp - kEpilogueWarp0) * kStagingBytesPerWarp;
+    uint8_t* staging_gen = smem_gen + (staging - smem_base);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int buf = 0;
+    bool ok = true;
+    const bool raw = p.split_k > 1;                 // partial sums: no scale / bias / activation
+    for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+      const Unit w = decode_unit(p, u);
+      const int m0 = w.mt * kBlockM + q * 32;
+      const int n0 = w.nt * p.block_n;
+      ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                              static_cast<uint32_t>(acc * kMaxBlockN);
+      const int cz = raw ? (w.b * p.split_k + w.s) : w.b;   // outer coordinate of the store
+      const int row = m0 + lane;
+      for (int c = 0; c < p.block_n / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.n) break;                      // warp-uniform
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr0 + c * 32, r);
+        ptx::tmem_ld_wait();
+        if (m0 >= p.m) continue;                     // warp-uniform: rows all out of range
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (!raw) {
+          if (p.alpha != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+          }
+          if (p.beta != 0.0f && row < p.m) {         // only reachable in direct-store mode
+            const float* crow = p.c + w.b * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.n) v[j] += p.beta * crow[col0 + j];
+          }
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
+          }
+          if (p.act != kActNone) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+          }
+        }
+        if (p.store_mode == 0) {
+          // staging tile: 32 rows x 128 B, 16-byte chunk j of row r at chunk (j ^ (r & 7))
+          if (lane == 0) ptx::tma_store_wait_read<1>();   // the tile used two stores ago is free
+          __syncwarp();
+          uint8_t* dst_row = staging_gen + buf * 4096 + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 f = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            *reinterpret_cast<float4*>(dst_row + ((j ^ (lane & 7)) << 4)) = f;
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_3d(&tmC, staging + buf * 4096, col0, m0, cz);
+            ptx::tma_store_commit();
+          }
+          buf ^= 1;
+        } else if (row < p.m) {
+          float* crow = p.c + static_cast<long long>(cz) * p.c_batch_stride +
+                        static_cast<long long>(row) * p.ldc;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.n) crow[col0 + j] = v[j];
+        }
+      }
+      // accumulator drained: hand it back to the MMA warp
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (p.store_mode == 0 && lane == 0) ptx::tma_store_wait_all<0>();
+  }
+
+  // ---------------------------------------------------------------- teardown ---
+  __syncwarp();
+  if (*abort_flag) {
+    // give loads that are still in flight towards this CTA's shared memory time to land
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) { }
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc_1cta(tmem_base, kTmemCols);
+  }
+}
+
+// Bytes of dynamic shared memory a launch with these parameters needs.
+inline size_t gemm_smem_bytes(int block_n, int num_stages) {
+  return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + block_n * kBlockK * 4) +
+         kStagingBytes + kBarrierBytes;
+}
+
+}  // namespace fnn

@@ -1,0 +1,233 @@
+"""Host wrappers over the C ABI, named after FastNN's ``src/tensor/cuda_backend.rs``.
+
+Each ``cuda_matmul*`` wrapper does what its Rust namesake does (cuda_backend.rs:121-147,
+175-204): allocate the output buffer, call the FFI entry with ``lda=k, ldb=n, ldc=n,
+alpha=1, beta=0``, and turn a non-zero status into an error.  ``matmul`` / ``matmul_nt`` /
+``matmul_tn`` add the 2-D-versus-batched dispatch and shape checks of ``Tensor::matmul*``
+(src/tensor/ops.rs:341-518).  Tensors are torch CUDA float32, used for device memory only.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ._lib import lib
+
+NN, NT, TN = 0, 1, 2
+ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
+
+
+class CudaError(RuntimeError):
+    """A C-ABI entry returned non-zero (FastNN maps this to Err(String))."""
+
+
+_initialised = set()
+
+
+def cuda_init(device: int = 0) -> None:
+    """CudaContext::new (src/cuda/context.rs:19-29): once per device."""
+    if device in _initialised:
+        return
+    if lib().fastnn_cuda_init(int(device)) != 0:
+        raise CudaError(f"Failed to initialize CUDA device {device}")
+    _initialised.add(device)
+
+
+def synchronize() -> None:
+    if lib().fastnn_cuda_synchronize() != 0:
+        raise CudaError("CUDA synchronize failed")
+
+
+def _check(t: torch.Tensor, name: str) -> None:
+    if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()):
+        raise ValueError(f"{name}: expected a contiguous float32 CUDA tensor")
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _ensure_ctx(t: torch.Tensor) -> None:
+    dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
+    if torch.cuda.current_device() != dev:
+        raise ValueError("tensor is not on the current CUDA device")
+    cuda_init(dev)
+
+
+def _out(shape, like, out):
+    if out is None:
+        return torch.empty(shape, dtype=torch.float32, device=like.device)
+    _check(out, "out")
+    if tuple(out.shape) != tuple(shape):
+        raise ValueError("out has the wrong shape")
+    return out
+
+
+# ---- FFI-level wrappers (names of cuda_backend.rs) -----------------------------------
+
+def cuda_matmul(a, b, m, n, k, out=None, alpha=1.0, beta=0.0):
+    _ensure_ctx(a)
+    c = _out((m, n), a, out)
+    if lib().fastnn_cuda_matmul(_ptr(a), _ptr(b), _ptr(c), m, n, k, k, n, n, alpha, beta) != 0:
+        raise CudaError("CUDA matmul failed")
+    return c
+
+
+def cuda_matmul_batched(a, b, m, n, k, batch, out=None, alpha=1.0, beta=0.0):
+    _ensure_ctx(a)
+    c = _out((batch, m, n), a, out)
+    if lib().fastnn_cuda_matmul_batched(_ptr(a), _ptr(b), _ptr(c), m, n, k, batch, alpha, beta) != 0:
+        raise CudaError("CUDA batched matmul failed")
+    return c
+
+
+def cuda_matmul_nt(a, b, m, n, k, out=None):
+    _ensure_ctx(a)
+    c = _out((m, n), a, out)
+    if lib().fastnn_cuda_matmul_nt(_ptr(a), _ptr(b), _ptr(c), m, n, k) != 0:
+        raise CudaError("CUDA matmul_nt failed")
+    return c
+
+
+def cuda_matmul_tn(a, b, m, n, k, out=None):
+    _ensure_ctx(a)
+    c = _out((m, n), a, out)
+    if lib().fastnn_cuda_matmul_tn(_ptr(a), _ptr(b), _ptr(c), m, n, k) != 0:
+        raise CudaError("CUDA matmul_tn failed")
+    return c
+
+
+def cuda_matmul_batched_nt(a, b, m, n, k, batch, out=None):
+    _ensure_ctx(a)
+    c = _out((batch, m, n), a, out)
+    if lib().fastnn_cuda_matmul_batched_nt(_ptr(a), _ptr(b), _ptr(c), m, n, k, batch) != 0:
+        raise CudaError("CUDA matmul_batched_nt failed")
+    return c
+
+
+def cuda_matmul_batched_tn(a, b, m, n, k, batch, out=None):
+    _ensure_ctx(a)
+    c = _out((batch, m, n), a, out)
+    if lib().fastnn_cuda_matmul_batched_tn(_ptr(a), _ptr(b), _ptr(c), m, n, k, batch) != 0:
+        raise CudaError("CUDA matmul_batched_tn failed")
+    return c
+
+
+# ---- Tensor-level dispatch (src/tensor/ops.rs) ------------------------------------------
+
+def _batch_of(t):
+    n = 1
+    for s in t.shape[:-2]:
+        n *= int(s)
+    return n
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, out=None) -> torch.Tensor:
+    """Tensor::matmul (ops.rs:341-438) for CUDA tensors: 2-D, or batched over leading dims.
+
+    The batched C ABI has no broadcast (dense strides m*k and k*n), so a batch-1 operand is
+    rejected here rather than read out of bounds."""
+    _check(a, "a"); _check(b, "b")
+    if a.dim() < 2 or b.dim() < 2:
+        raise ValueError("matmul requires at least 2D tensors")
+    m, k = int(a.shape[-2]), int(a.shape[-1])
+    k2, n = int(b.shape[-2]), int(b.shape[-1])
+    if k != k2:
+        raise ValueError(f"Matmul shape mismatch: {tuple(a.shape)} x {tuple(b.shape)}")
+    if a.dim() == 2 and b.dim() == 2:
+        return cuda_matmul(a, b, m, n, k, out)
+    ab, bb = _batch_of(a), _batch_of(b)
+    if ab != bb:
+        raise ValueError("Batch dimensions must match on CUDA tensors")
+    c = cuda_matmul_batched(a, b, m, n, k, ab,
+                            None if out is None else out.view(ab, m, n))
+    return c.view(*a.shape[:-2], m, n) if out is None else out
+
+
+def matmul_nt(a: torch.Tensor, b: torch.Tensor, out=None) -> torch.Tensor:
+    """Tensor::matmul_nt (ops.rs:441-478): a[..,m,k] . b[..,n,k]^T."""
+    _check(a, "a"); _check(b, "b")
+    m, k = int(a.shape[-2]), int(a.shape[-1])
+    n, k2 = int(b.shape[-2]), int(b.shape[-1])
+    if k != k2:
+        raise ValueError("matmul_nt shape mismatch")
+    if a.dim() == 2 and b.dim() == 2:
+        return cuda_matmul_nt(a, b, m, n, k, out)
+    batch = _batch_of(a)
+    if batch != _batch_of(b):
+        raise ValueError("Batch dimensions must match")
+    c = cuda_matmul_batched_nt(a, b, m, n, k, batch,
+                               None if out is None else out.view(batch, m, n))
+    return c.view(*a.shape[:-2], m, n) if out is None else out
+
+
+def matmul_tn(a: torch.Tensor, b: torch.Tensor, out=None) -> torch.Tensor:
+    """Tensor::matmul_tn (ops.rs:481-518): a[..,k,m]^T . b[..,k,n]."""
+    _check(a, "a"); _check(b, "b")
+    k, m = int(a.shape[-2]), int(a.shape[-1])
+    k2, n = int(b.shape[-2]), int(b.shape[-1])
+    if k != k2:
+        raise ValueError("matmul_tn shape mismatch")
+    if a.dim() == 2 and b.dim() == 2:
+        return cuda_matmul_tn(a, b, m, n, k, out)
+    batch = _batch_of(a)
+    if batch != _batch_of(b):
+        raise ValueError("Batch dimensions must match")
+    c = cuda_matmul_batched_tn(a, b, m, n, k, batch,
+                               None if out is None else out.view(batch, m, n))
+    return c.view(*a.shape[:-2], m, n) if out is None else out
+
+
+# ---- additions ------------------------------------------------------------------------------
+
+def linear_forward(x, w, bias=None, act=ACT_NONE, layout=NT, out=None):
+    """Linear::forward (src/nn/linear.rs:55-88) + optional ReLU/GELU in one launch.
+    layout NT: w is [out,in] as FastNN stores it; NN: w is [in,out]."""
+    _check(x, "x"); _check(w, "w")
+    _ensure_ctx(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    rows, in_f = int(x2.shape[0]), int(x2.shape[1])
+    out_f = int(w.shape[0] if layout == NT else w.shape[1])
+    if int(w.shape[1] if layout == NT else w.shape[0]) != in_f:
+        raise ValueError(f"Expected input features {in_f}")
+    if bias is not None:
+        _check(bias, "bias")
+    y = _out((rows, out_f), x, out)
+    if lib().fastnn_b200_linear_forward(layout, _ptr(x2), _ptr(w), _ptr(bias), _ptr(y), rows, in_f,
+                                        out_f, act) != 0:
+        raise CudaError("CUDA linear_forward failed")
+    return y.view(*x.shape[:-1], out_f)
+
+
+def gemm_ex(layout, a_ptr, b_ptr, c_ptr, m, n, k, batch, lda, ldb, ldc, sa, sb, sc,
+            alpha=1.0, beta=0.0, bias_ptr=0, act=ACT_NONE, stream=0) -> None:
+    """Raw general entry (pointers as integers, strides in elements)."""
+    rc = lib().fastnn_b200_gemm_ex(layout, ctypes.c_void_p(a_ptr), ctypes.c_void_p(b_ptr),
+                                   ctypes.c_void_p(c_ptr), m, n, k, batch, lda, ldb, ldc, sa, sb, sc,
+                                   alpha, beta, ctypes.c_void_p(bias_ptr), act,
+                                   ctypes.c_void_p(stream))
+    if rc != 0:
+        raise CudaError("fastnn_b200_gemm_ex failed")
+
+
+def set_policy(policy: int = 0, block_n: int = 0, split_k: int = 0) -> None:
+    if lib().fastnn_b200_set_policy(policy, block_n, split_k) != 0:
+        raise ValueError("bad policy")
+
+
+def last_path():
+    bn, sk, nc = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    path = lib().fastnn_b200_last_path(ctypes.byref(bn), ctypes.byref(sk), ctypes.byref(nc))
+    return {"path": path, "block_n": bn.value, "split_k": sk.value, "num_ctas": nc.value}
+
+
+def device_status() -> int:
+    v = ctypes.c_uint()
+    if lib().fastnn_b200_device_status(ctypes.byref(v)) != 0:
+        raise CudaError("device_status failed")
+    return v.value
+
+
+def launch_count() -> int:
+    return int(lib().fastnn_b200_launch_count())

@@ -1,0 +1,134 @@
+/*
+ * C ABI of libfastnn_b200.so: the matrix-multiply path of FastNN's CUDA backend,
+ * implemented with hand-written sm_100a kernels (tcgen05 kind::tf32, TMA, TMEM).
+ *
+ * Section 1 re-declares, with identical names, argument order and meaning, the entry
+ * points FastNN's Rust side binds for this path (FastNN: cuda/include/kernels.h;
+ * callers in src/tensor/cuda_backend.rs, src/cuda/memory.rs, src/cuda/context.rs), so
+ * the library can be linked in place of FastNN's own kernels for these symbols.
+ * Section 2 adds entry points FastNN does not have (fused Linear epilogue, explicit
+ * leading dimensions and stream, diagnostics); their names carry the fastnn_b200_ prefix.
+ *
+ * Conventions (same as FastNN): all matrices are dense row-major float32 in device
+ * memory; every function returns 0 on success and -1 on failure; work is enqueued on
+ * the legacy default stream unless a stream is passed explicitly; the caller owns all
+ * buffers and the callee writes every element of the output (an output buffer may be
+ * recycled and dirty).  There is no CPU fallback: without a CUDA device every compute
+ * entry returns -1.
+ */
+#ifndef FASTNN_B200_KERNELS_H
+#define FASTNN_B200_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+/* Every entry point below has default ELF visibility; nothing else is exported. */
+#if defined(__GNUC__)
+#define FASTNN_B200_API __attribute__((visibility("default")))
+#else
+#define FASTNN_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------ */
+/* 1. FastNN drop-in symbols                                                */
+/* ------------------------------------------------------------------------ */
+
+/* Device management -- FastNN cuda/include/kernels.h:13-16, cuda/kernels.cu:35-64.
+ * fastnn_cuda_init must be called (per process, per device used) before any GEMM. */
+FASTNN_B200_API int fastnn_cuda_init(int device_id);
+FASTNN_B200_API int fastnn_cuda_device_count(void);
+FASTNN_B200_API int fastnn_cuda_synchronize(void);
+FASTNN_B200_API void fastnn_cuda_get_memory_info(size_t* free_mem, size_t* total_mem);
+
+/* Memory -- FastNN cuda/include/kernels.h:21-26, cuda/kernels.cu:69-97.  Sizes in BYTES;
+ * copies are synchronous. */
+FASTNN_B200_API int fastnn_cuda_malloc(float** ptr, size_t size);
+FASTNN_B200_API int fastnn_cuda_free(float* ptr);
+FASTNN_B200_API int fastnn_cuda_memcpy_h2d(float* dst, const float* src, size_t size);
+FASTNN_B200_API int fastnn_cuda_memcpy_d2h(float* dst, const float* src, size_t size);
+FASTNN_B200_API int fastnn_cuda_memcpy_d2d(float* dst, const float* src, size_t size);
+FASTNN_B200_API int fastnn_cuda_memset(float* ptr, int value, size_t size);
+
+/* C[m,n] = alpha * A[m,k] . B[k,n] + beta * C, leading dimensions in elements.
+ * FastNN cuda/include/kernels.h:71-74, cuda/kernels.cu:431-445. */
+FASTNN_B200_API int fastnn_cuda_matmul(const float* a, const float* b, float* c,
+                       int m, int n, int k,
+                       int lda, int ldb, int ldc,
+                       float alpha, float beta);
+/* Per batch C[m,n] = alpha * A[m,k] . B[k,n] + beta * C, dense strides m*k, k*n, m*n.
+ * FastNN cuda/include/kernels.h:75-77, cuda/kernels.cu:509-526. */
+FASTNN_B200_API int fastnn_cuda_matmul_batched(const float* a, const float* b, float* c,
+                               int m, int n, int k, int batch_size,
+                               float alpha, float beta);
+/* C[m,n] = A[m,k] . B^T, B stored [n,k].  FastNN kernels.h:78, kernels.cu:452-461. */
+FASTNN_B200_API int fastnn_cuda_matmul_nt(const float* a, const float* b, float* c, int m, int n, int k);
+/* C[m,n] = A^T . B[k,n], A stored [k,m].  FastNN kernels.h:79, kernels.cu:464-473. */
+FASTNN_B200_API int fastnn_cuda_matmul_tn(const float* a, const float* b, float* c, int m, int n, int k);
+/* Batched forms, dense strides.  FastNN kernels.h:80-81, kernels.cu:476-507. */
+FASTNN_B200_API int fastnn_cuda_matmul_batched_nt(const float* a, const float* b, float* c,
+                                  int m, int n, int k, int batch_size);
+FASTNN_B200_API int fastnn_cuda_matmul_batched_tn(const float* a, const float* b, float* c,
+                                  int m, int n, int k, int batch_size);
+
+/* ------------------------------------------------------------------------ */
+/* 2. Additions (no FastNN symbol of these names)                            */
+/* ------------------------------------------------------------------------ */
+
+/* layout of the two operands */
+#define FASTNN_B200_NN 0   /* A[m,k], B[k,n] */
+#define FASTNN_B200_NT 1   /* A[m,k], B[n,k] */
+#define FASTNN_B200_TN 2   /* A[k,m], B[k,n] */
+
+/* epilogue activation */
+#define FASTNN_B200_ACT_NONE 0
+#define FASTNN_B200_ACT_RELU 1   /* max(x, 0)                   -- FastNN src/tensor/ops.rs:191-198 */
+#define FASTNN_B200_ACT_GELU 2   /* 0.5 x (1 + erf(x / sqrt 2)) -- FastNN src/tensor/ops.rs:220-230 */
+
+/* General form behind every GEMM entry:
+ *   C[b] = act( alpha * op(A[b]) . op(B[b]) + beta * C[b] + bias )      b in [0, batch)
+ * lda/ldb/ldc are row strides in elements, stride_a/b/c are batch strides in elements,
+ * bias is [n] or NULL, stream is a cudaStream_t (NULL = legacy default stream).
+ * Replaces, in one launch, the transpose + matmul + expand + add (+ gelu/relu) sequence of
+ * FastNN's Linear::forward (src/nn/linear.rs:71-87). */
+FASTNN_B200_API int fastnn_b200_gemm_ex(int layout, const float* a, const float* b, float* c,
+                        int m, int n, int k, int batch,
+                        long long lda, long long ldb, long long ldc,
+                        long long stride_a, long long stride_b, long long stride_c,
+                        float alpha, float beta,
+                        const float* bias, int act, void* stream);
+
+/* y[rows,out] = act( x[rows,in] . W + bias[out] ) with dense operands.
+ * layout NT takes W as FastNN stores it, [out,in] (Linear's weight); layout NN takes W
+ * already as [in,out].  Semantics of Linear::forward (+ Tensor::relu / Tensor::gelu). */
+FASTNN_B200_API int fastnn_b200_linear_forward(int layout, const float* x, const float* w, const float* bias,
+                               float* y, int rows, int in_features, int out_features, int act);
+
+/* Kernel selection for tests and sweeps.  policy: 0 = automatic (tcgen05 path whenever the
+ * operands meet TMA's 16-byte alignment rules, SIMT path otherwise), 1 = SIMT path only,
+ * 2 = tcgen05 path only (calls that cannot use it fail with -1).
+ * block_n in {0 (auto), 32, 64, 96, ..., 256}; split_k >= 0 (0 = auto). */
+FASTNN_B200_API int fastnn_b200_set_policy(int policy, int block_n, int split_k);
+
+/* Which path the most recent GEMM call on this thread took: 1 = SIMT, 2 = tcgen05
+ * 1-CTA, 3 = tcgen05 2-CTA; 0 before any call.  Also reports its tile and split choice. */
+FASTNN_B200_API int fastnn_b200_last_path(int* block_n, int* split_k, int* num_ctas);
+
+/* Reads and clears the device status word (synchronises the device).  0 = no kernel
+ * reported a problem; otherwise the code of the first bounded wait that ran out. */
+FASTNN_B200_API int fastnn_b200_device_status(unsigned int* status);
+
+/* Number of kernels this library has launched since load (all threads). */
+FASTNN_B200_API unsigned long long fastnn_b200_launch_count(void);
+
+/* Library version string, static storage. */
+FASTNN_B200_API const char* fastnn_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FASTNN_B200_KERNELS_H */
