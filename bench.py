@@ -1,0 +1,499 @@
+#!/usr/bin/env python
+"""Benchmark of the FastNN matmul path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference_gpu]
+                    [--workload square8192|linear_gelu|char_lm|attention|mnist_l1]
+                    [--scaling weak|strong] [--gather]
+
+One "step" is one pass of the workload's GEMMs over synthetic, seeded operands.  The default
+workload is the large square configuration: C = A.B (NN), A.B^T (NT) and A^T.B (TN) with
+M = N = K = 8192, FP32 operands ~ N(0,1), TF32 multiply, FP32 accumulate.
+
+* --impl ours       the hand-written sm_100a kernels behind the C ABI (libfastnn_b200.so).
+                    `value` is measured with operands resident in HBM; `e2e` goes through the
+                    same C ABI starting and ending in pinned host buffers.
+* --impl reference  FastNN's CPU matmul (C restatement of its serial loop nest, rows split over
+                    all host threads) on a bounded row slab of the same workload.
+* --impl reference_gpu  FastNN's own cuda/kernels.cu (cuBLAS TF32) built for sm_100a, when that
+                    library has been built; a comparator, never part of the product path.
+
+Multi-GPU (torchrun, one rank per GPU): the output rows M (or the batch) are partitioned over
+the ranks with the other operand replicated -- no collective on the data path.  Weak scaling
+(default) keeps 8192 rows per rank; --scaling strong splits 8192 rows over the ranks; --gather
+adds an NCCL all-gather of the C shards (reported separately, never inside `value`).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+NN, NT, TN = 0, 1, 2
+NOMINAL_TF32_TFLOPS = 1100.0     # dense, NVIDIA's per-GPU figure (half the 2:4-sparse number)
+FALLBACK_BF16_TFLOPS = 1590.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+# ------------------------------------------------------------------------- workloads ---
+
+def workload_spec(name, rows_scale=1.0):
+    """List of GEMMs of one step: dict(layout, m, n, k, batch, bias, act, name).
+
+    FLOPs = 2 m n k batch; algorithmic bytes = each operand once, FP32."""
+    def g(layout, m, n, k, batch=1, bias=False, act=0, label=""):
+        return dict(layout=layout, m=int(m), n=int(n), k=int(k), batch=batch, bias=bias, act=act,
+                    label=label)
+    if name == "square8192":
+        m = int(8192 * rows_scale)
+        return [g(NN, m, 8192, 8192, label="NN"), g(NT, m, 8192, 8192, label="NT"),
+                g(TN, m, 8192, 8192, label="TN")]
+    if name == "linear_gelu":
+        m = int(32768 * rows_scale)
+        return [g(NN, m, 16384, 4096, bias=True, act=2, label="fwd NN+bias+GELU"),
+                g(NT, m, 4096, 16384, label="dX NT"),
+                g(TN, 4096, 16384, m, label="dW TN")]
+    if name == "char_lm":
+        m = int(8192 * rows_scale)
+        out = []
+        for k, n, tag in ((256, 768, "qkv"), (256, 256, "o"), (256, 1024, "ff1"), (1024, 256, "ff2")):
+            out += [g(NN, m, n, k, label=f"{tag} fwd"), g(NT, m, k, n, label=f"{tag} dX"),
+                    g(TN, k, n, m, label=f"{tag} dW")]
+        return out
+    if name == "attention":
+        b = int(512 * rows_scale)
+        return [g(NT, 128, 128, 32, batch=b, label="S=Q.K^T"), g(NN, 128, 32, 128, batch=b, label="O=P.V")]
+    if name == "mnist_l1":
+        return [g(NN, int(512 * rows_scale), 256, 784, bias=True, label="layer1")]
+    raise SystemExit(f"unknown workload {name}")
+
+
+def gemm_flops(s):
+    return 2.0 * s["m"] * s["n"] * s["k"] * s["batch"]
+
+
+def gemm_bytes(s):
+    return 4.0 * s["batch"] * (s["m"] * s["k"] + s["k"] * s["n"] + s["m"] * s["n"]) + \
+        (4.0 * s["n"] if s["bias"] else 0.0)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            p = json.load(fh)
+        return dict(source="measured", hbm_gbs=float(p["hbm_gbs"]),
+                    bf16_burst=float(p["bf16_tflops"]),
+                    bf16_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])))
+    except Exception:
+        return dict(source="fallback", hbm_gbs=FALLBACK_HBM_GBS, bf16_burst=FALLBACK_BF16_TFLOPS,
+                    bf16_sustained=1400.0)
+
+
+# -------------------------------------------------------------------- clock sampling ---
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 100 ms on one GPU."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.t0 = [], None, None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t_start, t_end):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        inside = [r for t, r in self.rows if t_start <= t <= t_end + 0.12] or [r for _, r in self.rows]
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in inside:
+            parts = [x.strip() for x in r.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# -------------------------------------------------------------------------- our arm ---
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import fastnn_b200 as f
+
+    torch.cuda.set_device(local_rank)
+    f.cuda_init(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    scale = (1.0 / world) if (args.scaling == "strong" and world > 1) else 1.0
+    spec = workload_spec(args.workload, scale)
+
+    gen = torch.Generator(device="cuda").manual_seed(1000 + rank)     # this rank's rows / batches
+    gen_b = torch.Generator(device="cuda").manual_seed(2000)         # replicated operand
+    ops = []
+    for s in spec:
+        lay, m, n, k, b = s["layout"], s["m"], s["n"], s["k"], s["batch"]
+        sa = (k, m) if lay == TN else (m, k)
+        sb = (n, k) if lay == NT else (k, n)
+        if b > 1:
+            sa, sb = (b,) + sa, (b,) + sb
+        a = torch.randn(sa, device="cuda", generator=gen)
+        bm = torch.randn(sb, device="cuda", generator=gen if b > 1 else gen_b)
+        if args.workload in ("char_lm",):
+            bm = bm * 0.02
+        c = torch.empty(((b,) if b > 1 else ()) + (m, n), device="cuda")
+        bias = (torch.rand(n, device="cuda", generator=gen) * 0.02 - 0.01) if s["bias"] else None
+        ops.append((s, a, bm, c, bias))
+
+    def launch(s, a, bm, c, bias):
+        lay = s["layout"]
+        if s["bias"] or s["act"]:
+            f.linear_forward(a, bm, bias, act=s["act"], layout=lay, out=c)
+        elif lay == NN:
+            f.matmul(a, bm, out=c)
+        elif lay == NT:
+            f.matmul_nt(a, bm, out=c)
+        else:
+            f.matmul_tn(a, bm, out=c)
+
+    def step():
+        for op in ops:
+            launch(*op)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        time.sleep(0.25)
+    n0 = f.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_start = time.time()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    t_end = time.time()
+    launches = f.launch_count() - n0
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+    clocks = sampler.stop(t_start, t_end) if sampler else None
+    assert f.device_status() == 0, "a kernel reported a bounded-wait timeout"
+
+    # per-GEMM device time (own events, after the headline region) for the roofline entry
+    per_gemm = []
+    for op in ops:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(3, min(20, args.steps))
+        launch(*op)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            launch(*op)
+        e1.record()
+        torch.cuda.synchronize()
+        per_gemm.append(e0.elapsed_time(e1) / reps)
+
+    # end to end through the C ABI: pinned host operands -> device -> GEMMs -> host results
+    e2e = None
+    if not args.no_e2e:
+        lib = f.lib()
+        import ctypes
+        host = []
+        for s, a, bm, c, bias in ops:
+            host.append((a.cpu().pin_memory(), bm.cpu().pin_memory(),
+                         torch.empty(c.shape, dtype=torch.float32).pin_memory()))
+        h2d = sum(h[0].numel() + h[1].numel() for h in host) * 4
+        d2h = sum(h[2].numel() for h in host) * 4
+
+        def vp(t):
+            return ctypes.c_void_p(t.data_ptr())
+
+        def e2e_step():
+            for (s, a, bm, c, bias), (ha, hb, hc) in zip(ops, host):
+                assert lib.fastnn_cuda_memcpy_h2d(vp(a), vp(ha), ha.numel() * 4) == 0
+                assert lib.fastnn_cuda_memcpy_h2d(vp(bm), vp(hb), hb.numel() * 4) == 0
+                launch(s, a, bm, c, bias)
+                assert lib.fastnn_cuda_memcpy_d2h(vp(hc), vp(c), hc.numel() * 4) == 0
+
+        e2e_steps = max(1, min(args.steps, args.e2e_steps))
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        dt = torch.tensor([time.perf_counter() - t0], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        flops_step = sum(gemm_flops(s) for s in spec) * world
+        e2e = {"value": flops_step * e2e_steps / float(dt.item()) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e2e_steps}
+
+    gather_ms = None
+    if args.gather and world > 1:
+        s, a, bm, c, bias = ops[0]
+        full = torch.empty((world,) + tuple(c.shape), device="cuda")
+        for _ in range(3):
+            dist.all_gather_into_tensor(full, c)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            dist.all_gather_into_tensor(full, c)
+        e1.record()
+        barrier()
+        g = torch.tensor([e0.elapsed_time(e1) / 10], device="cuda")
+        dist.all_reduce(g, op=dist.ReduceOp.MAX)
+        gather_ms = float(g.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks = load_peaks()
+    flops_step = sum(gemm_flops(s) for s in spec)
+    value = flops_step * world * args.steps / (ms_total * 1e-3) / 1e12
+    # dominant kernel = the GEMM with the most device time
+    top = max(range(len(spec)), key=lambda i: per_gemm[i])
+    ts = spec[top]
+    ai = gemm_flops(ts) / gemm_bytes(ts)
+    tf32_peak = peaks["bf16_sustained"] / 2.0
+    ridge = tf32_peak * 1e12 / (peaks["hbm_gbs"] * 1e9)
+    if ai >= ridge:
+        ach = gemm_flops(ts) / (per_gemm[top] * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": ach, "peak": tf32_peak, "unit": "TFLOP/s",
+                "frac": ach / tf32_peak,
+                "peak_source": f"0.5 x {peaks['source']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s",
+                "frac_of_nominal_tf32": ach / NOMINAL_TF32_TFLOPS}
+    else:
+        ach = gemm_bytes(ts) / (per_gemm[top] * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": ach / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth"}
+    roof["kernel"] = "gemm_tf32_kernel"
+    roof["gemm"] = f"{ts['label']} m{ts['m']} n{ts['n']} k{ts['k']} b{ts['batch']}"
+    roof["ms_per_launch"] = per_gemm[top]
+    roof["traffic"] = TRAFFIC_BYTES.get((args.workload, ts["label"]))
+
+    line = {
+        "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "tf32",
+        "data": "synthetic",
+        "config": {"workload": args.workload,
+                   "gemms": [f"{s['label']}:{s['m']}x{s['n']}x{s['k']}" +
+                             (f"x{s['batch']}" if s["batch"] > 1 else "") for s in spec],
+                   "partition": "rows of C (batch for batched GEMMs) per rank, B replicated",
+                   "l2": "operands larger than L2" if max(gemm_bytes(s) for s in spec) > 3 * 126e6
+                   else "operands fit L2; back-to-back launches"},
+        "per_gemm_ms": {s["label"]: t for s, t in zip(spec, per_gemm)},
+        "per_gemm_tflops": {s["label"]: gemm_flops(s) / (t * 1e-3) / 1e12 for s, t in zip(spec, per_gemm)},
+        "roofline": roof, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if gather_ms is not None:
+        line["allgather_ms"] = gather_ms
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_baseline(args.workload, target_s=args.cpu_seconds)
+    elif world == 1:
+        line["cpu_baseline"] = None
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ncu-derived DRAM traffic per launch (bytes), filled from profiles/ for the kernels captured
+TRAFFIC_BYTES = {}
+
+
+# -------------------------------------------------------------------- CPU reference ---
+
+def cpu_baseline(workload, target_s=12.0, threads=None):
+    """Times the CPU restatement of FastNN's matmul (rows split over host threads) on a row
+    slab of the workload's first GEMM, sized for about `target_s` seconds."""
+    import numpy as np
+    import oracle
+    t = threads or oracle.host_threads()
+    s = workload_spec(workload)[0]
+    m, n, k = s["m"], s["n"], s["k"]
+    rng = np.random.default_rng(0)
+    probe_rows = max(t, min(m, 2 * t))
+    a = rng.standard_normal((max(probe_rows, 1), k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    t0 = time.perf_counter()
+    oracle.matmul(a[:probe_rows], b, threads=t)
+    dt = time.perf_counter() - t0
+    rate = 2.0 * probe_rows * n * k / dt
+    rows = int(min(m, max(probe_rows, target_s * rate / (2.0 * n * k))))
+    rows = max(t, rows // t * t)
+    a = rng.standard_normal((rows, k), dtype=np.float32)
+    t0 = time.perf_counter()
+    oracle.matmul(a, b, threads=t)
+    dt = time.perf_counter() - t0
+    val = 2.0 * rows * n * k / dt / 1e12
+    return {"value": val, "unit": "TFLOP/s", "cores": t, "kind": "port",
+            "sample": f"{rows} of {m} rows of the {s['label']} GEMM (n={n}, k={k}), {dt:.1f} s",
+            "seconds": dt}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    import numpy as np
+    import oracle
+    t = oracle.host_threads()
+    s = workload_spec(args.workload)[0]
+    m, n, k = s["m"], s["n"], s["k"]
+    rng = np.random.default_rng(0)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    a = rng.standard_normal((2 * t, k), dtype=np.float32)
+    t0 = time.perf_counter()
+    oracle.matmul(a, b, threads=t)
+    rate = 2.0 * a.shape[0] * n * k / (time.perf_counter() - t0)
+    budget = 150.0 / max(1, args.steps + args.warmup)          # whole run within a few minutes
+    rows = int(min(m, max(t, min(budget, 10.0) * rate / (2.0 * n * k))))
+    rows = max(t, rows // t * t)
+    a = rng.standard_normal((rows, k), dtype=np.float32)
+    for _ in range(args.warmup):
+        oracle.matmul(a, b, threads=t)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.matmul(a, b, threads=t)
+    dt = time.perf_counter() - t0
+    val = 2.0 * rows * n * k * args.steps / dt / 1e12
+    sample = f"{rows} of {m} rows of the {s['label']} GEMM (n={n}, k={k}) per step"
+    line = {
+        "impl": "reference", "metric": "gemm_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": args.scaling,
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": t, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_reference_gpu(args, rank, world, local_rank):
+    """FastNN's own GPU library (cuBLAS TF32) on the same workload -- comparator only."""
+    if rank != 0:
+        return
+    import ctypes
+    import torch
+    import oracle
+    path = oracle.ref_gpu_library_path()
+    if path is None:
+        print(json.dumps({"impl": "reference_gpu", "unavailable": "oracle/_ref/libfastnn_ref.so not built"}))
+        return
+    torch.cuda.set_device(local_rank)
+    lib = ctypes.CDLL(path)
+    assert lib.fastnn_cuda_init(local_rank) == 0
+    spec = workload_spec(args.workload)
+    gen = torch.Generator(device="cuda").manual_seed(1000)
+    vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    out = {}
+    for s in spec:
+        lay, m, n, k, b = s["layout"], s["m"], s["n"], s["k"], s["batch"]
+        a = torch.randn(b * m * k, device="cuda", generator=gen)
+        bm = torch.randn(b * k * n, device="cuda", generator=gen)
+        c = torch.empty(b * m * n, device="cuda")
+        pa, pb, pc = vp(a.data_ptr()), vp(bm.data_ptr()), vp(c.data_ptr())
+
+        def call():
+            if b > 1:
+                if lay == NN:
+                    return lib.fastnn_cuda_matmul_batched(pa, pb, pc, ci(m), ci(n), ci(k), ci(b), cf(1), cf(0))
+                name = "fastnn_cuda_matmul_batched_nt" if lay == NT else "fastnn_cuda_matmul_batched_tn"
+                return getattr(lib, name)(pa, pb, pc, ci(m), ci(n), ci(k), ci(b))
+            if lay == NN:
+                return lib.fastnn_cuda_matmul(pa, pb, pc, ci(m), ci(n), ci(k), ci(k), ci(n), ci(n), cf(1), cf(0))
+            name = "fastnn_cuda_matmul_nt" if lay == NT else "fastnn_cuda_matmul_tn"
+            return getattr(lib, name)(pa, pb, pc, ci(m), ci(n), ci(k))
+        for _ in range(max(3, args.warmup)):
+            assert call() == 0
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        out[s["label"]] = {"ms": ms, "tflops": gemm_flops(s) / (ms * 1e-3) / 1e12,
+                           "gbs": gemm_bytes(s) / (ms * 1e-3) / 1e9}
+    print(json.dumps({"impl": "reference_gpu", "what": "FastNN cuda/kernels.cu (cuBLAS TF32; bias/activation not included)",
+                      "workload": args.workload, "per_gemm": out}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_gpu"])
+    ap.add_argument("--workload", default="square8192")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--gather", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    elif args.impl == "reference_gpu":
+        run_reference_gpu(args, rank, world, local_rank)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

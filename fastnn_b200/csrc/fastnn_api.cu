@@ -78,9 +78,11 @@ DeviceState* current_state() {
   return st->ready ? st : nullptr;
 }
 
-// 3-D FP32 tensor map, 128-byte swizzle, zero fill outside the tensor.
+// 3-D FP32 tensor map, 128-byte swizzle span, zero fill outside the tensor.  `atom32` selects
+// the 32-byte swizzle unit that MN-major TF32 operands need; otherwise the unit is 16 bytes.
 bool encode_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
-                uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1) {
+                uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1,
+                bool atom32 = false) {
   if (g_encode == nullptr) return false;
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
@@ -88,7 +90,8 @@ bool encode_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, ui
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims,
                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -250,11 +253,11 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   if (!p.a_mn_major)
     ok = encode_map(&tmA, g.a, g.k, g.m, B, g.lda * 4ull, sa_bytes, fnn::kBlockK, fnn::kBlockM);
   else
-    ok = encode_map(&tmA, g.a, g.m, g.k, B, g.lda * 4ull, sa_bytes, 32, fnn::kBlockK);
+    ok = encode_map(&tmA, g.a, g.m, g.k, B, g.lda * 4ull, sa_bytes, 32, fnn::kBlockK, true);
   if (!p.b_mn_major)
     ok = ok && encode_map(&tmB, g.b, g.k, g.n, B, g.ldb * 4ull, sb_bytes, fnn::kBlockK, plan.block_n);
   else
-    ok = ok && encode_map(&tmB, g.b, g.n, g.k, B, g.ldb * 4ull, sb_bytes, 32, fnn::kBlockK);
+    ok = ok && encode_map(&tmB, g.b, g.n, g.k, B, g.ldb * 4ull, sb_bytes, 32, fnn::kBlockK, true);
   if (tma_store) {
     const uint64_t sc_bytes = (out_z > 1 ? out_bs : out_ld * g.m) * 4ull;
     ok = ok && encode_map(&tmC, out, g.n, g.m, static_cast<uint64_t>(out_z), out_ld * 4ull,

@@ -211,11 +211,17 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ----------------------------------------------------------- MMA issuer ---
     if (lane == 0) {
       const uint32_t idesc = ptx::idesc_tf32(kBlockM, p.block_n, p.a_mn_major, p.b_mn_major);
-      // K-major: rows of 128 B, 8-row groups 1024 B apart; one MMA advances 32 B along K.
-      // MN-major: 32-element chunks, each [32 k-rows][128 B]; chunks kBlockK*128 B apart,
-      //           8-k-row groups 1024 B apart; one MMA advances one 8-row group.
+      // K-major: rows of 128 B swizzled in 16-byte units, 8-row groups 1024 B apart (SBO);
+      //          one MMA advances 32 B along K inside the row.
+      // MN-major: 32-element chunks, each [32 k-rows][128 B] swizzled in 32-byte units over
+      //          4 rows; chunks kChunkBytes apart (LBO), 4-k-row groups 512 B apart (SBO);
+      //          one MMA (K = 8) covers two groups and advances 1024 B.
       const uint32_t a_lbo = p.a_mn_major ? kChunkBytes : 16u;
       const uint32_t b_lbo = p.b_mn_major ? kChunkBytes : 16u;
+      const uint32_t a_sbo = p.a_mn_major ? 512u : 1024u;
+      const uint32_t b_sbo = p.b_mn_major ? 512u : 1024u;
+      const uint32_t a_lay = p.a_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+      const uint32_t b_lay = p.b_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
       const uint32_t a_kstep = p.a_mn_major ? 1024u : kUmmaK * 4u;
       const uint32_t b_kstep = p.b_mn_major ? 1024u : kUmmaK * 4u;
       int stage = 0;
@@ -239,8 +245,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t sb = sa + kStageABytes;
 #pragma unroll
           for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
-            const uint64_t da = ptx::smem_desc_sw128(sa + ks * a_kstep, a_lbo, 1024u);
-            const uint64_t db = ptx::smem_desc_sw128(sb + ks * b_kstep, b_lbo, 1024u);
+            const uint64_t da = ptx::smem_desc_sw128(sa + ks * a_kstep, a_lbo, a_sbo, a_lay);
+            const uint64_t db = ptx::smem_desc_sw128(sb + ks * b_kstep, b_lbo, b_sbo, b_lay);
             ptx::mma_tf32_1cta(tmem_d, da, db, idesc, (kb > kb0 || ks > 0) ? 1u : 0u);
           }
           ptx::mma_commit_1cta(empty_bar(stage));   // stage reusable once these MMAs retire
@@ -266,6 +272,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int m0 = w.mt * kBlockM + q * 32;
       const int n0 = w.nt * p.block_n;
       ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
+      ok = __all_sync(0xffffffffu, ok);              // keep the warp converged for tcgen05.ld
       if (!ok) break;
       ptx::tc_fence_after_sync();
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +

@@ -194,17 +194,23 @@ __device__ __forceinline__ void cluster_wait_acquire() {
 }
 
 // --------------------------------------------------- UMMA descriptor words ---
-// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field = 1.
+// Shared-memory matrix descriptor, 128-byte swizzle span, sm_100 version field = 1.
 //   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
-//   bits 32-45 stride byte offset >> 4 bits 46-47 version (1)   bits 61-63 layout (2 = SW128)
+//   bits 32-45 stride byte offset >> 4 bits 46-47 version (1)
+//   bits 61-63 layout: 2 = 128B swizzle of 16-byte units (8-row pattern),
+//                      1 = 128B swizzle of 32-byte units (4-row pattern) -- the only swizzled
+//                          layout the tensor core accepts for MN-major 32-bit operands.
+constexpr uint32_t kLayoutSw128 = 2;
+constexpr uint32_t kLayoutSw128Base32 = 1;
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes,
-                                                    uint32_t sbo_bytes) {
+                                                    uint32_t sbo_bytes,
+                                                    uint32_t layout = kLayoutSw128) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((saddr >> 4) & 0x3FFFu);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
+  d |= static_cast<uint64_t>(layout) << 61;
   return d;
 }
 // Instruction descriptor for kind::tf32, FP32 accumulate.

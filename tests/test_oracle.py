@@ -1,0 +1,134 @@
+"""CPU: the oracle against the golden vectors and against itself (no GPU, no product code)."""
+import numpy as np
+import pytest
+
+import oracle
+
+
+def test_splitmix64_known_answer(golden):
+    # Published SplitMix64 seed-0 outputs are E220A8397B1DCDAF, 6E789E6AA1B965F4, 06C45D188009454F;
+    # the reference's Rng pre-advances once, so its first two draws are the 2nd and 3rd.
+    assert golden["splitmix_seed0_reference_stream"][:2] == ["0x6e789e6aa1b965f4", "0x6c45d188009454f"]
+    u = oracle.rand_data(2, 0)
+    want = [np.float32(np.float32(z >> 40) / np.float32(1 << 24) * np.float32(2) - np.float32(1))
+            for z in (0x6E789E6AA1B965F4, 0x06C45D188009454F)]
+    assert u.tolist() == [float(w) for w in want]
+
+
+def test_rand_data_matches_golden(golden):
+    for c in golden["cases"]:
+        a = oracle.rand_data(c["a"].size, 1).reshape(c["a"].shape)
+        b = oracle.rand_data(c["b"].size, 2).reshape(c["b"].shape)
+        assert np.array_equal(a.view(np.uint32), c["a"].view(np.uint32)), c["name"]
+        assert np.array_equal(b.view(np.uint32), c["b"].view(np.uint32)), c["name"]
+        w = oracle.rand_data(c["c"].size, 0xBADC0DE ^ len(c["name"]))
+        assert np.array_equal(w.view(np.uint32), c["w"].view(np.uint32).ravel())
+
+
+def _fwd(op, a, b):
+    return {"nn": oracle.matmul, "nt": oracle.matmul_nt, "tn": oracle.matmul_tn}[op](a, b)
+
+
+def test_forward_bit_exact_against_golden(golden):
+    for c in golden["cases"]:
+        got = _fwd(c["op"], c["a"], c["b"])
+        assert got.shape == c["c"].shape
+        assert np.array_equal(got.view(np.uint32), c["c"].view(np.uint32)), c["name"]
+
+
+def test_backward_identities_bit_exact_against_golden(golden):
+    # GradFns of src/autograd/backward_ops.rs:82-134 expressed with the oracle's entry points.
+    for c in golden["cases"]:
+        a, b, w = c["a"], c["b"], c["w"]
+        if c["op"] == "nn":
+            ga, gb = oracle.matmul_nt(w, b), oracle.matmul_tn(a, w)
+        elif c["op"] == "nt":
+            ga, gb = oracle.matmul(w, b), oracle.matmul_tn(w, a)
+        else:
+            ga, gb = oracle.matmul_nt(b, w), oracle.matmul(a, w)
+        assert np.array_equal(ga.view(np.uint32), c["grad_a"].view(np.uint32)), c["name"]
+        assert np.array_equal(gb.view(np.uint32), c["grad_b"].view(np.uint32)), c["name"]
+
+
+def test_integer_known_answers():
+    a = np.array([[1, 2, 3], [4, 5, 6]], dtype=np.float32)
+    b = np.array([[7, 8], [9, 10], [11, 12]], dtype=np.float32)
+    assert oracle.matmul(a, b).tolist() == [[58, 64], [139, 154]]
+    assert oracle.matmul_nt(a, b.T.copy()).tolist() == [[58, 64], [139, 154]]
+    assert oracle.matmul_tn(a.T.copy(), b).tolist() == [[58, 64], [139, 154]]
+
+
+def test_summation_order_is_p_ascending_unfused():
+    # 2^24 + 1 - 2^24: ascending order loses the 1 (rounds to 2^24, then 0); FMA or another
+    # order would give a different bit pattern.
+    a = np.array([[2.0 ** 24, 1.0, -(2.0 ** 24)]], dtype=np.float32)
+    b = np.ones((3, 1), dtype=np.float32)
+    assert oracle.matmul(a, b)[0, 0] == 0.0
+    # unfused multiply: (1+2^-12)^2 rounds to 1+2^-11 before the add
+    x = np.float32(1 + 2.0 ** -12)
+    a = np.array([[x, -1.0]], dtype=np.float32)
+    b = np.array([[x], [np.float32(1 + 2.0 ** -11)]], dtype=np.float32)
+    assert oracle.matmul(a, b)[0, 0] == 0.0
+
+
+@pytest.mark.parametrize("shape", [(17, 9, 33), (64, 64, 64), (1, 7, 5), (130, 3, 1)])
+def test_against_float64(shape):
+    m, n, k = shape
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    for got in (oracle.matmul(a, b), oracle.matmul_nt(a, b.T.copy()), oracle.matmul_tn(a.T.copy(), b)):
+        assert np.abs(got - want).max() <= 1e-6 * k * np.abs(a).max() * np.abs(b).max()
+
+
+def test_layout_variants_bit_identical():
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((4, 37, 29), dtype=np.float32)
+    b = rng.standard_normal((4, 29, 31), dtype=np.float32)
+    c = oracle.matmul(a, b)
+    assert np.array_equal(c, oracle.matmul_nt(a, oracle.transpose(b)))
+    assert np.array_equal(c, oracle.matmul_tn(oracle.transpose(a), b))
+    # batch-1 broadcast of the CPU arm (src/tensor/ops.rs:401-411)
+    c1 = oracle.matmul(a[:1], b)
+    assert np.array_equal(c1[2], oracle.matmul(a[0], b[2]))
+
+
+def test_row_parallel_twin_is_bit_identical():
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((203, 77), dtype=np.float32)
+    b = rng.standard_normal((77, 65), dtype=np.float32)
+    c = oracle.matmul(a, b)
+    for t in (2, 3, 8):
+        assert np.array_equal(c, oracle.matmul(a, b, threads=t))
+    assert np.array_equal(c[50:120], oracle.matmul_rows(a, b, 50, 120, threads=4))
+
+
+def test_empty_and_degenerate_shapes():
+    z = np.zeros((0, 4), dtype=np.float32)
+    b = np.ones((4, 3), dtype=np.float32)
+    assert oracle.matmul(z, b).shape == (0, 3)
+    a = np.ones((2, 0), dtype=np.float32)
+    assert oracle.matmul(a, np.ones((0, 3), dtype=np.float32)).tolist() == [[0, 0, 0], [0, 0, 0]]
+
+
+def test_linear_bias_relu_gelu():
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((9, 6), dtype=np.float32)
+    w = rng.standard_normal((5, 6), dtype=np.float32)
+    bias = rng.standard_normal(5, dtype=np.float32)
+    y = oracle.linear(x, w, bias)
+    assert np.array_equal(y, oracle.matmul(x, oracle.transpose(w)) + bias[None, :])
+    assert np.array_equal(oracle.linear(x, w, bias, oracle.ACT_RELU), np.maximum(y, 0))
+    from math import erf, sqrt
+    g = oracle.linear(x, w, bias, oracle.ACT_GELU)
+    want = np.array([[0.5 * v * (1 + erf(v / sqrt(2))) for v in row] for row in y.astype(np.float64)])
+    assert np.abs(g - want).max() < 1e-6
+
+
+def test_causal_softmax_rows():
+    rng = np.random.default_rng(2)
+    s = rng.standard_normal((3, 8, 8), dtype=np.float32)
+    p = oracle.causal_softmax(s, 1.0 / np.sqrt(32.0))
+    assert np.allclose(p.sum(-1), 1.0, atol=1e-6)
+    assert np.all(np.triu(p, 1) == 0.0)
