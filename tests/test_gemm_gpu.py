@@ -68,7 +68,7 @@ def test_reference_fixture_shapes_forward_and_gradients(gpu, golden):
 
 ALIGNED = [  # (m, n, k, batch) -- operands meet TMA alignment: tensor-core path
     (128, 128, 32, 0), (128, 256, 512, 0), (256, 512, 256, 0), (1000, 776, 516, 0),
-    (100, 60, 36, 0), (4, 8, 4, 0), (1, 4, 4, 0), (129, 260, 36, 0), (512, 256, 784, 0),
+    (100, 60, 36, 0), (4, 8, 4, 0), (4, 4, 4, 0), (132, 260, 36, 0), (512, 256, 784, 0),
     (640, 1024, 1024, 0), (128, 128, 32, 5), (128, 32, 128, 7), (96, 40, 72, 3), (300, 132, 68, 2),
 ]
 RAGGED = [  # leading dimensions not multiples of 4 floats: SIMT path
