@@ -55,6 +55,10 @@ def workload_spec(name, rows_scale=1.0):
         m = int(8192 * rows_scale)
         return [g(NN, m, 8192, 8192, label="NN"), g(NT, m, 8192, 8192, label="NT"),
                 g(TN, m, 8192, 8192, label="TN")]
+    if name == "square4096":        # small case of the same kernels, sized for profiler captures
+        m = int(4096 * rows_scale)
+        return [g(NN, m, 4096, 4096, label="NN"), g(NT, m, 4096, 4096, label="NT"),
+                g(TN, m, 4096, 4096, label="TN")]
     if name == "linear_gelu":
         m = int(32768 * rows_scale)
         return [g(NN, m, 16384, 4096, bias=True, act=2, label="fwd NN+bias+GELU"),
