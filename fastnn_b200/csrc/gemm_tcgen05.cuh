@@ -120,6 +120,73 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, vola
   }
 }
 
+// Drains one accumulator tile (this warp's 32 TMEM lanes x block_n columns): scale, bias,
+// activation, then either a swizzled staging tile + TMA store or predicated global stores.
+// m0 is the first output row of this warp, n0 the first column of the tile, cz the outer
+// (batch or batch*split) coordinate, cb the batch index used for the beta read.
+__device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const CUtensorMap* tmC,
+                                                    uint32_t taddr0, uint32_t staging,
+                                                    uint8_t* staging_gen, int& buf, int m0, int n0,
+                                                    int cz, int cb, bool raw, int lane) {
+  const int row = m0 + lane;
+  for (int c = 0; c < p.block_n / 32; ++c) {
+    const int col0 = n0 + c * 32;
+    if (col0 >= p.n) break;                      // warp-uniform
+    uint32_t r[32];
+    ptx::tmem_ld_32x32(taddr0 + c * 32, r);
+    ptx::tmem_ld_wait();
+    if (m0 >= p.m) continue;                     // warp-uniform: rows all out of range
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (!raw) {
+      if (p.alpha != 1.0f) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+      }
+      if (p.beta != 0.0f && row < p.m) {         // only reachable in direct-store mode
+        const float* crow = p.c + cb * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.n) v[j] += p.beta * crow[col0 + j];
+      }
+      if (p.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
+      }
+      if (p.act != kActNone) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+      }
+    }
+    if (p.store_mode == 0) {
+      // staging tile: 32 rows x 128 B, 16-byte chunk j of row r at chunk (j ^ (r & 7))
+      if (lane == 0) ptx::tma_store_wait_read<1>();   // the tile used two stores ago is free
+      __syncwarp();
+      uint8_t* dst_row = staging_gen + buf * 4096 + lane * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 f = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        *reinterpret_cast<float4*>(dst_row + ((j ^ (lane & 7)) << 4)) = f;
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
+        ptx::tma_store_commit();
+      }
+      buf ^= 1;
+    } else if (row < p.m) {
+      float* crow = p.c + static_cast<long long>(cz) * p.c_batch_stride +
+                    static_cast<long long>(row) * p.ldc;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.n) crow[col0 + j] = v[j];
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
@@ -278,63 +345,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                               static_cast<uint32_t>(acc * kMaxBlockN);
       const int cz = raw ? (w.b * p.split_k + w.s) : w.b;   // outer coordinate of the store
-      const int row = m0 + lane;
-      for (int c = 0; c < p.block_n / 32; ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.n) break;                      // warp-uniform
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(taddr0 + c * 32, r);
-        ptx::tmem_ld_wait();
-        if (m0 >= p.m) continue;                     // warp-uniform: rows all out of range
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (!raw) {
-          if (p.alpha != 1.0f) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
-          }
-          if (p.beta != 0.0f && row < p.m) {         // only reachable in direct-store mode
-            const float* crow = p.c + w.b * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.n) v[j] += p.beta * crow[col0 + j];
-          }
-          if (p.bias != nullptr) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
-          }
-          if (p.act != kActNone) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
-          }
-        }
-        if (p.store_mode == 0) {
-          // staging tile: 32 rows x 128 B, 16-byte chunk j of row r at chunk (j ^ (r & 7))
-          if (lane == 0) ptx::tma_store_wait_read<1>();   // the tile used two stores ago is free
-          __syncwarp();
-          uint8_t* dst_row = staging_gen + buf * 4096 + lane * 128;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 f = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            *reinterpret_cast<float4*>(dst_row + ((j ^ (lane & 7)) << 4)) = f;
-          }
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            ptx::tma_store_3d(&tmC, staging + buf * 4096, col0, m0, cz);
-            ptx::tma_store_commit();
-          }
-          buf ^= 1;
-        } else if (row < p.m) {
-          float* crow = p.c + static_cast<long long>(cz) * p.c_batch_stride +
-                        static_cast<long long>(row) * p.ldc;
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.n) crow[col0 + j] = v[j];
-        }
-      }
+      epilogue_drain_tile(p, &tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, w.b, raw, lane);
       // accumulator drained: hand it back to the MMA warp
       ptx::tc_fence_before_sync();
       __syncwarp();

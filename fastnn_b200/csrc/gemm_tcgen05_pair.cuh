@@ -1,0 +1,227 @@
+// CTA-pair variant of the persistent TF32 GEMM: two CTAs on neighbouring SMs (a cluster of 2)
+// compute one 256 x block_n tile with tcgen05.mma cta_group::2.
+//
+// Each CTA loads its own 128 rows of A and HALF of the B tile (block_n / 2 columns) and keeps
+// its own 128 x block_n half of the accumulator in its own TMEM; the tensor cores of both SMs
+// read the two B halves from both shared memories.  Against two independent 128 x block_n
+// tiles this halves the shared-memory bytes read per MMA for B and cuts the L2 -> SM traffic
+// per output element by a third, which is what the MN-major (transposed) operand layouts need
+// to keep the tensor pipe fed.
+//
+// Roles per CTA as in the single-CTA kernel; differences:
+//   * both producers credit the LEADER CTA's (cluster rank 0) full barrier, which therefore
+//     expects two arrivals per stage;
+//   * only the leader issues MMAs; its commits arrive on the empty / accumulator-full barriers
+//     of both CTAs (one commit per destination, no multicast form);
+//   * the epilogue warps of both CTAs arrive on the leader's accumulator-empty barrier (8);
+//   * every producer ends by waiting for the last stage releases, and both CTAs meet at a
+//     cluster barrier before freeing TMEM, so no arrival targets a CTA that has exited.
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace fnn {
+
+constexpr int kPairBlockM = 2 * kBlockM;
+
+__device__ __forceinline__ Unit decode_unit_pair(const GemmParams& p, int u) {
+  // identical rasterisation, with tiles_m counting 256-row tiles (set by the host)
+  return decode_unit(p, u);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();          // 0 = leader
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+  const int half_n = p.block_n >> 1;                     // B columns this CTA loads
+
+  const uint32_t stage_b_bytes = static_cast<uint32_t>(half_n) * kBlockK * 4;
+  const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
+  const uint32_t staging_base = smem_base + p.num_stages * stage_bytes;
+  const uint32_t bar_base = staging_base + kStagingBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 64u + 8u * s; };
+  auto tfull_bar = [&](int a) { return bar_base + 128u + 8u * a; };
+  auto tempty_bar = [&](int a) { return bar_base + 144u + 8u * a; };
+  const uint32_t tmem_slot = bar_base + 160u;
+  uint8_t* bar_gen = smem_gen + (bar_base - smem_base);
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(bar_gen + 160);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 168);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.num_stages; ++s) {
+      ptx::mbar_init(full_bar(s), 2);          // one arrive.expect_tx from each CTA's producer
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 8);        // four epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+    ptx::prefetch_tensormap(&tmA);
+    ptx::prefetch_tensormap(&tmB);
+    if (p.store_mode == 0) ptx::prefetch_tensormap(&tmC);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_2cta(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish_2cta();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  // the peer's barriers must exist before anything arrives on them
+  ptx::cluster_arrive_release();
+  ptx::cluster_wait_acquire();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer ---
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = cluster_id; u < p.total_units && ok; u += num_clusters) {
+        const Unit w = decode_unit_pair(p, u);
+        const int m0 = w.mt * kPairBlockM + static_cast<int>(rank) * kBlockM;
+        const int n0 = w.nt * p.block_n + static_cast<int>(rank) * half_n;
+        const int kb0 = w.s * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = wait_barrier(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
+          if (!ok) break;
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint32_t sb = sa + kStageABytes;
+          const uint32_t fb = ptx::mapa_shared(full_bar(stage), 0);     // leader's barrier
+          ptx::mbar_expect_tx_cluster(fb, stage_bytes);
+          const int k0 = kb * kBlockK;
+          if (!p.a_mn_major) {
+            ptx::tma_load_3d_pair(sa, &tmA, fb, k0, m0, w.b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBlockM / 32; ++c)
+              ptx::tma_load_3d_pair(sa + c * kChunkBytes, &tmA, fb, m0 + 32 * c, k0, w.b);
+          }
+          if (!p.b_mn_major) {
+            ptx::tma_load_3d_pair(sb, &tmB, fb, k0, n0, w.b);         // box 32 x (block_n / 2)
+          } else {
+            for (int c = 0; c < half_n / 32; ++c)
+              ptx::tma_load_3d_pair(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b);
+          }
+          if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      // tail: every release the leader's commits still owe this CTA must land before exit
+      for (int i = 0; i < p.num_stages && ok; ++i) {
+        ok = wait_barrier(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
+        if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------- MMA issuer (leader only) ---
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = ptx::idesc_tf32(kPairBlockM, p.block_n, p.a_mn_major, p.b_mn_major);
+      const uint32_t a_lbo = p.a_mn_major ? kChunkBytes : 16u;
+      const uint32_t b_lbo = p.b_mn_major ? kChunkBytes : 16u;
+      const uint32_t a_sbo = p.a_mn_major ? 512u : 1024u;
+      const uint32_t b_sbo = p.b_mn_major ? 512u : 1024u;
+      const uint32_t a_lay = p.a_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+      const uint32_t b_lay = p.b_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+      const uint32_t a_kstep = p.a_mn_major ? 1024u : kUmmaK * 4u;
+      const uint32_t b_kstep = p.b_mn_major ? 1024u : kUmmaK * 4u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int u = cluster_id; u < p.total_units && ok; u += num_clusters) {
+        const Unit w = decode_unit_pair(p, u);
+        const int kb0 = w.s * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        ok = wait_barrier(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBlockN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = wait_barrier(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint32_t sb = sa + kStageABytes;
+#pragma unroll
+          for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
+            const uint64_t da = ptx::smem_desc_sw128(sa + ks * a_kstep, a_lbo, a_sbo, a_lay);
+            const uint64_t db = ptx::smem_desc_sw128(sb + ks * b_kstep, b_lbo, b_sbo, b_lay);
+            ptx::mma_tf32_2cta(tmem_d, da, db, idesc, (kb > kb0 || ks > 0) ? 1u : 0u);
+          }
+          ptx::mma_commit_2cta(ptx::mapa_shared(empty_bar(stage), 0));
+          ptx::mma_commit_2cta(ptx::mapa_shared(empty_bar(stage), 1));
+          if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::mma_commit_2cta(ptx::mapa_shared(tfull_bar(acc), 0));
+        ptx::mma_commit_2cta(ptx::mapa_shared(tfull_bar(acc), 1));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue ---
+    const int q = warp & 3;
+    const uint32_t staging = staging_base + (warp - kEpilogueWarp0) * kStagingBytesPerWarp;
+    uint8_t* staging_gen = smem_gen + (staging - smem_base);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int buf = 0;
+    bool ok = true;
+    const bool raw = p.split_k > 1;
+    for (int u = cluster_id; u < p.total_units && ok; u += num_clusters) {
+      const Unit w = decode_unit_pair(p, u);
+      const int m0 = w.mt * kPairBlockM + static_cast<int>(rank) * kBlockM + q * 32;
+      const int n0 = w.nt * p.block_n;
+      ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                              static_cast<uint32_t>(acc * kMaxBlockN);
+      const int cz = raw ? (w.b * p.split_k + w.s) : w.b;
+      epilogue_drain_tile(p, &tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, w.b, raw, lane);
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(acc), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (p.store_mode == 0 && lane == 0) ptx::tma_store_wait_all<0>();
+  }
+
+  // ---------------------------------------------------------------- teardown ---
+  __syncwarp();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) { }
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::cluster_arrive_release();
+  ptx::cluster_wait_acquire();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc_2cta(tmem_base, kTmemCols);
+  }
+}
+
+// Dynamic shared memory per CTA of the pair kernel.
+inline size_t gemm_pair_smem_bytes(int block_n, int num_stages) {
+  return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + (block_n / 2) * kBlockK * 4) +
+         kStagingBytes + kBarrierBytes;
+}
+
+}  // namespace fnn
