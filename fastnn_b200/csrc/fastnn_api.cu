@@ -502,3 +502,153 @@ extern "C" unsigned long long fastnn_b200_launch_count(void) {
 }
 
 extern "C" const char* fastnn_b200_version(void) { return "fastnn_b200 0.1 (sm_100a)"; }
+
+// ======================================================== allocation-free entry ===
+//
+// Split-K GEMM whose partial sums live in a fixed array inside the library image instead of
+// a cudaMalloc'ed workspace.  See the declaration in the header for who needs this and why.
+
+namespace {
+
+constexpr size_t kStaticScratchFloats = 4u * 1024u * 1024u;     // 16 MiB per device
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+static __device__ unsigned int g_static_status;
+
+struct StaticState {
+  bool ready = false;
+  float* scratch = nullptr;        // device address of g_static_scratch on this device
+  unsigned int* status = nullptr;  // device address of g_static_status on this device
+  int num_sms = 0;
+  long long spin_budget = 0;
+};
+StaticState g_static[kMaxDevices];
+
+// Once per device, with that device current.  Resolves device addresses of the two symbols
+// (their host-side names are not device pointers) and the driver's tensor-map encoder.
+// Nothing here allocates device memory.
+int static_setup(int dev, StaticState** out) {
+  StaticState& st = g_static[dev];
+  if (!st.ready) {
+    int major = 0, sms = 0, khz = 0;
+    FNN_CUDA_OK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) {
+      std::fprintf(stderr, "fastnn_b200: device %d is not sm_100; no kernel image for it\n", dev);
+      return -1;
+    }
+    FNN_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev) != cudaSuccess || khz <= 0) {
+      (void)cudaGetLastError();
+      khz = 2000000;
+    }
+    void* p = nullptr;
+    FNN_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
+    st.scratch = static_cast<float*>(p);
+    p = nullptr;
+    FNN_CUDA_OK(cudaGetSymbolAddress(&p, g_static_status));
+    st.status = static_cast<unsigned int*>(p);
+    if (st.scratch == nullptr || st.status == nullptr) return -1;
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      FNN_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return -1;
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kMaxDynSmem)));
+    st.num_sms = sms;
+    st.spin_budget = 2000ll * khz;
+    st.ready = true;
+  }
+  *out = &st;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int fastnn_b200_gemm_splitk_static(int layout, const float* a, const float* b, float* c,
+                                              int m, int n, int k, int split_k, void* stream) {
+  if (layout < 0 || layout > 2 || m < 0 || n < 0 || k < 1 || split_k < 1) return -1;
+  if (m == 0 || n == 0) return 0;
+  if (a == nullptr || b == nullptr || c == nullptr) return -1;
+  const long long lda = (layout == FASTNN_B200_TN) ? m : k;
+  const long long ldb = (layout == FASTNN_B200_NT) ? k : n;
+  // TMA addressing rules for the operands and the float4 reduce pass over C
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c) || (lda & 3) || (ldb & 3) || (n & 3)) {
+    std::fprintf(stderr, "fastnn_b200_gemm_splitk_static: operands must be 16-byte aligned with "
+                         "row lengths that are multiples of 4 floats\n");
+    return -1;
+  }
+  const int num_kb = ceil_div(k, fnn::kBlockK);
+  if (split_k > num_kb) split_k = num_kb;
+  const int kbps = ceil_div(num_kb, split_k);
+  split_k = ceil_div(num_kb, kbps);
+  const unsigned long long need = 1ull * m * n * split_k;
+  if (need > kStaticScratchFloats) {
+    std::fprintf(stderr, "fastnn_b200_gemm_splitk_static: m*n*split_k = %llu floats exceeds the "
+                         "built-in scratch of %zu floats (16 MiB); use fewer splits or the "
+                         "allocating entry points\n", need, kStaticScratchFloats);
+    return -2;
+  }
+  int dev = -1;
+  FNN_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return -1;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  StaticState* st = nullptr;
+  if (static_setup(dev, &st) != 0) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  const int block_n = n >= 128 ? 128 : ceil_div(n, 32) * 32;
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.m = m; p.n = n; p.k = k; p.batch = 1;
+  p.block_n = block_n;
+  p.num_stages = stages_for(block_n);
+  p.tiles_m = ceil_div(m, fnn::kBlockM);
+  p.tiles_n = ceil_div(n, block_n);
+  p.num_kb = num_kb;
+  p.split_k = split_k + 0;
+  p.kb_per_split = kbps;
+  const long long units = 1ll * p.tiles_m * p.tiles_n * split_k;
+  if (units > 0x7fffffffll) return -1;
+  p.total_units = static_cast<int>(units);
+  p.a_mn_major = (layout == FASTNN_B200_TN) ? 1 : 0;
+  p.b_mn_major = (layout == FASTNN_B200_NT) ? 0 : 1;
+  p.alpha = 1.0f; p.beta = 0.0f; p.bias = nullptr; p.act = 0;
+  p.status = st->status;
+  p.spin_budget = st->spin_budget;
+  p.store_mode = 0;
+  p.c = st->scratch; p.ldc = n; p.c_batch_stride = 1ll * m * n;
+  // With alpha = 1, beta = 0 and no bias the kernel's epilogue is the identity, so a single
+  // split also lands in the scratch unchanged and the reduce pass copies it to C.
+
+  CUtensorMap tmA, tmB, tmC;
+  bool ok;
+  if (!p.a_mn_major)
+    ok = encode_map(&tmA, a, k, m, 1, lda * 4ull, lda * 4ull * m, fnn::kBlockK, fnn::kBlockM);
+  else
+    ok = encode_map(&tmA, a, m, k, 1, lda * 4ull, lda * 4ull * k, 32, fnn::kBlockK, true);
+  if (!p.b_mn_major)
+    ok = ok && encode_map(&tmB, b, k, n, 1, ldb * 4ull, ldb * 4ull * n, fnn::kBlockK, block_n);
+  else
+    ok = ok && encode_map(&tmB, b, n, k, 1, ldb * 4ull, ldb * 4ull * k, 32, fnn::kBlockK, true);
+  ok = ok && encode_map(&tmC, st->scratch, n, m, static_cast<uint64_t>(split_k), n * 4ull,
+                        4ull * m * n, 32, 32);
+  if (!ok) return -1;
+  const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
+  fnn::gemm_tf32_kernel<<<grid, fnn::kNumThreads, fnn::gemm_smem_bytes(block_n, p.num_stages), s>>>(
+      tmA, tmB, tmC, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  FNN_CUDA_OK(cudaGetLastError());
+  long long blocks = (1ll * m * n / 4 + 255) / 256;
+  if (blocks > 8ll * st->num_sms) blocks = 8ll * st->num_sms;
+  if (blocks < 1) blocks = 1;
+  fnn::splitk_reduce_vec4_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+      reinterpret_cast<const float4*>(st->scratch), c, nullptr, m, n, 1, split_k, n,
+      1ll * m * n, 1.0f, 0.0f, 0);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  FNN_CUDA_OK(cudaGetLastError());
+  t_last = LastCall{2, block_n, split_k, grid};
+  return 0;
+}

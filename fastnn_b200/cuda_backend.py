@@ -211,6 +211,19 @@ def gemm_ex(layout, a_ptr, b_ptr, c_ptr, m, n, k, batch, lda, ldb, ldc, sa, sb, 
         raise CudaError("fastnn_b200_gemm_ex failed")
 
 
+def gemm_splitk_static(layout, a, b, m, n, k, split_k, out=None, stream=0):
+    """C = op(A).op(B) through the entry point that allocates nothing: split-K partial sums go
+    to the 16 MiB array built into the library.  Returns the output tensor; raises CudaError
+    with ``too_large=True`` in its args when m*n*split_k floats exceed that array."""
+    _check(a, "a"); _check(b, "b")
+    c = _out((m, n), a, out)
+    rc = lib().fastnn_b200_gemm_splitk_static(layout, _ptr(a), _ptr(b), _ptr(c), m, n, k, split_k,
+                                              ctypes.c_void_p(stream))
+    if rc != 0:
+        raise CudaError("fastnn_b200_gemm_splitk_static failed", rc == -2)
+    return c
+
+
 def set_policy(policy: int = 0, block_n: int = 0, split_k: int = 0) -> None:
     if lib().fastnn_b200_set_policy(policy, block_n, split_k) != 0:
         raise ValueError("bad policy")

@@ -107,6 +107,39 @@ FASTNN_B200_API int fastnn_b200_gemm_ex(int layout, const float* a, const float*
 FASTNN_B200_API int fastnn_b200_linear_forward(int layout, const float* x, const float* w, const float* bias,
                                float* y, int rows, int in_features, int out_features, int act);
 
+/* Split-K GEMM that allocates nothing.  It has no counterpart in FastNN.
+ *
+ *   C[m,n] = op(A) . op(B)      dense operands, layout as above, alpha = 1, beta = 0
+ *
+ * Who it is for: callers that are not allowed to call cudaMalloc / cudaFree at the moment
+ * they need a GEMM -- code running while another thread has a stream capture open (an
+ * allocation would invalidate the capture or block), real-time loops that may not take the
+ * allocator's device-wide synchronisation, and hosts whose memory budget is fixed up front and
+ * audited, where a library that grows a hidden workspace is not acceptable.  The other entry
+ * points keep their split-K partial sums in a workspace obtained from cudaMalloc on first
+ * use; this one keeps them in a 16 MiB array that is part of the library image (every GPU
+ * that loads the library holds those 16 MiB until the process exits).
+ *
+ * The K range is cut into split_k parts (clamped so each part has at least one 32-deep
+ * block); each part's partial tile goes to the built-in array and a second kernel adds the
+ * parts in ascending order into C.
+ * Limits and rules:
+ *   - m * n * split_k floats must fit the array (4 Mi floats); otherwise nothing is launched,
+ *     a message goes to stderr and the call returns -2.
+ *   - a, b, c 16-byte aligned; row lengths (k or m for A, k or n for B, n for C) multiples
+ *     of 4 floats.  Other failures return -1.
+ *   - It does not need fastnn_cuda_init.  The first call on each device looks up the device
+ *     address of the array and of the tensor-map encoder; make that first call before any
+ *     stream capture begins.
+ *   - All calls on one device share the array and it keeps the previous call's contents.
+ *     Every element that is read was written earlier in the same call, so nothing has to be
+ *     cleared, but two calls that overlap on the GPU (different streams without an ordering
+ *     between them) race on it.  Calls on one stream are safe back to back.
+ *   - No cudaMalloc, cudaFree or other allocating routine is called, on any call. */
+FASTNN_B200_API int fastnn_b200_gemm_splitk_static(int layout, const float* a, const float* b,
+                                                   float* c, int m, int n, int k, int split_k,
+                                                   void* stream);
+
 /* Kernel selection for tests and sweeps.  policy: 0 = automatic (tcgen05 path whenever the
  * operands meet TMA's 16-byte alignment rules, SIMT path otherwise), 1 = SIMT path only,
  * 2 = tcgen05 path only (calls that cannot use it fail with -1).
