@@ -16,6 +16,7 @@
 #include "../../include/fastnn_b200_kernels.h"
 #include "gemm_simt.cuh"
 #include "gemm_tcgen05.cuh"
+#include "gemm_tcgen05_pair.cuh"
 
 namespace {
 
@@ -37,6 +38,7 @@ struct Workspace {
 struct DeviceState {
   bool ready = false;
   int num_sms = 0;
+  int max_clusters = 0;             // co-resident CTA pairs of the pair kernel
   unsigned int* status = nullptr;   // device word written by a kernel whose wait ran out
   long long spin_budget = 0;        // clock ticks one wait may last
   std::map<cudaStream_t, Workspace> workspaces;   // split-K partials, one per stream
@@ -98,48 +100,64 @@ bool encode_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, ui
 
 struct Plan {
   int block_n, split_k, stages;
+  bool pair;                        // 256 x block_n tiles on CTA pairs (cta_group::2)
 };
 
-// Cycle model used to pick the tile width and the K split.  Per 32-deep k-block a CTA is
-// bound either by the tensor pipe (block_n / 2 cycles at 4096 dense TF32 flop/clk/SM) or by
-// reading A (4 KiB) and B (block_n * 32 B) from shared memory at 128 B/clk.
-Plan choose_plan(int m, int n, int k, int batch, int num_sms) {
-  const int tiles_m = ceil_div(m, fnn::kBlockM);
+// Cycle model used to pick the tile shape and the K split.  Per 32-deep k-block (four MMAs) a
+// CTA is bound either by the tensor pipe (block_n / 2 cycles at 4096 dense TF32 flop/clk/SM) or by
+// reading its A and B stage from shared memory at 128 B/clk; an MN-major (32-byte swizzled)
+// operand is charged twice its bytes, which is what the measured NT/NN/TN ratios show.  A CTA
+// pair computes 256 x block_n with each CTA reading only half of B.
+Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, bool a_mn,
+                 bool b_mn, int pair_mode /* 0 auto, 1 never, 2 always */) {
   const int num_kb = ceil_div(k, fnn::kBlockK);
   const int n32 = ceil_div(n, 32) * 32;
   const double out_bytes = 4.0 * m * n * batch;
   const double hbm_per_clk = 3000.0;
   const double floor_cycles = (4.0 * batch * (1.0 * m * k + 1.0 * k * n) + out_bytes) / hbm_per_clk;
-  Plan best{32, 1, 4};
+  Plan best{32, 1, 4, false};
   double best_cost = 1e300;
   static const int splits[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
-  for (int bn = 32; bn <= fnn::kMaxBlockN; bn += 32) {
-    if (bn > n32) break;
-    const int tiles_n = ceil_div(n, bn);
-    const double t_kb = bn / 2.0 > 32.0 + bn / 4.0 ? bn / 2.0 : 32.0 + bn / 4.0;
-    for (int s : splits) {
-      if (s > 1 && num_kb / s < 4) break;
-      const int kbps = ceil_div(num_kb, s);
-      const int real_split = ceil_div(num_kb, kbps);
-      const long long units = 1ll * batch * tiles_m * tiles_n * real_split;
-      const double waves = static_cast<double>((units + num_sms - 1) / num_sms);
-      double cycles = waves * (kbps * t_kb + 1200.0);
-      if (real_split > 1) cycles += (2.0 * real_split + 1.0) * out_bytes / hbm_per_clk + 6000.0;
-      if (cycles < floor_cycles) cycles = floor_cycles;
-      // prefer wider tiles and fewer splits on ties
-      cycles *= 1.0 + 1e-4 * (8 - bn / 32) + 1e-3 * (real_split - 1);
-      if (cycles < best_cost) {
-        best_cost = cycles;
-        best.block_n = bn;
-        best.split_k = real_split;
+  for (int pair = 0; pair < 2; ++pair) {
+    if (pair == 1 && (pair_mode == 1 || max_clusters < 1)) continue;
+    if (pair == 0 && pair_mode == 2) continue;
+    if (pair == 1 && pair_mode == 0 && m <= fnn::kBlockM) continue;
+    const int tile_m = pair ? 2 * fnn::kBlockM : fnn::kBlockM;
+    const int tiles_m = ceil_div(m, tile_m);
+    const int slots = pair ? max_clusters : num_sms;
+    for (int bn = pair ? 64 : 32; bn <= fnn::kMaxBlockN; bn += pair ? 64 : 32) {
+      if (bn > n32 && bn > (pair ? 64 : 32)) break;
+      const int tiles_n = ceil_div(n, bn);
+      const double a_bytes = 4096.0 * (a_mn ? 2.0 : 1.0);
+      const double b_bytes = (pair ? 16.0 : 32.0) * bn * (b_mn ? 2.0 : 1.0);
+      const double t_smem = (a_bytes + b_bytes) / 128.0;
+      const double t_kb = bn / 2.0 > t_smem ? bn / 2.0 : t_smem;
+      for (int s : splits) {
+        if (s > 1 && num_kb / s < 4) break;
+        const int kbps = ceil_div(num_kb, s);
+        const int real_split = ceil_div(num_kb, kbps);
+        const long long units = 1ll * batch * tiles_m * tiles_n * real_split;
+        const double waves = static_cast<double>((units + slots - 1) / slots);
+        double cycles = waves * (kbps * t_kb + 1200.0);
+        if (real_split > 1) cycles += (2.0 * real_split + 1.0) * out_bytes / hbm_per_clk + 6000.0;
+        if (cycles < floor_cycles) cycles = floor_cycles;
+        // prefer wider tiles, fewer splits and single CTAs on ties
+        cycles *= 1.0 + 1e-4 * (8 - bn / 32) + 1e-3 * (real_split - 1) + 1e-4 * pair;
+        if (cycles < best_cost) {
+          best_cost = cycles;
+          best.block_n = bn;
+          best.split_k = real_split;
+          best.pair = pair != 0;
+        }
       }
     }
   }
   return best;
 }
 
-int stages_for(int block_n) {
-  const size_t stage = fnn::kStageABytes + static_cast<size_t>(block_n) * fnn::kBlockK * 4;
+int stages_for(int block_n, bool pair = false) {
+  const size_t stage = fnn::kStageABytes +
+                       static_cast<size_t>(pair ? block_n / 2 : block_n) * fnn::kBlockK * 4;
   const size_t avail = kMaxDynSmem - 1024 - fnn::kStagingBytes - fnn::kBarrierBytes;
   int s = static_cast<int>(avail / stage);
   if (s > fnn::kMaxStages) s = fnn::kMaxStages;
@@ -192,21 +210,29 @@ int launch_simt(const GemmArgs& g) {
 }
 
 int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
-  Plan plan = choose_plan(g.m, g.n, g.k, g.batch, st->num_sms);
+  const bool a_mn = (g.layout == FASTNN_B200_TN), b_mn = (g.layout != FASTNN_B200_NT);
+  const int pair_mode = pol.policy == 3 ? 1 : (pol.policy == 4 ? 2 : 0);
+  Plan plan = choose_plan(g.m, g.n, g.k, g.batch, st->num_sms, st->max_clusters, a_mn, b_mn,
+                          pair_mode);
   if (pol.block_n > 0) plan.block_n = pol.block_n;
   if (pol.split_k > 0) plan.split_k = pol.split_k;
+  if (plan.pair && (plan.block_n % 64) != 0) plan.block_n = ceil_div(plan.block_n, 64) * 64;
   const int num_kb = ceil_div(g.k, fnn::kBlockK);
   if (plan.split_k > num_kb) plan.split_k = num_kb;
   const int kbps = ceil_div(num_kb, plan.split_k);
   plan.split_k = ceil_div(num_kb, kbps);
-  plan.stages = stages_for(plan.block_n);
+  plan.stages = stages_for(plan.block_n, plan.pair);
+  if (const char* e = std::getenv("FASTNN_B200_STAGES")) {
+    const int s = std::atoi(e);
+    if (s >= 1 && s < plan.stages) plan.stages = s;
+  }
 
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
   p.m = g.m; p.n = g.n; p.k = g.k; p.batch = g.batch;
   p.block_n = plan.block_n;
   p.num_stages = plan.stages;
-  p.tiles_m = ceil_div(g.m, fnn::kBlockM);
+  p.tiles_m = ceil_div(g.m, plan.pair ? fnn::kPairBlockM : fnn::kBlockM);
   p.tiles_n = ceil_div(g.n, plan.block_n);
   p.num_kb = num_kb;
   p.split_k = plan.split_k;
@@ -219,6 +245,9 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   p.alpha = g.alpha; p.beta = g.beta; p.bias = g.bias; p.act = g.act;
   p.status = st->status;
   p.spin_budget = st->spin_budget;
+  if (const char* e = std::getenv("FASTNN_B200_DEBUG_FLAGS")) p.debug_flags = std::atoi(e);
+  if (const char* e = std::getenv("FASTNN_B200_DEBUG_PTR"))
+    p.debug_buf = reinterpret_cast<unsigned long long*>(std::strtoull(e, nullptr, 0));
 
   // output target: C itself, or the split-K workspace
   float* out = g.c;
@@ -255,7 +284,8 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   else
     ok = encode_map(&tmA, g.a, g.m, g.k, B, g.lda * 4ull, sa_bytes, 32, fnn::kBlockK, true);
   if (!p.b_mn_major)
-    ok = ok && encode_map(&tmB, g.b, g.k, g.n, B, g.ldb * 4ull, sb_bytes, fnn::kBlockK, plan.block_n);
+    ok = ok && encode_map(&tmB, g.b, g.k, g.n, B, g.ldb * 4ull, sb_bytes, fnn::kBlockK,
+                          plan.pair ? plan.block_n / 2 : plan.block_n);
   else
     ok = ok && encode_map(&tmB, g.b, g.n, g.k, B, g.ldb * 4ull, sb_bytes, 32, fnn::kBlockK, true);
   if (tma_store) {
@@ -267,9 +297,17 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   }
   if (!ok) return -1;
 
-  const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
-  const size_t smem = fnn::gemm_smem_bytes(plan.block_n, plan.stages);
-  fnn::gemm_tf32_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, p);
+  int grid;
+  if (plan.pair) {
+    const int clusters = p.total_units < st->max_clusters ? p.total_units : st->max_clusters;
+    grid = 2 * clusters;
+    const size_t smem = fnn::gemm_pair_smem_bytes(plan.block_n, plan.stages);
+    fnn::gemm_tf32_pair_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, p);
+  } else {
+    grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
+    const size_t smem = fnn::gemm_smem_bytes(plan.block_n, plan.stages);
+    fnn::gemm_tf32_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, p);
+  }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   FNN_CUDA_OK(cudaGetLastError());
 
@@ -292,7 +330,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
     FNN_CUDA_OK(cudaGetLastError());
   }
-  t_last = LastCall{2, plan.block_n, plan.split_k, grid};
+  t_last = LastCall{plan.pair ? 3 : 2, plan.block_n, plan.split_k, grid};
   return 0;
 }
 
@@ -312,7 +350,7 @@ int gemm_dispatch(const GemmArgs& g) {
   if (st == nullptr) return -1;                                   // fastnn_cuda_init not called
   const Policy pol = g_policy;
   const bool can_tma = tma_operands_ok(g);
-  if (pol.policy == 2 && !can_tma) return -1;
+  if (pol.policy >= 2 && !can_tma) return -1;
   if (pol.policy == 1 || !can_tma) return launch_simt(g);
   return launch_tcgen05(st, g, pol);
 }
@@ -345,6 +383,28 @@ extern "C" int fastnn_cuda_init(int device_id) {
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
   st.num_sms = prop.multiProcessorCount;
+  FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_pair_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kMaxDynSmem)));
+  {
+    // how many CTA pairs of the pair kernel can be resident at once (normally one per TPC)
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * prop.multiProcessorCount, 1, 1);
+    cfg.blockDim = dim3(fnn::kNumThreads, 1, 1);
+    cfg.dynamicSmemBytes = fnn::gemm_pair_smem_bytes(fnn::kMaxBlockN, stages_for(fnn::kMaxBlockN, true));
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, fnn::gemm_tf32_pair_kernel, &cfg) != cudaSuccess) {
+      (void)cudaGetLastError();
+      clusters = 0;
+    }
+    st.max_clusters = clusters;
+  }
   FNN_CUDA_OK(cudaMalloc(&st.status, sizeof(unsigned int)));
   FNN_CUDA_OK(cudaMemset(st.status, 0, sizeof(unsigned int)));
   // about two seconds at the maximum SM clock (clockRate is in kHz)
@@ -468,7 +528,7 @@ extern "C" int fastnn_b200_linear_forward(int layout, const float* x, const floa
 }
 
 extern "C" int fastnn_b200_set_policy(int policy, int block_n, int split_k) {
-  if (policy < 0 || policy > 2) return -1;
+  if (policy < 0 || policy > 4) return -1;
   if (block_n < 0 || block_n > fnn::kMaxBlockN || (block_n % 32) != 0) return -1;
   if (split_k < 0) return -1;
   std::lock_guard<std::mutex> lock(g_mutex);

@@ -70,6 +70,8 @@ struct GemmParams {
   long long ldc, c_batch_stride;   // elements
   unsigned int* status;
   long long spin_budget;           // clock64 ticks a single wait may last
+  int debug_flags;                 // experiment switches (0 in production)
+  unsigned long long* debug_buf;   // timestamp trace (null in production)
 };
 
 struct Unit {
@@ -103,11 +105,13 @@ __device__ __forceinline__ float apply_act(float x, int act) {
 // another role's did).
 __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                              const GemmParams& p, unsigned int code) {
-  if (ptx::mbar_try_wait(bar, parity)) return true;
+  if ((p.debug_flags & 2) ? ptx::mbar_test_wait(bar, parity) : ptx::mbar_try_wait(bar, parity))
+    return true;
   const long long t0 = clock64();
   int it = 0;
   while (true) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if ((p.debug_flags & 2) ? ptx::mbar_test_wait(bar, parity) : ptx::mbar_try_wait(bar, parity))
+      return true;
     if ((++it & 63) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > p.spin_budget) {
@@ -276,6 +280,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------- MMA issuer ---
+    // One lane issues.  Descriptors are a per-stage constant plus the stage's address (>> 4),
+    // so the loop body is two 64-bit adds per MMA.
     if (lane == 0) {
       const uint32_t idesc = ptx::idesc_tf32(kBlockM, p.block_n, p.a_mn_major, p.b_mn_major);
       // K-major: rows of 128 B swizzled in 16-byte units, 8-row groups 1024 B apart (SBO);
@@ -283,14 +289,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // MN-major: 32-element chunks, each [32 k-rows][128 B] swizzled in 32-byte units over
       //          4 rows; chunks kChunkBytes apart (LBO), 4-k-row groups 512 B apart (SBO);
       //          one MMA (K = 8) covers two groups and advances 1024 B.
-      const uint32_t a_lbo = p.a_mn_major ? kChunkBytes : 16u;
-      const uint32_t b_lbo = p.b_mn_major ? kChunkBytes : 16u;
-      const uint32_t a_sbo = p.a_mn_major ? 512u : 1024u;
-      const uint32_t b_sbo = p.b_mn_major ? 512u : 1024u;
-      const uint32_t a_lay = p.a_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
-      const uint32_t b_lay = p.b_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
-      const uint32_t a_kstep = p.a_mn_major ? 1024u : kUmmaK * 4u;
-      const uint32_t b_kstep = p.b_mn_major ? 1024u : kUmmaK * 4u;
+      const uint64_t a_desc0 = ptx::smem_desc_sw128(
+          smem_base, p.a_mn_major ? kChunkBytes : 16u, p.a_mn_major ? 512u : 1024u,
+          p.a_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128);
+      const uint64_t b_desc0 = ptx::smem_desc_sw128(
+          smem_base + kStageABytes, p.b_mn_major ? kChunkBytes : 16u, p.b_mn_major ? 512u : 1024u,
+          p.b_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128);
+      const uint64_t a_kstep = (p.a_mn_major ? 1024u : kUmmaK * 4u) >> 4;   // in 16-byte units
+      const uint64_t b_kstep = (p.b_mn_major ? 1024u : kUmmaK * 4u) >> 4;
+      const uint64_t stage_step = stage_bytes >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -302,20 +309,17 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         ok = wait_barrier(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout);
         if (!ok) break;
-        ptx::tc_fence_after_sync();
+        ptx::tc_fence_after_sync();                  // orders the epilogue's TMEM reads before us
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBlockN);
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = wait_barrier(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout);
           if (!ok) break;
-          ptx::tc_fence_after_sync();
-          const uint32_t sa = smem_base + stage * stage_bytes;
-          const uint32_t sb = sa + kStageABytes;
+          const uint64_t da = a_desc0 + stage * stage_step;
+          const uint64_t db = b_desc0 + stage * stage_step;
 #pragma unroll
-          for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
-            const uint64_t da = ptx::smem_desc_sw128(sa + ks * a_kstep, a_lbo, a_sbo, a_lay);
-            const uint64_t db = ptx::smem_desc_sw128(sb + ks * b_kstep, b_lbo, b_sbo, b_lay);
-            ptx::mma_tf32_1cta(tmem_d, da, db, idesc, (kb > kb0 || ks > 0) ? 1u : 0u);
-          }
+          for (int ks = 0; ks < kBlockK / kUmmaK; ++ks)
+            ptx::mma_tf32_1cta(tmem_d, da + ks * a_kstep, db + ks * b_kstep, idesc,
+                               (kb > kb0 || ks > 0) ? 1u : 0u);
           ptx::mma_commit_1cta(empty_bar(stage));   // stage reusable once these MMAs retire
           if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
         }

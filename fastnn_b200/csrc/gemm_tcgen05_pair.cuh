@@ -129,14 +129,18 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     // ------------------------------------------------- MMA issuer (leader only) ---
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = ptx::idesc_tf32(kPairBlockM, p.block_n, p.a_mn_major, p.b_mn_major);
-      const uint32_t a_lbo = p.a_mn_major ? kChunkBytes : 16u;
-      const uint32_t b_lbo = p.b_mn_major ? kChunkBytes : 16u;
-      const uint32_t a_sbo = p.a_mn_major ? 512u : 1024u;
-      const uint32_t b_sbo = p.b_mn_major ? 512u : 1024u;
-      const uint32_t a_lay = p.a_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
-      const uint32_t b_lay = p.b_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
-      const uint32_t a_kstep = p.a_mn_major ? 1024u : kUmmaK * 4u;
-      const uint32_t b_kstep = p.b_mn_major ? 1024u : kUmmaK * 4u;
+      const uint64_t a_desc0 = ptx::smem_desc_sw128(
+          smem_base, p.a_mn_major ? kChunkBytes : 16u, p.a_mn_major ? 512u : 1024u,
+          p.a_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128);
+      const uint64_t b_desc0 = ptx::smem_desc_sw128(
+          smem_base + kStageABytes, p.b_mn_major ? kChunkBytes : 16u, p.b_mn_major ? 512u : 1024u,
+          p.b_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128);
+      const uint64_t a_kstep = (p.a_mn_major ? 1024u : kUmmaK * 4u) >> 4;
+      const uint64_t b_kstep = (p.b_mn_major ? 1024u : kUmmaK * 4u) >> 4;
+      const uint64_t stage_step = stage_bytes >> 4;
+      // the two CTAs' copies of a barrier differ by a constant in the cluster address space
+      const uint32_t bar0 = ptx::mapa_shared(bar_base, 0);
+      const uint32_t bar1 = ptx::mapa_shared(bar_base, 1);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -153,22 +157,23 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = wait_barrier(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout);
           if (!ok) break;
-          ptx::tc_fence_after_sync();
-          const uint32_t sa = smem_base + stage * stage_bytes;
-          const uint32_t sb = sa + kStageABytes;
+          const uint64_t da = a_desc0 + stage * stage_step;
+          const uint64_t db = b_desc0 + stage * stage_step;
 #pragma unroll
-          for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
-            const uint64_t da = ptx::smem_desc_sw128(sa + ks * a_kstep, a_lbo, a_sbo, a_lay);
-            const uint64_t db = ptx::smem_desc_sw128(sb + ks * b_kstep, b_lbo, b_sbo, b_lay);
-            ptx::mma_tf32_2cta(tmem_d, da, db, idesc, (kb > kb0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < kBlockK / kUmmaK; ++ks)
+            ptx::mma_tf32_2cta(tmem_d, da + ks * a_kstep, db + ks * b_kstep, idesc,
+                               (kb > kb0 || ks > 0) ? 1u : 0u);
+          if (p.debug_flags & 1) {
+            ptx::mma_commit_2cta_mask(empty_bar(stage), 3);
+          } else {
+            ptx::mma_commit_2cta(bar0 + 64u + 8u * stage);    // empty[stage], leader
+            ptx::mma_commit_2cta(bar1 + 64u + 8u * stage);    // empty[stage], peer
           }
-          ptx::mma_commit_2cta(ptx::mapa_shared(empty_bar(stage), 0));
-          ptx::mma_commit_2cta(ptx::mapa_shared(empty_bar(stage), 1));
           if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        ptx::mma_commit_2cta(ptx::mapa_shared(tfull_bar(acc), 0));
-        ptx::mma_commit_2cta(ptx::mapa_shared(tfull_bar(acc), 1));
+        ptx::mma_commit_2cta(bar0 + 128u + 8u * acc);       // accumulator full, leader
+        ptx::mma_commit_2cta(bar1 + 128u + 8u * acc);       // accumulator full, peer
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }

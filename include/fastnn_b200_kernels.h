@@ -142,8 +142,10 @@ FASTNN_B200_API int fastnn_b200_gemm_splitk_static(int layout, const float* a, c
 
 /* Kernel selection for tests and sweeps.  policy: 0 = automatic (tcgen05 path whenever the
  * operands meet TMA's 16-byte alignment rules, SIMT path otherwise), 1 = SIMT path only,
- * 2 = tcgen05 path only (calls that cannot use it fail with -1).
- * block_n in {0 (auto), 32, 64, 96, ..., 256}; split_k >= 0 (0 = auto). */
+ * 2 = tcgen05 path only (calls that cannot use it fail with -1), 3 = tcgen05 with single-CTA
+ * 128-row tiles only, 4 = tcgen05 with CTA-pair 256-row tiles only.
+ * block_n in {0 (auto), 32, 64, 96, ..., 256} (rounded up to a multiple of 64 for CTA
+ * pairs); split_k >= 0 (0 = auto). */
 FASTNN_B200_API int fastnn_b200_set_policy(int policy, int block_n, int split_k);
 
 /* Which path the most recent GEMM call on this thread took: 1 = SIMT, 2 = tcgen05

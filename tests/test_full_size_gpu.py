@@ -40,7 +40,7 @@ def test_square_8192_integer_checksums_are_exact(gpu, layout):
     m = n = k = 8192
     a, b = _int_operands(torch, m, n, k, 40 + layout)
     c = _run(f, layout, a, b)
-    assert f.last_path()["path"] == 2
+    assert f.last_path()["path"] in (2, 3)
     ad, bd, cd = a.double(), b.double(), c.double()
     ones_n = torch.ones(n, 1, device="cuda", dtype=torch.float64)
     ones_m = torch.ones(1, m, device="cuda", dtype=torch.float64)
@@ -85,7 +85,7 @@ def test_scaled_linear_gelu_full_size(gpu):
     w = (torch.rand(k, n, device="cuda", generator=g) * 2 - 1) * bound
     bias = (torch.rand(n, device="cuda", generator=g) * 2 - 1) * 0.01
     y = f.linear_forward(x, w, bias, act=2, layout=NN)
-    assert f.last_path()["path"] == 2
+    assert f.last_path()["path"] in (2, 3)
     rows = np.sort(np.random.default_rng(2).choice(m, 32, replace=False))
     ridx = torch.from_numpy(rows).cuda()
     xh, wh, bh = x[ridx].cpu().numpy(), w.cpu().numpy(), bias.cpu().numpy()

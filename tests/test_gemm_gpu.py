@@ -76,21 +76,22 @@ RAGGED = [  # leading dimensions not multiples of 4 floats: SIMT path
 ]
 
 
+@pytest.mark.parametrize("policy", [3, 4])      # 3: single-CTA tiles, 4: CTA-pair tiles
 @pytest.mark.parametrize("layout", [NN, NT, TN])
 @pytest.mark.parametrize("shape", ALIGNED)
-def test_tensor_core_path_matches_oracle(gpu, layout, shape):
+def test_tensor_core_path_matches_oracle(gpu, layout, shape, policy):
     f = gpu
     m, n, k, batch = shape
     rng = np.random.default_rng(1000 + 7 * layout + m + n + k)
     sa, sb = _shapes(layout, m, n, k, batch)
     a = rng.standard_normal(sa, dtype=np.float32)
     b = rng.standard_normal(sb, dtype=np.float32)
-    f.set_policy(2, 0, 0)          # tensor-core path or fail
+    f.set_policy(policy, 0, 0)     # that tensor-core kernel or fail
     try:
         got = _gpu_fn(f, layout)(_dev(a), _dev(b))
     finally:
         f.set_policy(0, 0, 0)
-    assert f.last_path()["path"] == 2
+    assert f.last_path()["path"] == policy - 1
     check_tf32_parity(_host(got), _oracle(layout, a, b), k, a, b, what=f"L{layout} {shape}")
 
 
@@ -137,13 +138,16 @@ def test_every_tile_width(gpu, layout, block_n):
     sa, sb = _shapes(layout, m, n, k, 0)
     a = rng.standard_normal(sa, dtype=np.float32)
     b = rng.standard_normal(sb, dtype=np.float32)
-    f.set_policy(2, block_n, 1)
-    try:
-        got = _gpu_fn(f, layout)(_dev(a), _dev(b))
-    finally:
-        f.set_policy(0, 0, 0)
-    assert f.last_path()["block_n"] == block_n
-    check_tf32_parity(_host(got), _oracle(layout, a, b), k, a, b)
+    da, db = _dev(a), _dev(b)
+    want = _oracle(layout, a, b)
+    for policy in ([3, 4] if block_n % 64 == 0 else [3]):    # pair tiles come in multiples of 64
+        f.set_policy(policy, block_n, 1)
+        try:
+            got = _gpu_fn(f, layout)(da, db)
+        finally:
+            f.set_policy(0, 0, 0)
+        assert f.last_path()["block_n"] == block_n and f.last_path()["path"] == policy - 1
+        check_tf32_parity(_host(got), want, k, a, b)
 
 
 @pytest.mark.parametrize("split_k", [2, 3, 8, 64])
@@ -156,15 +160,17 @@ def test_split_k_is_exact_in_structure_and_deterministic(gpu, layout, split_k):
     a = rng.standard_normal(sa, dtype=np.float32)
     b = rng.standard_normal(sb, dtype=np.float32)
     da, db = _dev(a), _dev(b)
-    f.set_policy(2, 128, split_k)
-    try:
-        got1 = _host(_gpu_fn(f, layout)(da, db))
-        assert f.last_path()["split_k"] > 1
-        got2 = _host(_gpu_fn(f, layout)(da, db))
-    finally:
-        f.set_policy(0, 0, 0)
-    assert np.array_equal(got1, got2), "split-K reduction must not depend on CTA arrival order"
-    check_tf32_parity(got1, _oracle(layout, a, b), k, a, b)
+    want = _oracle(layout, a, b)
+    for policy in (3, 4):
+        f.set_policy(policy, 128, split_k)
+        try:
+            got1 = _host(_gpu_fn(f, layout)(da, db))
+            assert f.last_path()["split_k"] > 1 and f.last_path()["path"] == policy - 1
+            got2 = _host(_gpu_fn(f, layout)(da, db))
+        finally:
+            f.set_policy(0, 0, 0)
+        assert np.array_equal(got1, got2), "split-K reduction must not depend on CTA arrival order"
+        check_tf32_parity(got1, want, k, a, b)
 
 
 def test_skinny_output_takes_split_k_automatically(gpu):
@@ -219,7 +225,7 @@ def test_general_entry_alpha_beta_strides(gpu, layout, aligned):
               ca + pad, cb + pad, n + pad, ra * (ca + pad), rb * (cb + pad), m * (n + pad),
               alpha, beta)
     torch.cuda.synchronize()
-    assert f.last_path()["path"] == (2 if aligned else 1)
+    assert f.last_path()["path"] in ((2, 3) if aligned else (1,))
     got = _host(dC)
     a, b = np.ascontiguousarray(A[..., :ca]), np.ascontiguousarray(B[..., :cb])
     prod = _oracle(layout, a, b)

@@ -31,7 +31,7 @@ def _operands(layout, m, n, k, seed):
 
 
 def _existing(f, layout, da, db, split_k):
-    f.set_policy(2, 128, split_k)          # same tile width and split as the static entry uses
+    f.set_policy(3, 128, split_k)          # same kernel, tile width and split as the static entry
     try:
         return [f.matmul, f.matmul_nt, f.matmul_tn][layout](da, db)
     finally:
