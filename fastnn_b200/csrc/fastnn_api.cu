@@ -98,6 +98,23 @@ bool encode_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, ui
   return r == CUDA_SUCCESS;
 }
 
+// 4-D FP32 tensor map with the 32-byte-atom swizzle: the chunked view of an MN-major operand.
+// Strides need not ascend: dimension 1 (k) strides by a whole row, dimension 2 (chunk) by 128 B.
+bool encode_map4(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                 uint64_t d3, uint64_t stride1_bytes, uint64_t stride2_bytes,
+                 uint64_t stride3_bytes, uint32_t box0, uint32_t box1, uint32_t box2) {
+  if (g_encode == nullptr) return false;
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {stride1_bytes, stride2_bytes, stride3_bytes};
+  cuuint32_t box[4] = {box0, box1, box2, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 struct Plan {
   int block_n, split_k, stages;
   bool pair;                        // 256 x block_n tiles on CTA pairs (cta_group::2)
@@ -105,9 +122,10 @@ struct Plan {
 
 // Cycle model used to pick the tile shape and the K split.  Per 32-deep k-block (four MMAs) a
 // CTA is bound either by the tensor pipe (block_n / 2 cycles at 4096 dense TF32 flop/clk/SM) or by
-// reading its A and B stage from shared memory at 128 B/clk; an MN-major (32-byte swizzled)
-// operand is charged twice its bytes, which is what the measured NT/NN/TN ratios show.  A CTA
-// pair computes 256 x block_n with each CTA reading only half of B.
+// reading its A and B stage from shared memory at 128 B/clk, or by the producer's TMA issue rate
+// when an MN-major operand has to be fetched one 32-wide chunk per instruction (a_mn / b_mn:
+// extent not a multiple of 32, so the single-box chunked view does not apply).  A CTA pair
+// computes 256 x block_n with each CTA reading only half of B.
 Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, bool a_mn,
                  bool b_mn, int pair_mode /* 0 auto, 1 never, 2 always */) {
   const int num_kb = ceil_div(k, fnn::kBlockK);
@@ -128,10 +146,14 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
     for (int bn = pair ? 64 : 32; bn <= fnn::kMaxBlockN; bn += pair ? 64 : 32) {
       if (bn > n32 && bn > (pair ? 64 : 32)) break;
       const int tiles_n = ceil_div(n, bn);
-      const double a_bytes = 4096.0 * (a_mn ? 2.0 : 1.0);
-      const double b_bytes = (pair ? 16.0 : 32.0) * bn * (b_mn ? 2.0 : 1.0);
+      const double a_bytes = 4096.0;
+      const double b_bytes = (pair ? 16.0 : 32.0) * bn;
       const double t_smem = (a_bytes + b_bytes) / 128.0;
-      const double t_kb = bn / 2.0 > t_smem ? bn / 2.0 : t_smem;
+      // an operand fetched as one box per 32-wide chunk costs the producer ~90 cycles per box
+      const double t_issue = 90.0 * ((a_mn ? 4 : 1) + (b_mn ? (pair ? bn / 64 : bn / 32) : 1));
+      double t_kb = bn / 2.0 > t_smem ? bn / 2.0 : t_smem;
+      if (t_issue > t_kb) t_kb = t_issue;
+      if (pair) t_kb *= 1.12;   // measured: the pair kernel's extra commits and cluster traffic
       for (int s : splits) {
         if (s > 1 && num_kb / s < 4) break;
         const int kbps = ceil_div(num_kb, s);
@@ -210,7 +232,9 @@ int launch_simt(const GemmArgs& g) {
 }
 
 int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
-  const bool a_mn = (g.layout == FASTNN_B200_TN), b_mn = (g.layout != FASTNN_B200_NT);
+  const bool no_chunk = std::getenv("FASTNN_B200_NO_CHUNKED") != nullptr;
+  const bool a_mn = (g.layout == FASTNN_B200_TN) && ((g.m % 32) != 0 || no_chunk);
+  const bool b_mn = (g.layout != FASTNN_B200_NT) && ((g.n % 32) != 0 || no_chunk);
   const int pair_mode = pol.policy == 3 ? 1 : (pol.policy == 4 ? 2 : 0);
   Plan plan = choose_plan(g.m, g.n, g.k, g.batch, st->num_sms, st->max_clusters, a_mn, b_mn,
                           pair_mode);
@@ -245,9 +269,6 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   p.alpha = g.alpha; p.beta = g.beta; p.bias = g.bias; p.act = g.act;
   p.status = st->status;
   p.spin_budget = st->spin_budget;
-  if (const char* e = std::getenv("FASTNN_B200_DEBUG_FLAGS")) p.debug_flags = std::atoi(e);
-  if (const char* e = std::getenv("FASTNN_B200_DEBUG_PTR"))
-    p.debug_buf = reinterpret_cast<unsigned long long*>(std::strtoull(e, nullptr, 0));
 
   // output target: C itself, or the split-K workspace
   float* out = g.c;
@@ -279,15 +300,37 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   const uint64_t sa_bytes = (g.batch > 1 ? g.sa : g.lda * (p.a_mn_major ? g.k : g.m)) * 4ull;
   const uint64_t sb_bytes = (g.batch > 1 ? g.sb : g.ldb * (p.b_mn_major ? g.k : g.n)) * 4ull;
   bool ok;
+  // An MN-major operand whose contiguous extent is a multiple of 32 is also addressable as
+  // (32, k, extent/32, batch): one box then brings all 32-wide chunks of a stage, laid out
+  // chunk-major in shared memory exactly as the per-chunk boxes would.
+  p.a_chunked = (p.a_mn_major && (g.m % 32) == 0 && !no_chunk) ? 1 : 0;
+  p.b_chunked = (p.b_mn_major && (g.n % 32) == 0 && !no_chunk) ? 1 : 0;
   if (!p.a_mn_major)
     ok = encode_map(&tmA, g.a, g.k, g.m, B, g.lda * 4ull, sa_bytes, fnn::kBlockK, fnn::kBlockM);
-  else
-    ok = encode_map(&tmA, g.a, g.m, g.k, B, g.lda * 4ull, sa_bytes, 32, fnn::kBlockK, true);
+  else {
+    ok = false;
+    if (p.a_chunked)
+      ok = encode_map4(&tmA, g.a, 32, g.k, g.m / 32, B, g.lda * 4ull, 128ull, sa_bytes, 32,
+                       fnn::kBlockK, fnn::kBlockM / 32);
+    if (!ok) {   // driver refused the chunked view (or it does not apply): one box per chunk
+      p.a_chunked = 0;
+      ok = encode_map(&tmA, g.a, g.m, g.k, B, g.lda * 4ull, sa_bytes, 32, fnn::kBlockK, true);
+    }
+  }
+  const int b_cols = plan.pair ? plan.block_n / 2 : plan.block_n;   // B columns one CTA loads
   if (!p.b_mn_major)
-    ok = ok && encode_map(&tmB, g.b, g.k, g.n, B, g.ldb * 4ull, sb_bytes, fnn::kBlockK,
-                          plan.pair ? plan.block_n / 2 : plan.block_n);
-  else
-    ok = ok && encode_map(&tmB, g.b, g.n, g.k, B, g.ldb * 4ull, sb_bytes, 32, fnn::kBlockK, true);
+    ok = ok && encode_map(&tmB, g.b, g.k, g.n, B, g.ldb * 4ull, sb_bytes, fnn::kBlockK, b_cols);
+  else {
+    bool okb = false;
+    if (p.b_chunked)
+      okb = encode_map4(&tmB, g.b, 32, g.k, g.n / 32, B, g.ldb * 4ull, 128ull, sb_bytes, 32,
+                        fnn::kBlockK, b_cols / 32);
+    if (!okb) {
+      p.b_chunked = 0;
+      okb = encode_map(&tmB, g.b, g.n, g.k, B, g.ldb * 4ull, sb_bytes, 32, fnn::kBlockK, true);
+    }
+    ok = ok && okb;
+  }
   if (tma_store) {
     const uint64_t sc_bytes = (out_z > 1 ? out_bs : out_ld * g.m) * 4ull;
     ok = ok && encode_map(&tmC, out, g.n, g.m, static_cast<uint64_t>(out_z), out_ld * 4ull,

@@ -62,6 +62,8 @@ struct GemmParams {
   int total_units;     // batch * tiles_m * tiles_n * split_k
   int a_mn_major;      // A stored [k, m]
   int b_mn_major;      // B stored [k, n]
+  int a_chunked;       // MN-major A through a 4-D map (32, k, m/32, batch): one box per stage
+  int b_chunked;       // same for B; needs the M (N) extent to be a multiple of 32
   int store_mode;      // 0: TMA store through tmC, 1: predicated global stores
   float alpha, beta;
   const float* bias;   // [n] or null (ignored when split_k > 1: applied by the reduce pass)
@@ -70,8 +72,6 @@ struct GemmParams {
   long long ldc, c_batch_stride;   // elements
   unsigned int* status;
   long long spin_budget;           // clock64 ticks a single wait may last
-  int debug_flags;                 // experiment switches (0 in production)
-  unsigned long long* debug_buf;   // timestamp trace (null in production)
 };
 
 struct Unit {
@@ -105,13 +105,11 @@ __device__ __forceinline__ float apply_act(float x, int act) {
 // another role's did).
 __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                              const GemmParams& p, unsigned int code) {
-  if ((p.debug_flags & 2) ? ptx::mbar_test_wait(bar, parity) : ptx::mbar_try_wait(bar, parity))
-    return true;
+  if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int it = 0;
   while (true) {
-    if ((p.debug_flags & 2) ? ptx::mbar_test_wait(bar, parity) : ptx::mbar_try_wait(bar, parity))
-      return true;
+    if (ptx::mbar_try_wait(bar, parity)) return true;
     if ((++it & 63) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > p.spin_budget) {
@@ -263,6 +261,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int k0 = kb * kBlockK;
           if (!p.a_mn_major) {
             ptx::tma_load_3d(sa, &tmA, fb, k0, m0, w.b);                       // 32 x 128 box
+          } else if (p.a_chunked) {
+            ptx::tma_load_4d(sa, &tmA, fb, 0, k0, m0 >> 5, w.b);               // 32 x 32 x 4 box
           } else {
 #pragma unroll
             for (int c = 0; c < kBlockM / 32; ++c)
@@ -270,6 +270,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (!p.b_mn_major) {
             ptx::tma_load_3d(sb, &tmB, fb, k0, n0, w.b);                       // 32 x block_n box
+          } else if (p.b_chunked) {
+            ptx::tma_load_4d(sb, &tmB, fb, 0, k0, n0 >> 5, w.b);               // 32 x 32 x bn/32
           } else {
             for (int c = 0; c < p.block_n / 32; ++c)
               ptx::tma_load_3d(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b);

@@ -12,7 +12,7 @@
 //   * both producers credit the LEADER CTA's (cluster rank 0) full barrier, which therefore
 //     expects two arrivals per stage;
 //   * only the leader issues MMAs; its commits arrive on the empty / accumulator-full barriers
-//     of both CTAs (one commit per destination, no multicast form);
+//     of both CTAs (one commit per destination CTA);
 //   * the epilogue warps of both CTAs arrive on the leader's accumulator-empty barrier (8);
 //   * every producer ends by waiting for the last stage releases, and both CTAs meet at a
 //     cluster barrier before freeing TMEM, so no arrival targets a CTA that has exited.
@@ -105,6 +105,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           const int k0 = kb * kBlockK;
           if (!p.a_mn_major) {
             ptx::tma_load_3d_pair(sa, &tmA, fb, k0, m0, w.b);
+          } else if (p.a_chunked) {
+            ptx::tma_load_4d_pair(sa, &tmA, fb, 0, k0, m0 >> 5, w.b);
           } else {
 #pragma unroll
             for (int c = 0; c < kBlockM / 32; ++c)
@@ -112,6 +114,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           }
           if (!p.b_mn_major) {
             ptx::tma_load_3d_pair(sb, &tmB, fb, k0, n0, w.b);         // box 32 x (block_n / 2)
+          } else if (p.b_chunked) {
+            ptx::tma_load_4d_pair(sb, &tmB, fb, 0, k0, n0 >> 5, w.b);
           } else {
             for (int c = 0; c < half_n / 32; ++c)
               ptx::tma_load_3d_pair(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b);
@@ -163,12 +167,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           for (int ks = 0; ks < kBlockK / kUmmaK; ++ks)
             ptx::mma_tf32_2cta(tmem_d, da + ks * a_kstep, db + ks * b_kstep, idesc,
                                (kb > kb0 || ks > 0) ? 1u : 0u);
-          if (p.debug_flags & 1) {
-            ptx::mma_commit_2cta_mask(empty_bar(stage), 3);
-          } else {
-            ptx::mma_commit_2cta(bar0 + 64u + 8u * stage);    // empty[stage], leader
-            ptx::mma_commit_2cta(bar1 + 64u + 8u * stage);    // empty[stage], peer
-          }
+          ptx::mma_commit_2cta(bar0 + 64u + 8u * stage);    // empty[stage], leader
+          ptx::mma_commit_2cta(bar1 + 64u + 8u * stage);    // empty[stage], peer
           if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
