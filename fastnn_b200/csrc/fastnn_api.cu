@@ -131,8 +131,8 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
   const int num_kb = ceil_div(k, fnn::kBlockK);
   const int n32 = ceil_div(n, 32) * 32;
   const double out_bytes = 4.0 * m * n * batch;
-  const double hbm_per_clk = 3000.0;
-  const double floor_cycles = (4.0 * batch * (1.0 * m * k + 1.0 * k * n) + out_bytes) / hbm_per_clk;
+  const double hbm_per_clk = 3400.0;     // 6.5 TB/s at 1.9 GHz
+  const double in_bytes = 4.0 * batch * (1.0 * m * k + 1.0 * k * n);
   Plan best{32, 1, 4, false};
   double best_cost = 1e300;
   static const int splits[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
@@ -146,6 +146,8 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
     for (int bn = pair ? 64 : 32; bn <= fnn::kMaxBlockN; bn += pair ? 64 : 32) {
       if (bn > n32 && bn > (pair ? 64 : 32)) break;
       const int tiles_n = ceil_div(n, bn);
+      // skip widths whose last tile is mostly padding (more than 1/8 of the columns wasted)
+      if ((tiles_n * bn - n32) * 8 > n32 && bn > (pair ? 64 : 32)) continue;
       const double a_bytes = 4096.0;
       const double b_bytes = (pair ? 16.0 : 32.0) * bn;
       const double t_smem = (a_bytes + b_bytes) / 128.0;
@@ -153,16 +155,26 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
       const double t_issue = 90.0 * ((a_mn ? 4 : 1) + (b_mn ? (pair ? bn / 64 : bn / 32) : 1));
       double t_kb = bn / 2.0 > t_smem ? bn / 2.0 : t_smem;
       if (t_issue > t_kb) t_kb = t_issue;
+      // measured floor of one stage hand-over (wait, four MMAs, commit) in the issuing thread
+      if (t_kb < 550.0) t_kb = 550.0;
       if (pair) t_kb *= 1.12;   // measured: the pair kernel's extra commits and cluster traffic
       for (int s : splits) {
-        if (s > 1 && num_kb / s < 4) break;
+        if (s > 1 && num_kb / s < 2) break;
         const int kbps = ceil_div(num_kb, s);
         const int real_split = ceil_div(num_kb, kbps);
         const long long units = 1ll * batch * tiles_m * tiles_n * real_split;
         const double waves = static_cast<double>((units + slots - 1) / slots);
-        double cycles = waves * (kbps * t_kb + 1200.0);
-        if (real_split > 1) cycles += (2.0 * real_split + 1.0) * out_bytes / hbm_per_clk + 6000.0;
-        if (cycles < floor_cycles) cycles = floor_cycles;
+        // HBM time is stretched by idle SMs: a wave that fills only part of the machine still
+        // takes a full wave
+        const double imbalance = waves * slots * (pair ? 2 : 1) / ((pair ? 2.0 : 1.0) * units);
+        const double partial_bytes = real_split > 1 ? real_split * out_bytes : 0.0;
+        const double l2_discount = partial_bytes < 48e6 ? (1.0 / 3.0) : 1.0;   // stays in L2
+        const double main_bytes = in_bytes + (real_split > 1 ? partial_bytes * l2_discount : out_bytes);
+        const double t_hbm = main_bytes / hbm_per_clk * imbalance;
+        const double t_cmp = waves * kbps * t_kb;
+        double cycles = (t_hbm > t_cmp ? t_hbm : t_cmp) + waves * 800.0;
+        if (real_split > 1)
+          cycles += (partial_bytes * l2_discount + out_bytes) / hbm_per_clk + 5000.0;
         // prefer wider tiles, fewer splits and single CTAs on ties
         cycles *= 1.0 + 1e-4 * (8 - bn / 32) + 1e-3 * (real_split - 1) + 1e-4 * pair;
         if (cycles < best_cost) {
@@ -269,6 +281,10 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   p.alpha = g.alpha; p.beta = g.beta; p.bias = g.bias; p.act = g.act;
   p.status = st->status;
   p.spin_budget = st->spin_budget;
+#ifdef FNN_PROFILE_MMA
+  if (const char* e = std::getenv("FASTNN_B200_DEBUG_PTR"))
+    p.debug_buf = reinterpret_cast<long long*>(std::strtoull(e, nullptr, 0));
+#endif
 
   // output target: C itself, or the split-K workspace
   float* out = g.c;
