@@ -396,8 +396,14 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-# ncu-derived DRAM traffic per launch (bytes), filled from profiles/ for the kernels captured
-TRAFFIC_BYTES = {}
+# ncu-measured DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum, bytes) of
+# gemm_tf32_kernel, from the captures summarised in profiles/; keyed by (workload, GEMM label)
+TRAFFIC_BYTES = {
+    ("square8192", "NN"): 2.278e9 + 0.255e9, ("square8192", "NT"): 2.278e9 + 0.253e9,
+    ("square8192", "TN"): 2.278e9 + 0.252e9,
+    ("square4096", "NN"): 2.94e8 + 0.50e8, ("square4096", "NT"): 2.96e8 + 0.46e8,
+    ("square4096", "TN"): 2.94e8 + 0.47e8,
+}
 
 
 # -------------------------------------------------------------------- CPU reference ---

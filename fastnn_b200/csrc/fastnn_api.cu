@@ -157,10 +157,14 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
       if (t_issue > t_kb) t_kb = t_issue;
       // measured floor of one stage hand-over (wait, four MMAs, commit) in the issuing thread
       if (t_kb < 550.0) t_kb = 550.0;
-      if (pair) t_kb *= 1.12;   // measured: the pair kernel's extra commits and cluster traffic
       for (int s : splits) {
         if (s > 1 && num_kb / s < 2) break;
         const int kbps = ceil_div(num_kb, s);
+        // measured at 8192^3: a CTA pair with 256-wide tiles and two k-blocks per stage is ~5 %
+        // faster than single CTAs for a few launches, equal after ~0.2 s and ~8 % slower once the
+        // power cap has pulled the clock down (long runs) -- so single CTAs are the default and
+        // pairs are taken only on request (policy 4)
+        const double t_kb_scale = !pair ? 1.0 : ((bn == 256 && kbps >= 8) ? 1.05 : 1.12);
         const int real_split = ceil_div(num_kb, kbps);
         const long long units = 1ll * batch * tiles_m * tiles_n * real_split;
         const double waves = static_cast<double>((units + slots - 1) / slots);
@@ -171,7 +175,7 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
         const double l2_discount = partial_bytes < 48e6 ? (1.0 / 3.0) : 1.0;   // stays in L2
         const double main_bytes = in_bytes + (real_split > 1 ? partial_bytes * l2_discount : out_bytes);
         const double t_hbm = main_bytes / hbm_per_clk * imbalance;
-        const double t_cmp = waves * kbps * t_kb;
+        const double t_cmp = waves * kbps * t_kb * t_kb_scale;
         double cycles = (t_hbm > t_cmp ? t_hbm : t_cmp) + waves * 800.0;
         if (real_split > 1)
           cycles += (partial_bytes * l2_discount + out_bytes) / hbm_per_clk + 5000.0;
@@ -189,9 +193,9 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
   return best;
 }
 
-int stages_for(int block_n, bool pair = false) {
-  const size_t stage = fnn::kStageABytes +
-                       static_cast<size_t>(pair ? block_n / 2 : block_n) * fnn::kBlockK * 4;
+int stages_for(int block_n, bool pair = false, int kb_per_stage = 1) {
+  const size_t stage = kb_per_stage * (fnn::kStageABytes + static_cast<size_t>(pair ? block_n / 2 : block_n) *
+                                                               fnn::kBlockK * 4);
   const size_t avail = kMaxDynSmem - 1024 - fnn::kStagingBytes - fnn::kBarrierBytes;
   int s = static_cast<int>(avail / stage);
   if (s > fnn::kMaxStages) s = fnn::kMaxStages;
@@ -257,7 +261,15 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   if (plan.split_k > num_kb) plan.split_k = num_kb;
   const int kbps = ceil_div(num_kb, plan.split_k);
   plan.split_k = ceil_div(num_kb, kbps);
-  plan.stages = stages_for(plan.block_n, plan.pair);
+  // CTA pairs with wide tiles take two k-blocks per stage: the issuing thread's per-stage
+  // cost (wait, commit, loop) is then paid once per eight MMAs instead of once per four
+  int kb_per_stage = (plan.pair && plan.block_n == 256 && kbps >= 8) ? 2 : 1;
+  if (const char* e = std::getenv("FASTNN_B200_KB_PER_STAGE")) {
+    const int r = std::atoi(e);
+    if (plan.pair && r >= 1 && r <= 4) kb_per_stage = r;
+  }
+  plan.stages = stages_for(plan.block_n, plan.pair, kb_per_stage);
+  if (plan.stages < 2) { kb_per_stage = 1; plan.stages = stages_for(plan.block_n, plan.pair, 1); }
   if (const char* e = std::getenv("FASTNN_B200_STAGES")) {
     const int s = std::atoi(e);
     if (s >= 1 && s < plan.stages) plan.stages = s;
@@ -273,6 +285,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   p.num_kb = num_kb;
   p.split_k = plan.split_k;
   p.kb_per_split = kbps;
+  p.kb_per_stage = kb_per_stage;
   const long long units = 1ll * g.batch * p.tiles_m * p.tiles_n * plan.split_k;
   if (units > 0x7fffffffll) return -1;
   p.total_units = static_cast<int>(units);
@@ -281,10 +294,6 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   p.alpha = g.alpha; p.beta = g.beta; p.bias = g.bias; p.act = g.act;
   p.status = st->status;
   p.spin_budget = st->spin_budget;
-#ifdef FNN_PROFILE_MMA
-  if (const char* e = std::getenv("FASTNN_B200_DEBUG_PTR"))
-    p.debug_buf = reinterpret_cast<long long*>(std::strtoull(e, nullptr, 0));
-#endif
 
   // output target: C itself, or the split-K workspace
   float* out = g.c;
@@ -360,7 +369,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   if (plan.pair) {
     const int clusters = p.total_units < st->max_clusters ? p.total_units : st->max_clusters;
     grid = 2 * clusters;
-    const size_t smem = fnn::gemm_pair_smem_bytes(plan.block_n, plan.stages);
+    const size_t smem = fnn::gemm_pair_smem_bytes(plan.block_n, plan.stages, kb_per_stage);
     fnn::gemm_tf32_pair_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, p);
   } else {
     grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
@@ -451,7 +460,7 @@ extern "C" int fastnn_cuda_init(int device_id) {
     std::memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(2 * prop.multiProcessorCount, 1, 1);
     cfg.blockDim = dim3(fnn::kNumThreads, 1, 1);
-    cfg.dynamicSmemBytes = fnn::gemm_pair_smem_bytes(fnn::kMaxBlockN, stages_for(fnn::kMaxBlockN, true));
+    cfg.dynamicSmemBytes = fnn::gemm_pair_smem_bytes(fnn::kMaxBlockN, stages_for(fnn::kMaxBlockN, true), 1);
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;

@@ -59,6 +59,7 @@ struct GemmParams {
   int num_kb;          // ceil(k / 32)
   int split_k;         // >= 1
   int kb_per_split;
+  int kb_per_stage;    // 32-deep k-blocks per pipeline stage (CTA-pair kernel only; else 1)
   int total_units;     // batch * tiles_m * tiles_n * split_k
   int a_mn_major;      // A stored [k, m]
   int b_mn_major;      // B stored [k, n]
@@ -72,9 +73,6 @@ struct GemmParams {
   long long ldc, c_batch_stride;   // elements
   unsigned int* status;
   long long spin_budget;           // clock64 ticks a single wait may last
-#ifdef FNN_PROFILE_MMA
-  long long* debug_buf;
-#endif
 };
 
 struct Unit {
@@ -311,10 +309,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t full_addr = full_bar(0);            // barrier, descriptors of the current stage
       uint64_t da = a_desc0, db = b_desc0;
       uint32_t ready = 0;                          // early probe result for the current stage
-#ifdef FNN_PROFILE_MMA
-      long long prof[5] = {0, 0, 0, 0, 0};
-      long long prof_last = 0;
-#endif
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         const Unit w = decode_unit(p, u);
         const int kb0 = w.s * p.kb_per_split;
@@ -325,18 +319,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBlockN);
         uint32_t first = 0u;                          // 0 on the unit's first MMA: overwrite
         for (int kb = kb0; kb < kb1; ++kb) {
-#ifdef FNN_PROFILE_MMA
-          const long long c0 = clock64();
-#endif
           // `ready` is a probe of this stage's barrier issued one iteration earlier, so its
           // latency is hidden behind the previous stage's MMA issue
           if (!ready) {
             ok = wait_barrier(full_addr, phase, abort_flag, p, kStatusMmaTimeout);
             if (!ok) break;
           }
-#ifdef FNN_PROFILE_MMA
-          const long long c1 = clock64();
-#endif
           const uint32_t cur_empty = full_addr + 64u;
           const uint64_t cda = da, cdb = db;
           if (++stage == p.num_stages) {
@@ -350,25 +338,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int ks = 1; ks < kBlockK / kUmmaK; ++ks)
             ptx::mma_tf32_1cta(tmem_d, cda + ks * a_kstep, cdb + ks * b_kstep, idesc, 1u);
-#ifdef FNN_PROFILE_MMA
-          const long long c2 = clock64();
-#endif
           ptx::mma_commit_1cta(cur_empty);            // stage reusable once these MMAs retire
-#ifdef FNN_PROFILE_MMA
-          const long long c3 = clock64();
-          prof[0] += c1 - c0; prof[1] += c2 - c1; prof[2] += c3 - c2; prof[3] += 1;
-          if (prof_last) prof[4] += c0 - prof_last;
-          prof_last = c3;
-#endif
         }
         if (!ok) break;
         ptx::mma_commit_1cta(tfull_bar(acc));       // accumulator complete
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
-#ifdef FNN_PROFILE_MMA
-      if (blockIdx.x == 0 && p.debug_buf != nullptr)
-        for (int i = 0; i < 5; ++i) p.debug_buf[i] = prof[i];
-#endif
     }
   } else {
     // -------------------------------------------------------------- epilogue ---

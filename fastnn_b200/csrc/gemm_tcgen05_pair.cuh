@@ -42,8 +42,11 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int num_clusters = gridDim.x >> 1;
   const int half_n = p.block_n >> 1;                     // B columns this CTA loads
 
-  const uint32_t stage_b_bytes = static_cast<uint32_t>(half_n) * kBlockK * 4;
-  const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
+  // A stage holds kb_per_stage consecutive 32-deep k-blocks, each as [A 16 KiB][B half]; one
+  // barrier round trip (wait, commit) then covers 4 * kb_per_stage MMAs.
+  const int R = p.kb_per_stage;
+  const uint32_t sub_bytes = kStageABytes + static_cast<uint32_t>(half_n) * kBlockK * 4;
+  const uint32_t stage_bytes = static_cast<uint32_t>(R) * sub_bytes;
   const uint32_t staging_base = smem_base + p.num_stages * stage_bytes;
   const uint32_t bar_base = staging_base + kStagingBytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -95,14 +98,16 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const int n0 = w.nt * p.block_n + static_cast<int>(rank) * half_n;
         const int kb0 = w.s * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; kb += R) {
           ok = wait_barrier(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
           if (!ok) break;
-          const uint32_t sa = smem_base + stage * stage_bytes;
-          const uint32_t sb = sa + kStageABytes;
+          const int nsub = min(R, kb1 - kb);          // k-blocks of this unit left for the stage
           const uint32_t fb = ptx::mapa_shared(full_bar(stage), 0);     // leader's barrier
-          ptx::mbar_expect_tx_cluster(fb, stage_bytes);
-          const int k0 = kb * kBlockK;
+          ptx::mbar_expect_tx_cluster(fb, static_cast<uint32_t>(nsub) * sub_bytes);
+          for (int r = 0; r < nsub; ++r) {
+          const uint32_t sa = smem_base + stage * stage_bytes + r * sub_bytes;
+          const uint32_t sb = sa + kStageABytes;
+          const int k0 = (kb + r) * kBlockK;
           if (!p.a_mn_major) {
             ptx::tma_load_3d_pair(sa, &tmA, fb, k0, m0, w.b);
           } else if (p.a_chunked) {
@@ -119,6 +124,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           } else {
             for (int c = 0; c < half_n / 32; ++c)
               ptx::tma_load_3d_pair(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b);
+          }
           }
           if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
         }
@@ -142,6 +148,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const uint64_t a_kstep = (p.a_mn_major ? 1024u : kUmmaK * 4u) >> 4;
       const uint64_t b_kstep = (p.b_mn_major ? 1024u : kUmmaK * 4u) >> 4;
       const uint64_t stage_step = stage_bytes >> 4;
+      const uint64_t sub_step = sub_bytes >> 4;
       // the two CTAs' copies of a barrier differ by a constant in the cluster address space
       const uint32_t bar0 = ptx::mapa_shared(bar_base, 0);
       const uint32_t bar1 = ptx::mapa_shared(bar_base, 1);
@@ -158,15 +165,20 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBlockN);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        uint32_t accumulate = 0u;                     // 0 on the unit's first MMA: overwrite
+        for (int kb = kb0; kb < kb1; kb += R) {
           ok = wait_barrier(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout);
           if (!ok) break;
-          const uint64_t da = a_desc0 + stage * stage_step;
-          const uint64_t db = b_desc0 + stage * stage_step;
+          const int nsub = min(R, kb1 - kb);
+          for (int r = 0; r < nsub; ++r) {
+            const uint64_t da = a_desc0 + stage * stage_step + r * sub_step;
+            const uint64_t db = b_desc0 + stage * stage_step + r * sub_step;
 #pragma unroll
-          for (int ks = 0; ks < kBlockK / kUmmaK; ++ks)
-            ptx::mma_tf32_2cta(tmem_d, da + ks * a_kstep, db + ks * b_kstep, idesc,
-                               (kb > kb0 || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
+              ptx::mma_tf32_2cta(tmem_d, da + ks * a_kstep, db + ks * b_kstep, idesc, accumulate);
+              accumulate = 1u;
+            }
+          }
           ptx::mma_commit_2cta(bar0 + 64u + 8u * stage);    // empty[stage], leader
           ptx::mma_commit_2cta(bar1 + 64u + 8u * stage);    // empty[stage], peer
           if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
@@ -224,8 +236,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 }
 
 // Dynamic shared memory per CTA of the pair kernel.
-inline size_t gemm_pair_smem_bytes(int block_n, int num_stages) {
-  return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + (block_n / 2) * kBlockK * 4) +
+inline size_t gemm_pair_smem_bytes(int block_n, int num_stages, int kb_per_stage) {
+  return 1024 + static_cast<size_t>(num_stages) * kb_per_stage *
+                    (kStageABytes + (block_n / 2) * kBlockK * 4) +
          kStagingBytes + kBarrierBytes;
 }
 

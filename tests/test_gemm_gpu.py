@@ -173,6 +173,27 @@ def test_split_k_is_exact_in_structure_and_deterministic(gpu, layout, split_k):
         check_tf32_parity(got1, want, k, a, b)
 
 
+@pytest.mark.parametrize("layout", [NN, NT, TN])
+@pytest.mark.parametrize("k,split_k", [(2052, 3), (1000, 1), (288, 1), (8192, 5)])
+def test_pair_kernel_two_k_blocks_per_stage(gpu, layout, k, split_k):
+    """256 x 256 CTA-pair tiles take two 32-deep k-blocks per pipeline stage once a unit has at
+    least eight of them; odd block counts and split boundaries leave a half-filled stage."""
+    f = gpu
+    m, n = 520, 512
+    rng = np.random.default_rng(k + split_k + layout)
+    sa, sb = _shapes(layout, m, n, k, 0)
+    a = rng.standard_normal(sa, dtype=np.float32)
+    b = rng.standard_normal(sb, dtype=np.float32)
+    f.set_policy(4, 256, split_k)
+    try:
+        got = _host(_gpu_fn(f, layout)(_dev(a), _dev(b)))
+    finally:
+        f.set_policy(0, 0, 0)
+    lp = f.last_path()
+    assert lp["path"] == 3 and lp["block_n"] == 256 and lp["split_k"] == split_k
+    check_tf32_parity(got, _oracle(layout, a, b), k, a, b)
+
+
 def test_skinny_output_takes_split_k_automatically(gpu):
     f = gpu
     rng = np.random.default_rng(9)
