@@ -552,6 +552,57 @@ def run_reference_gpu(args, rank, world, local_rank):
                       "workload": args.workload, "per_gemm": out}), flush=True)
 
 
+def run_dw_ksharded(args, rank, world, local_rank):
+    """Extra arm (needs >= 2 GPUs): the data-parallel weight gradient dW[4096,16384] = X^T . dY with
+    the contraction dimension sharded over ranks (32768 rows of X and dY per rank).  Times the fused
+    form (GEMM epilogues store partial tiles into the owning rank's symmetric memory over NVLink,
+    then a fixed-order reduce) against local GEMM + NCCL all_reduce."""
+    import torch
+    import torch.distributed as dist
+    import fastnn_b200 as f
+    from fastnn_b200 import sharding
+    torch.cuda.set_device(local_rank)
+    f.cuda_init(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    m, n, k = 4096, 16384, 32768
+    gen = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    x = torch.randn(k, m, device="cuda", generator=gen)
+    dy = torch.randn(k, n, device="cuda", generator=gen) * 1e-3
+    ws = sharding.KShardedGradWorkspace(m, n)
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        dist.barrier(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    fused_ms = timed(lambda: sharding.k_sharded_matmul_tn(x, dy, workspace=ws, fused=True))
+    plain_ms = timed(lambda: sharding.k_sharded_matmul_tn(x, dy, fused=False))
+    gemm_ms = timed(lambda: f.matmul_tn(x, dy))
+    a = sharding.k_sharded_matmul_tn(x, dy, workspace=ws, fused=True)
+    b = sharding.k_sharded_matmul_tn(x, dy, fused=False)
+    err = ((a - b).norm() / b.norm()).item()
+    assert f.device_status() == 0
+    if rank == 0:
+        flops = 2.0 * m * n * k * world
+        print(json.dumps({
+            "impl": "dw_ksharded", "n_gpus": world, "m": m, "n": n, "k_per_rank": k,
+            "local_gemm_ms": gemm_ms, "fused_ms": fused_ms, "gemm_plus_allreduce_ms": plain_ms,
+            "fused_tflops": flops / (fused_ms * 1e-3) / 1e12,
+            "gemm_plus_allreduce_tflops": flops / (plain_ms * 1e-3) / 1e12,
+            "exchange_bytes_per_rank": 4.0 * m * n * (world - 1) / world,
+            "fused_vs_plain_rel_diff": err}), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -571,7 +622,12 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.workload == "dw_ksharded":
+        if world < 2:
+            print(json.dumps({"impl": "dw_ksharded", "unavailable": "needs at least two ranks (torchrun)"}))
+            return
+        run_dw_ksharded(args, rank, world, local_rank)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     elif args.impl == "reference_gpu":
         run_reference_gpu(args, rank, world, local_rank)

@@ -595,6 +595,33 @@ extern "C" int fastnn_b200_linear_forward(int layout, const float* x, const floa
   return gemm_dispatch(g);
 }
 
+extern "C" int fastnn_b200_reduce_partials(const float* partials, float* c, int m, int n, int count,
+                                           long long ldc, float alpha, float beta,
+                                           const float* bias, int act, void* stream) {
+  if (m < 0 || n < 0 || count < 1 || act < 0 || act > 2 || ldc < n) return -1;
+  if (m == 0 || n == 0) return 0;
+  if (partials == nullptr || c == nullptr) return -1;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState* st = current_state();
+  if (st == nullptr) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long total = 1ll * m * n;
+  const bool vec = (n & 3) == 0 && aligned16(partials) && aligned16(c) && (ldc & 3) == 0 &&
+                   (bias == nullptr || aligned16(bias));
+  long long blocks = ((vec ? total / 4 : total) + 255) / 256;
+  if (blocks > 8ll * st->num_sms) blocks = 8ll * st->num_sms;
+  if (blocks < 1) blocks = 1;
+  if (vec)
+    fnn::splitk_reduce_vec4_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        reinterpret_cast<const float4*>(partials), c, bias, m, n, 1, count, ldc, total, alpha, beta, act);
+  else
+    fnn::splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        partials, c, bias, m, n, 1, count, ldc, total, alpha, beta, act);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  FNN_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 extern "C" int fastnn_b200_set_policy(int policy, int block_n, int split_k) {
   if (policy < 0 || policy > 4) return -1;
   if (block_n < 0 || block_n > fnn::kMaxBlockN || (block_n % 32) != 0) return -1;

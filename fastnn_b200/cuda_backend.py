@@ -224,6 +224,16 @@ def gemm_splitk_static(layout, a, b, m, n, k, split_k, out=None, stream=0):
     return c
 
 
+def reduce_partials(partials_ptr, c_ptr, m, n, count, ldc=None, alpha=1.0, beta=0.0, bias_ptr=0,
+                    act=ACT_NONE, stream=0) -> None:
+    """c = act(alpha * sum_i partials[i] + beta * c + bias), partials = count dense [m,n] blocks."""
+    rc = lib().fastnn_b200_reduce_partials(ctypes.c_void_p(partials_ptr), ctypes.c_void_p(c_ptr), m, n,
+                                           count, n if ldc is None else ldc, alpha, beta,
+                                           ctypes.c_void_p(bias_ptr), act, ctypes.c_void_p(stream))
+    if rc != 0:
+        raise CudaError("fastnn_b200_reduce_partials failed")
+
+
 def set_policy(policy: int = 0, block_n: int = 0, split_k: int = 0) -> None:
     if lib().fastnn_b200_set_policy(policy, block_n, split_k) != 0:
         raise ValueError("bad policy")

@@ -94,3 +94,81 @@ def all_gather_rows(c_local: torch.Tensor, total_rows: int, group=None) -> torch
         q0, q1 = row_partition(total_rows, world, r)
         pieces.append(parts[r][: q1 - q0])
     return torch.cat(pieces, dim=0)
+
+
+# ------------------------------------------------------------------------------------------
+# K-sharded weight gradient:  dW[m,n] = X^T . dY  with the CONTRACTION dimension split over ranks
+# (each rank holds its own rows of X[k,m] and dY[k,n] -- the data-parallel case of FastNN's
+# MatmulBackward, src/autograd/backward_ops.rs:93).  Every rank's product is a partial sum of the
+# whole dW, so an exchange is unavoidable; the result is reduce-scattered: rank r ends with rows
+# row_partition(m, world, r) of dW.
+#
+# Fused form (CUDA): this is split-K across GPUs.  Rank r runs one GEMM per destination rank o
+# over the column slice of X that produces o's rows, and the GEMM's own epilogue (TMA stores)
+# writes the partial tile straight into slot r of o's symmetric-memory workspace over NVLink --
+# the transfer of tile i overlaps the math of tile i+1, no staging copy, no separate collective.
+# After one symmetric-memory barrier each rank adds its `world` slots in ascending rank order
+# (deterministic) with the split-K reduce kernel.
+# Plain form: local GEMM + all_reduce, then slice (what "call NCCL after the GEMM" costs; also the
+# path CPU ranks can run).
+# ------------------------------------------------------------------------------------------
+
+class KShardedGradWorkspace:
+    """Symmetric-memory slots for one (m, n): on every rank [world][rows_max][n] floats."""
+
+    def __init__(self, m: int, n: int, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.m, self.n = m, n
+        self.rows_max = -(-m // self.world)
+        self.slots = symm_mem.empty((self.world, self.rows_max, n), dtype=torch.float32,
+                                    device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm_mem.rendezvous(self.slots, self.group)
+        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+
+    def slot_ptr(self, owner: int, writer: int) -> int:
+        return self.peer_ptrs[owner] + 4 * writer * self.rows_max * self.n
+
+
+def k_sharded_matmul_tn(x_local: torch.Tensor, dy_local: torch.Tensor, group=None,
+                        workspace: Optional[KShardedGradWorkspace] = None, fused: bool = True,
+                        local_matmul: Optional[Callable] = None) -> torch.Tensor:
+    """This rank's rows of dW = sum over ranks of X_r^T . dY_r.  x_local [k_r, m], dy_local [k_r, n]."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    k_r, m = x_local.shape
+    n = dy_local.shape[1]
+    if dy_local.shape[0] != k_r:
+        raise ValueError("x_local and dy_local must have the same number of rows")
+    r0, r1 = row_partition(m, world, rank)
+    if not fused or not x_local.is_cuda:
+        fn = local_matmul or _cuda_local
+        partial = fn(TN, x_local, dy_local)                  # full [m, n] partial sum
+        dist.all_reduce(partial, group=group)
+        return partial[r0:r1].contiguous()
+    ws = workspace or KShardedGradWorkspace(m, n, group)
+    if (ws.m, ws.n, ws.world) != (m, n, world):
+        raise ValueError("workspace was built for another problem")
+    cb._check(x_local, "x_local"); cb._check(dy_local, "dy_local")
+    cb._ensure_ctx(x_local)
+    ws.handle.barrier(channel=0)                             # previous use of the slots is over
+    for step in range(world):                                # start at the neighbour: spread traffic
+        owner = (rank + 1 + step) % world
+        o0, o1 = row_partition(m, world, owner)
+        if o1 == o0:
+            continue
+        cb.gemm_ex(TN, x_local.data_ptr() + 4 * o0, dy_local.data_ptr(), ws.slot_ptr(owner, rank),
+                   o1 - o0, n, k_r, 1, m, n, n, 0, 0, 0)
+    ws.handle.barrier(channel=1)                             # every partial has landed
+    out = torch.empty((r1 - r0, n), dtype=torch.float32, device=x_local.device)
+    if r1 > r0:
+        # slots are [world][rows_max][n]; a partial occupies the first r1-r0 rows of its slot, so
+        # the reduce walks slots with a stride of rows_max*n by treating them as rows_max-row blocks
+        if r1 - r0 == ws.rows_max:
+            cb.reduce_partials(ws.slots.data_ptr(), out.data_ptr(), r1 - r0, n, world)
+        else:
+            packed = ws.slots[:, : r1 - r0].contiguous()
+            cb.reduce_partials(packed.data_ptr(), out.data_ptr(), r1 - r0, n, world)
+    return out

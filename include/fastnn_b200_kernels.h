@@ -107,6 +107,16 @@ FASTNN_B200_API int fastnn_b200_gemm_ex(int layout, const float* a, const float*
 FASTNN_B200_API int fastnn_b200_linear_forward(int layout, const float* x, const float* w, const float* bias,
                                float* y, int rows, int in_features, int out_features, int act);
 
+/* c[m,n] = act( alpha * (partials[0] + partials[1] + ... + partials[count-1]) + beta * c + bias ),
+ * partials stored back to back as count dense [m,n] matrices, added in ascending order.
+ * The reduce step of split-K, exposed for the multi-GPU weight-gradient path where the K
+ * dimension is split over ranks and every rank stores its partial product for a block of rows
+ * straight into the owning rank's memory (K-sharded form of FastNN's MatmulBackward
+ * dB = A^T . dC, src/autograd/backward_ops.rs:93).  ldc in elements; stream as above. */
+FASTNN_B200_API int fastnn_b200_reduce_partials(const float* partials, float* c, int m, int n,
+                                                int count, long long ldc, float alpha, float beta,
+                                                const float* bias, int act, void* stream);
+
 /* Split-K GEMM that allocates nothing.  It has no counterpart in FastNN.
  *
  *   C[m,n] = op(A) . op(B)      dense operands, layout as above, alpha = 1, beta = 0

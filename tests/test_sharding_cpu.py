@@ -69,6 +69,15 @@ def _worker(rank, world, port, results):
         s_local = sharding.sharded_matmul(NT, q[r0:r1], kk[r0:r1], local_matmul=_oracle_local)
         full = sharding.all_gather_rows(s_local, 5)
         ok = ok and torch.equal(full, _oracle_local(NT, q, kk))
+        # K-sharded weight gradient (plain form: local product + all_reduce, then this rank's rows)
+        x = torch.from_numpy(rng.standard_normal((12, 7), dtype=np.float32))     # [k, m]
+        dy = torch.from_numpy(rng.standard_normal((12, 5), dtype=np.float32))    # [k, n]
+        k0, k1 = sharding.row_partition(12, world, rank)
+        mine = sharding.k_sharded_matmul_tn(x[k0:k1].contiguous(), dy[k0:k1].contiguous(), fused=False,
+                                            local_matmul=_oracle_local)
+        m0, m1 = sharding.row_partition(7, world, rank)
+        ok = ok and tuple(mine.shape) == (m1 - m0, 5)
+        ok = ok and torch.allclose(mine, _oracle_local(TN, x, dy)[m0:m1], atol=1e-5)
         flag = torch.tensor([1 if ok else 0])
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if rank == 0:
