@@ -603,6 +603,55 @@ def run_dw_ksharded(args, rank, world, local_rank):
     dist.destroy_process_group()
 
 
+def run_attention_fused(args, local_rank):
+    """Extra arm: the fused attention core (512 heads, T = 128, head_dim 32, causal) against the
+    two batched GEMMs it replaces.  Device time from CUDA graphs; bytes = Q, K, V, O once."""
+    import torch
+    import fastnn_b200 as f
+    torch.cuda.set_device(local_rank)
+    f.cuda_init(local_rank)
+    heads, t, d = 512, 128, 32
+    gen = torch.Generator(device="cuda").manual_seed(3000)
+    q = torch.randn(heads, t, d, device="cuda", generator=gen)
+    k = torch.randn(heads, t, d, device="cuda", generator=gen)
+    v = torch.randn(heads, t, d, device="cuda", generator=gen)
+    o = torch.empty_like(q)
+    s = torch.empty(heads, t, t, device="cuda")
+    scale = 1.0 / d ** 0.5
+    side = torch.cuda.Stream()
+
+    def graph_us(fn, reps=20):
+        with torch.cuda.stream(side):
+            fn(side.cuda_stream)
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(reps):
+                fn(torch.cuda.current_stream().cuda_stream)
+        g.replay(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            g.replay()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (5 * reps) * 1e3
+
+    fused = graph_us(lambda sp: f.attention_forward(q, k, v, scale=scale, causal=True, out=o, stream=sp))
+    gemm_s = graph_us(lambda sp: f.gemm_ex(NT, q.data_ptr(), k.data_ptr(), s.data_ptr(), t, t, d, heads,
+                                           d, d, t, t * d, t * d, t * t, 1.0, 0.0, 0, 0, sp))
+    gemm_o = graph_us(lambda sp: f.gemm_ex(NN, s.data_ptr(), v.data_ptr(), o.data_ptr(), t, d, t, heads,
+                                           t, d, d, t * t, t * d, t * d, 1.0, 0.0, 0, 0, sp))
+    peaks = load_peaks()
+    byts = 4.0 * heads * t * d * 4
+    assert f.device_status() == 0
+    print(json.dumps({
+        "impl": "attention_fused", "heads": heads, "t": t, "head_dim": d, "causal": True,
+        "fused_us": fused, "fused_gbs": byts / fused / 1e3, "fused_frac_of_hbm": byts / fused / 1e3 / peaks["hbm_gbs"],
+        "unfused_gemms_only_us": gemm_s + gemm_o,
+        "note": "unfused figure omits FastNN's scale, mask-add and softmax launches and their 3 x 33.5 MB temporaries",
+        "algorithmic_bytes": byts}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -622,7 +671,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.workload == "dw_ksharded":
+    if args.workload == "attention_fused":
+        if rank == 0:
+            run_attention_fused(args, local_rank)
+    elif args.workload == "dw_ksharded":
         if world < 2:
             print(json.dumps({"impl": "dw_ksharded", "unavailable": "needs at least two ranks (torchrun)"}))
             return

@@ -17,6 +17,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_tcgen05.cuh"
 #include "gemm_tcgen05_pair.cuh"
+#include "attention_tcgen05.cuh"
 
 namespace {
 
@@ -593,6 +594,60 @@ extern "C" int fastnn_b200_linear_forward(int layout, const float* x, const floa
              1ll * rows * in_features, 1ll * in_features * out_features, 1ll * rows * out_features,
              1.0f, 0.0f, bias, act, nullptr};
   return gemm_dispatch(g);
+}
+
+extern "C" int fastnn_b200_attention_forward(const float* q, const float* k, const float* v, float* o,
+                                             int batch_heads, int t_q, int t_k, int head_dim,
+                                             float scale, int causal, void* stream) {
+  if (batch_heads < 0 || t_q < 0 || t_k < 1 || head_dim < 1) return -1;
+  if (batch_heads == 0 || t_q == 0) return 0;
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr) return -1;
+  // what the fused kernel covers; anything else is for the caller to compose from the GEMMs
+  if ((head_dim % 32) != 0 || head_dim > 128 || t_k > 256 || !(scale > 0.0f)) return -1;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return -1;
+  const int tk_pad = ceil_div(t_k, 32) * 32;
+  int nsets = 2;                                   // double-buffer Q/K/V across units if it fits
+  fnn::AttnSmem plan = fnn::attn_smem_plan(head_dim, tk_pad, nsets);
+  if (plan.total > kMaxDynSmem) {
+    nsets = 1;
+    plan = fnn::attn_smem_plan(head_dim, tk_pad, nsets);
+  }
+  if (plan.total > kMaxDynSmem) return -1;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState* st = current_state();
+  if (st == nullptr) return -1;
+  static bool attr_set[kMaxDevices] = {};
+  int dev = 0;
+  FNN_CUDA_OK(cudaGetDevice(&dev));
+  if (!attr_set[dev]) {
+    FNN_CUDA_OK(cudaFuncSetAttribute(fnn::attention_tf32_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kMaxDynSmem)));
+    attr_set[dev] = true;
+  }
+  fnn::AttnParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.heads = batch_heads; p.tq = t_q; p.tk = t_k; p.d = head_dim; p.tk_pad = tk_pad;
+  p.q_tiles = ceil_div(t_q, 128);
+  const long long units = 1ll * batch_heads * p.q_tiles;
+  if (units > 0x7fffffffll) return -1;
+  p.total_units = static_cast<int>(units);
+  p.scale = scale; p.causal = causal ? 1 : 0; p.nsets = nsets;
+  p.status = st->status; p.spin_budget = st->spin_budget;
+  CUtensorMap tmQ, tmK, tmV, tmO;
+  const uint64_t D = head_dim, H = batch_heads;
+  bool ok = encode_map(&tmQ, q, D, t_q, H, D * 4ull, D * 4ull * t_q, 32, 128);
+  ok = ok && encode_map(&tmK, k, D, t_k, H, D * 4ull, D * 4ull * t_k, 32, tk_pad);
+  ok = ok && encode_map(&tmV, v, D, t_k, H, D * 4ull, D * 4ull * t_k, 32, tk_pad, true);
+  ok = ok && encode_map(&tmO, o, D, t_q, H, D * 4ull, D * 4ull * t_q, 32, 32);
+  if (!ok) return -1;
+  const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
+  fnn::attention_tf32_kernel<<<grid, fnn::kNumThreads, plan.total, static_cast<cudaStream_t>(stream)>>>(
+      tmQ, tmK, tmV, tmO, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  FNN_CUDA_OK(cudaGetLastError());
+  t_last = LastCall{4, tk_pad, 1, grid};
+  return 0;
 }
 
 extern "C" int fastnn_b200_reduce_partials(const float* partials, float* c, int m, int n, int count,

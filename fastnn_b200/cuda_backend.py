@@ -224,6 +224,26 @@ def gemm_splitk_static(layout, a, b, m, n, k, split_k, out=None, stream=0):
     return c
 
 
+def attention_forward(q, k, v, scale=None, causal=False, out=None, stream=0):
+    """softmax(scale * q.k^T + causal mask) . v for q [.., t_q, d], k, v [.., t_k, d] in one
+    launch (the core of MultiHeadAttention::forward_attn, src/nn/transformer.rs:87-115)."""
+    _check(q, "q"); _check(k, "k"); _check(v, "v")
+    _ensure_ctx(q)
+    tq, d = int(q.shape[-2]), int(q.shape[-1])
+    tk = int(k.shape[-2])
+    heads = _batch_of(q)
+    if tuple(k.shape) != tuple(v.shape) or int(k.shape[-1]) != d or _batch_of(k) != heads:
+        raise ValueError("attention shape mismatch")
+    if scale is None:
+        scale = 1.0 / (d ** 0.5)
+    o = _out(tuple(q.shape), q, out)
+    rc = lib().fastnn_b200_attention_forward(_ptr(q), _ptr(k), _ptr(v), _ptr(o), heads, tq, tk, d,
+                                             float(scale), 1 if causal else 0, ctypes.c_void_p(stream))
+    if rc != 0:
+        raise CudaError("CUDA attention_forward failed (shape outside the fused kernel's range?)")
+    return o
+
+
 def reduce_partials(partials_ptr, c_ptr, m, n, count, ldc=None, alpha=1.0, beta=0.0, bias_ptr=0,
                     act=ACT_NONE, stream=0) -> None:
     """c = act(alpha * sum_i partials[i] + beta * c + bias), partials = count dense [m,n] blocks."""

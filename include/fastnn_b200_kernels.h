@@ -107,6 +107,20 @@ FASTNN_B200_API int fastnn_b200_gemm_ex(int layout, const float* a, const float*
 FASTNN_B200_API int fastnn_b200_linear_forward(int layout, const float* x, const float* w, const float* bias,
                                float* y, int rows, int in_features, int out_features, int act);
 
+/* Fused attention core, per head h in [0, batch_heads):
+ *   O[h] = softmax( scale * Q[h] . K[h]^T + mask ) . V[h]
+ * q [batch_heads, t_q, head_dim], k and v [batch_heads, t_k, head_dim], o like q, all dense.
+ * mask: with causal != 0, key j is hidden from query i when j > i (FastNN adds -1e9 there,
+ * src/nn/transformer.rs:22-27); softmax over keys as src/tensor/ops.rs:273-284.  One launch
+ * instead of FastNN's batched matmul + mul_scalar + add + softmax + batched matmul
+ * (src/nn/transformer.rs:87-115); the [batch_heads, t_q, t_k] scores never reach memory.
+ * Covers head_dim in {32, 64, 96, 128}, t_k <= 256, scale > 0 and shapes whose working set
+ * fits shared memory; returns -1 for anything else (compose it from the GEMM entries). */
+FASTNN_B200_API int fastnn_b200_attention_forward(const float* q, const float* k, const float* v,
+                                                  float* o, int batch_heads, int t_q, int t_k,
+                                                  int head_dim, float scale, int causal,
+                                                  void* stream);
+
 /* c[m,n] = act( alpha * (partials[0] + partials[1] + ... + partials[count-1]) + beta * c + bias ),
  * partials stored back to back as count dense [m,n] matrices, added in ascending order.
  * The reduce step of split-K, exposed for the multi-GPU weight-gradient path where the K

@@ -182,6 +182,27 @@ ORACLE_API void oracle_causal_softmax(float* s, size_t batch, size_t t, float sc
     }
 }
 
+/* Rectangular form of the same composition (t_q queries, t_k keys), mask optional:
+ * mul_scalar(scale) -> (+ 0/-1e9 mask where key > query) -> row softmax over keys.
+ * In place on s[batch, t_q, t_k]. */
+ORACLE_API void oracle_masked_softmax(float* s, size_t batch, size_t tq, size_t tk, float scale,
+                                      int causal) {
+  for (size_t b = 0; b < batch; ++b)
+    for (size_t qi = 0; qi < tq; ++qi) {
+      float* row = s + (b * tq + qi) * tk;
+      for (size_t ki = 0; ki < tk; ++ki) {
+        float v = row[ki] * scale;
+        if (causal) v = v + (ki > qi ? -1e9f : 0.0f);
+        row[ki] = v;
+      }
+      float mx = -INFINITY;
+      for (size_t ki = 0; ki < tk; ++ki) mx = row[ki] > mx ? row[ki] : mx;
+      float sum = 0.0f;
+      for (size_t ki = 0; ki < tk; ++ki) sum += expf(row[ki] - mx);
+      for (size_t ki = 0; ki < tk; ++ki) row[ki] = expf(row[ki] - mx) / sum;
+    }
+}
+
 /* ---------------------------------------------------------------------------
  * Row-parallel twin.  NOT in the reference (its rayon dependency is never
  * called): the outer row loop of the same nest is split over threads, each row

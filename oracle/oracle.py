@@ -14,7 +14,7 @@ from . import build_oracle as _b
 
 __all__ = [
     "rand_data", "matmul", "matmul_nt", "matmul_tn", "matmul_rows", "transpose",
-    "bias_act", "linear", "causal_softmax", "host_threads", "ACT_NONE", "ACT_RELU",
+    "bias_act", "linear", "causal_softmax", "attention", "host_threads", "ACT_NONE", "ACT_RELU",
     "ACT_GELU", "ref_gpu_library_path",
 ]
 
@@ -188,6 +188,20 @@ def causal_softmax(scores: np.ndarray, scale: float) -> np.ndarray:
     assert t == t2
     _load().oracle_causal_softmax(_p(s), batch, t, ctypes.c_float(scale))
     return s
+
+
+def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, causal: bool) -> np.ndarray:
+    """The attention core of MultiHeadAttention::forward_attn on CPU tensors
+    (src/nn/transformer.rs:87-115): matmul(q, k^T) * scale (+ mask) -> softmax -> matmul(., v).
+    q [heads, t_q, d], k and v [heads, t_k, d]."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    s = matmul(q, transpose(k))                 # forward uses the NN entry on a materialised K^T
+    heads, tq, tk = s.shape
+    lib = _load()
+    lib.oracle_masked_softmax.argtypes = [_fp, _sz, _sz, _sz, ctypes.c_float, ctypes.c_int]
+    lib.oracle_masked_softmax.restype = None
+    lib.oracle_masked_softmax(_p(s), heads, tq, tk, ctypes.c_float(scale), 1 if causal else 0)
+    return matmul(s, v)
 
 
 def ref_gpu_library_path():
