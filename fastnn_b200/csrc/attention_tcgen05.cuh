@@ -4,17 +4,19 @@
 // What FastNN does for this (src/nn/transformer.rs:87-115): batched matmul Q.K^T, mul_scalar,
 // additive mask (0 / -1e9 above the diagonal, :22-27), row softmax (src/tensor/ops.rs:273-284),
 // batched matmul with V -- five launches and three [heads, Tq, Tk] temporaries.  Here one
-// persistent CTA per SM walks (head, 128-query tile) units:
+// persistent CTA per SM walks (head, 128-query tile) units as a software pipeline:
 //   warp 0     TMA: Q tile, all keys K and values V of the head into one of two buffer sets
-//   warp 1     one lane issues  S = Q.K^T   (tcgen05.mma kind::tf32, M=128, N=Tk padded, TMEM)
-//              and later        O = P.V     (A = P from shared memory, B = V MN-major)
-//   warps 2-5  one thread per query row: read S from TMEM, scale + mask, row max, exp, row
-//              sum; write the unnormalised probabilities P to shared memory in the K-major
-//              128B-swizzled layout the second MMA reads; afterwards read O from TMEM,
-//              divide by the row sum and store through a swizzled staging tile + TMA store.
-// Limits: head_dim a multiple of 32 up to 128, Tk up to 256 (one softmax pass, no rescaling),
-// and the working set must fit 227 KiB of shared memory (checked on the host).
-// All mbarrier waits are bounded as in the GEMM kernels.
+//   warp 1     one lane issues  S = Q.K^T   (tcgen05.mma kind::tf32, M=128, N=Tk padded) into one
+//              of two score tiles in TMEM, and  O = P.V  with the A operand P read FROM TMEM
+//              (V is the MN-major B operand in shared memory) into one of two O tiles
+//   warps 2-9  two groups of four warps, one thread per query row, taking alternate units: read S
+//              from TMEM, scale + mask, row max, exp2, row sum, write the unnormalised
+//              probabilities P back over S in TMEM (tcgen05.st); then read O from TMEM, divide
+//              by the row sum and store through a swizzled staging tile + TMA store.
+// While one group waits for P.V of unit i and writes it out, the other runs the softmax of unit
+// i+1 and the tensor core the products on either side.
+// Limits: head_dim a multiple of 32 up to 128, Tk up to 256, scale > 0, and the operand sets must
+// fit shared memory (checked on the host).  Every mbarrier wait is bounded as in the GEMM kernels.
 #pragma once
 #include "gemm_tcgen05.cuh"
 
@@ -27,7 +29,7 @@ struct AttnParams {
   int total_units;               // heads * q_tiles
   float scale;
   int causal;
-  int nsets;                     // Q/K/V buffer sets in shared memory: 2 when they fit, else 1
+  int nsets;                     // Q/K/V buffer sets in shared memory, 1..4 as fit and are useful
   unsigned int* status;
   long long spin_budget;
 };
@@ -40,8 +42,12 @@ enum : unsigned int {
 
 // shared-memory plan (bytes); every region is 1024-byte aligned
 struct AttnSmem {
-  uint32_t q_bytes, k_bytes, v_bytes, set_bytes, p_bytes, staging_bytes, total;
+  uint32_t q_bytes, k_bytes, v_bytes, set_bytes, staging_bufs, staging_bytes, total;
 };
+constexpr int kAttnSoftmaxWarps = 8;                         // two groups of four
+constexpr int kAttnThreads = 64 + 32 * kAttnSoftmaxWarps;
+constexpr uint32_t kAttnSmemLimit = 232448u;                 // 227 KiB per CTA
+constexpr int kAttnMaxSets = 4;                              // Q/K/V sets in flight per CTA
 __host__ __device__ inline AttnSmem attn_smem_plan(int d, int tk_pad, int nsets) {
   AttnSmem s;
   const uint32_t kb = static_cast<uint32_t>(d / 32);
@@ -49,9 +55,15 @@ __host__ __device__ inline AttnSmem attn_smem_plan(int d, int tk_pad, int nsets)
   s.k_bytes = kb * static_cast<uint32_t>(tk_pad) * 128u;     // [d/32][tk_pad rows][128 B]
   s.v_bytes = kb * static_cast<uint32_t>(tk_pad) * 128u;     // [d/32 chunks][tk_pad rows][128 B]
   s.set_bytes = s.q_bytes + s.k_bytes + s.v_bytes;
-  s.p_bytes = static_cast<uint32_t>(tk_pad / 32) * 128u * 128u;   // [tk_pad/32][128 rows][128 B]
-  s.staging_bytes = 4u * 2u * 4096u;
-  s.total = 1024u + static_cast<uint32_t>(nsets) * s.set_bytes + s.p_bytes + s.staging_bytes + 256u;
+  // one 32x32 output staging tile per softmax warp, two when they fit
+  s.staging_bufs = 2u;
+  s.staging_bytes = kAttnSoftmaxWarps * s.staging_bufs * 4096u;
+  s.total = 1024u + static_cast<uint32_t>(nsets) * s.set_bytes + s.staging_bytes + 256u;
+  if (s.total > kAttnSmemLimit) {
+    s.staging_bufs = 1u;
+    s.staging_bytes = kAttnSoftmaxWarps * 4096u;
+    s.total = 1024u + static_cast<uint32_t>(nsets) * s.set_bytes + s.staging_bytes + 256u;
+  }
   return s;
 }
 
@@ -74,7 +86,7 @@ __device__ __forceinline__ bool attn_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                       const AttnParams p) {
@@ -85,32 +97,32 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int lane = threadIdx.x & 31;
 
   const AttnSmem sm = attn_smem_plan(p.d, p.tk_pad, p.nsets);
-  const uint32_t p_base = smem_base + static_cast<uint32_t>(p.nsets) * sm.set_bytes;
-  const uint32_t staging_base = p_base + sm.p_bytes;
+  const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.nsets) * sm.set_bytes;
   const uint32_t bar_base = staging_base + sm.staging_bytes;
-  // barriers: full[2] @0, empty[2] @16, s_full[2] @32, s_empty[2] @48, p_full @64, p_empty @72,
-  //           o_full @80, o_empty @88 | tmem slot @96 | abort @104
+  // barriers (8 bytes each): full[4] @0, empty[4] @32, s_full[2] @64, p_full[2] @80,
+  //                          o_full[2] @96, o_free[2] @112 | tmem slot @128 | abort @136
   auto full_bar = [&](int b) { return bar_base + 8u * b; };
-  auto empty_bar = [&](int b) { return bar_base + 16u + 8u * b; };
-  auto s_full = [&](int b) { return bar_base + 32u + 8u * b; };
-  auto s_empty = [&](int b) { return bar_base + 48u + 8u * b; };
-  const uint32_t p_full = bar_base + 64u, p_empty = bar_base + 72u, o_full = bar_base + 80u,
-                 o_empty = bar_base + 88u;
-  const uint32_t tmem_slot = bar_base + 96u;
+  auto empty_bar = [&](int b) { return bar_base + 32u + 8u * b; };
+  auto s_full = [&](int b) { return bar_base + 64u + 8u * b; };
+  auto p_full = [&](int b) { return bar_base + 80u + 8u * b; };
+  auto o_full = [&](int b) { return bar_base + 96u + 8u * b; };
+  auto o_free = [&](int b) { return bar_base + 112u + 8u * b; };
+  const uint32_t tmem_slot = bar_base + 128u;
   uint8_t* bar_gen = smem_gen + (bar_base - smem_base);
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(bar_gen + 96);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 104);
-  // With two operand sets in shared memory and room for two score tiles in TMEM, the scores of
-  // unit i+1 are computed while unit i is still in its softmax / second product.
-  const bool dbl = (p.nsets == 2) && (2 * p.tk_pad <= 256);
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(bar_gen + 128);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 136);
+  // Two score tiles when they fit beside the two output tiles in TMEM and two operand sets fit in
+  // shared memory; otherwise one score tile and the two products of a unit run back to back.
+  const bool dbl = (p.nsets >= 2) && (2 * p.tk_pad <= 256);
 
   if (threadIdx.x == 0) {
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kAttnMaxSets; ++b) {
       ptx::mbar_init(full_bar(b), 1); ptx::mbar_init(empty_bar(b), 1);
-      ptx::mbar_init(s_full(b), 1);   ptx::mbar_init(s_empty(b), 4);
     }
-    ptx::mbar_init(p_full, 4);  ptx::mbar_init(p_empty, 1);
-    ptx::mbar_init(o_full, 1);  ptx::mbar_init(o_empty, 4);
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(s_full(b), 1);   ptx::mbar_init(p_full(b), 4);
+      ptx::mbar_init(o_full(b), 1);   ptx::mbar_init(o_free(b), 4);
+    }
     *abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_smem();
@@ -125,21 +137,30 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
-  // score tiles at columns [0, tk_pad) and, when doubled, [tk_pad, 2 tk_pad); O at [256, 256 + d)
+  // score / probability tiles at columns [0, tk_pad) and [tk_pad, 2 tk_pad); O tiles at 256 + b*d
   auto tmem_s = [&](int b) { return tmem_base + static_cast<uint32_t>(b * p.tk_pad); };
-  const uint32_t tmem_o = tmem_base + 256u;
+  auto tmem_o = [&](int b) { return tmem_base + 256u + static_cast<uint32_t>(b * p.d); };
   const int kblocks = p.d / 32;
+  const int n_units = (p.total_units - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                      static_cast<int>(gridDim.x);
+  // Where this CTA's i-th unit lives.  The s_full / p_full / o_full / o_free barriers and the O
+  // tile are indexed by i & 1 with phase (i >> 1) & 1, so that each softmax group waits only on
+  // its own barriers and is never more than one phase behind them.  Nothing guards the reuse of a
+  // score tile by a later Q.K^T: the tensor core runs one thread's MMAs in issue order, so that
+  // product follows the P.V that read the tile.
+  auto tile_of = [&](int i) { return dbl ? (i & 1) : 0; };
+  auto set_of = [&](int i) { return i % p.nsets; };
+  auto set_phase = [&](int i) { return static_cast<uint32_t>(i / p.nsets) & 1u; };
+  auto out_phase = [&](int i) { return static_cast<uint32_t>(i >> 1) & 1u; };
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer ---
     if (lane == 0) {
-      int buf = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+      for (int i = 0; i < n_units; ++i) {
+        const int u = blockIdx.x + i * gridDim.x;
         const int head = u / p.q_tiles, qt = u - head * p.q_tiles;
-        ok = attn_wait(empty_bar(buf), phase ^ 1u, abort_flag, p, kStatusAttnProducer);
-        if (!ok) break;
+        const int buf = set_of(i);
+        if (!attn_wait(empty_bar(buf), set_phase(i) ^ 1u, abort_flag, p, kStatusAttnProducer)) break;
         const uint32_t sq = smem_base + buf * sm.set_bytes;
         const uint32_t sk = sq + sm.q_bytes;
         const uint32_t sv = sk + sm.k_bytes;
@@ -150,27 +171,20 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ptx::tma_load_3d(sk + kb * p.tk_pad * 128u, &tmK, fb, kb * 32, 0, head);
           ptx::tma_load_3d(sv + kb * p.tk_pad * 128u, &tmV, fb, kb * 32, 0, head);
         }
-        if (++buf == p.nsets) { buf = 0; phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------- MMA issuer ---
     if (lane == 0) {
       const uint32_t idesc_s = ptx::idesc_tf32(128, p.tk_pad, 0, 0);     // Q, K both K-major
-      const uint32_t idesc_o = ptx::idesc_tf32(128, p.d, 0, 1);          // P K-major, V MN-major
-      const int n_units = (p.total_units - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                          static_cast<int>(gridDim.x);
+      const uint32_t idesc_o = ptx::idesc_tf32(128, p.d, 0, 1);          // P from TMEM, V MN-major
       bool ok = true;
-      // S(i) = Q.K^T of this CTA's i-th unit into score tile i & 1 (or tile 0 when not doubled)
+      // S(i) = Q.K^T of this CTA's i-th unit into its score tile
       auto issue_scores = [&](int i) {
-        const int buf = i % p.nsets;
-        const uint32_t set_phase = static_cast<uint32_t>(i / p.nsets) & 1u;
-        const int sb = dbl ? (i & 1) : 0;
-        const uint32_t s_phase = static_cast<uint32_t>(dbl ? (i >> 1) : i) & 1u;
+        const int buf = set_of(i), sb = tile_of(i);
         const uint32_t sq = smem_base + buf * sm.set_bytes;
         const uint32_t sk = sq + sm.q_bytes;
-        ok = attn_wait(full_bar(buf), set_phase, abort_flag, p, kStatusAttnMma);
-        if (ok) ok = attn_wait(s_empty(sb), s_phase ^ 1u, abort_flag, p, kStatusAttnMma);
+        ok = attn_wait(full_bar(buf), set_phase(i), abort_flag, p, kStatusAttnMma);
         if (!ok) return;
         ptx::tc_fence_after_sync();
         uint32_t acc = 0u;
@@ -182,80 +196,69 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             ptx::mma_tf32_1cta(tmem_s(sb), da, db, idesc_s, acc);
             acc = 1u;
           }
-        ptx::mma_commit_1cta(s_full(sb));
+        ptx::mma_commit_1cta(s_full(i & 1));
       };
       if (n_units > 0) issue_scores(0);
       int issued = 0;                                          // last unit whose scores are issued
       for (int i = 0; i < n_units && ok; ++i) {
-        // Early start of the next unit's scores (they then run under unit i's softmax), but only
-        // if its operands have already landed: waiting here would hold back unit i's P.V.
-        if (dbl && i + 1 < n_units && issued == i) {
-          const int nb = (i + 1) % p.nsets;
-          const uint32_t nphase = static_cast<uint32_t>((i + 1) / p.nsets) & 1u;
-          if (ptx::mbar_test_wait(full_bar(nb), nphase)) { issue_scores(i + 1); issued = i + 1; }
+        // Early start of the next unit's scores into the other tile, but only if its operands
+        // have already landed: blocking here would hold back unit i's second product.
+        if (dbl && i + 1 < n_units && issued == i &&
+            ptx::mbar_test_wait(full_bar(set_of(i + 1)), set_phase(i + 1))) {
+          issue_scores(i + 1);
+          issued = i + 1;
         }
         if (!ok) break;
-        const int buf = i % p.nsets;
-        const uint32_t tphase = static_cast<uint32_t>(i) & 1u;
+        const int buf = set_of(i), sb = tile_of(i), ob = i & 1;
         const uint32_t sv = smem_base + buf * sm.set_bytes + sm.q_bytes + sm.k_bytes;
-        // second product once the probabilities are in shared memory
-        ok = attn_wait(p_full, tphase, abort_flag, p, kStatusAttnMma);
-        if (ok) ok = attn_wait(o_empty, tphase ^ 1u, abort_flag, p, kStatusAttnMma);
+        // O(i) = P(i) . V once the probabilities are in TMEM and that O tile has been drained
+        ok = attn_wait(p_full(ob), out_phase(i), abort_flag, p, kStatusAttnMma);
+        if (ok) ok = attn_wait(o_free(ob), out_phase(i) ^ 1u, abort_flag, p, kStatusAttnMma);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         uint32_t acc = 0u;
         for (int ks = 0; ks < p.tk_pad / 8; ++ks) {
-          const uint64_t da = ptx::smem_desc_sw128(p_base + (ks >> 2) * 16384u + (ks & 3) * 32u, 16u, 1024u);
           const uint64_t db = ptx::smem_desc_sw128(sv + ks * 1024u, p.tk_pad * 128u, 512u,
                                                    ptx::kLayoutSw128Base32);
-          ptx::mma_tf32_1cta(tmem_o, da, db, idesc_o, acc);
+          ptx::mma_tf32_1cta_ts(tmem_o(ob), tmem_s(sb) + ks * 8, db, idesc_o, acc);
           acc = 1u;
         }
-        ptx::mma_commit_1cta(o_full);
-        ptx::mma_commit_1cta(p_empty);
-        ptx::mma_commit_1cta(empty_bar(buf));
+        ptx::mma_commit_1cta(o_full(ob));
+        ptx::mma_commit_1cta(empty_bar(buf));        // the operand set may be refilled
         if (i + 1 < n_units && issued == i) { issue_scores(i + 1); issued = i + 1; }
       }
     }
   } else {
     // ------------------------------------------------- softmax + output warps ---
+    // Two groups of four warps; group g takes this CTA's units g, g+2, ...  A warp may touch the
+    // TMEM lane quarter (warp index mod 4) only, so each group covers all 128 rows.
+    const int group = (warp - 2) >> 2;
     const int q = warp & 3;
-    const uint32_t staging = staging_base + (warp - kEpilogueWarp0) * 8192u;
+    const uint32_t nbufs = sm.staging_bufs;
+    const uint32_t staging = staging_base + (warp - 2) * nbufs * 4096u;
     uint8_t* staging_gen = smem_gen + (staging - smem_base);
-    uint8_t* p_gen = smem_gen + (p_base - smem_base);
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     const int row_in_tile = q * 32 + lane;
-    int sbuf = 0;
-    bool ok = true;
     const float sl2 = p.scale * 1.4426950408889634f;            // scale * log2(e)
     const int nchunks = p.tk_pad / 32;
-    int i = 0;                                                   // this CTA's unit counter
-    for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x, ++i) {
-      const int head = u / p.q_tiles, qt = u - head * p.q_tiles;
+    int sbuf = 0;
+    bool ok = true;
+
+    // One thread owns one query row.  e = 2^(scale*log2e*(s - max)) over the visible keys
+    // replaces the scores in TMEM, unnormalised; the row sum divides the output instead.
+    // ex2.approx is good to 2^-22, far inside TF32 rounding.  Returns 1 / row sum.
+    auto softmax_unit = [&](int i) -> float {
+      const int u = blockIdx.x + i * gridDim.x;
+      const int qt = u % p.q_tiles;
       const int qi = qt * 128 + row_in_tile;                     // query index in the sequence
-      // keys this row may see: j < tk and (not causal or j <= qi)
-      const int jmax = p.causal ? min(p.tk, qi + 1) : p.tk;
-      const uint32_t tphase = static_cast<uint32_t>(i) & 1u;
-      const int sb = dbl ? (i & 1) : 0;
-      const uint32_t s_phase = static_cast<uint32_t>(dbl ? (i >> 1) : i) & 1u;
+      const int jmax = p.causal ? min(p.tk, qi + 1) : p.tk;      // keys j < jmax are visible
+      const int sb = tile_of(i);
       const uint32_t ts = tmem_s(sb) + lane_off;
-      ok = attn_wait(s_full(sb), s_phase, abort_flag, p, kStatusAttnSoftmax);
+      ok = attn_wait(s_full(i & 1), out_phase(i), abort_flag, p, kStatusAttnSoftmax);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!ok) return 0.0f;
       ptx::tc_fence_after_sync();
-      // One thread owns one query row.  e = 2^(scale*log2e*(s - max)) over the visible keys goes
-      // to shared memory unnormalised (K-major, 128B-swizzled: the A operand of P.V); the row
-      // sum divides the output instead.  ex2.approx is good to 2^-22, far inside TF32 rounding.
-      auto store_p = [&](int c, const float (&e)[32]) {
-        uint8_t* dst = p_gen + c * 16384 + row_in_tile * 128;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<float4*>(dst + ((j ^ (row_in_tile & 7)) << 4)) =
-              make_float4(e[4 * j], e[4 * j + 1], e[4 * j + 2], e[4 * j + 3]);
-      };
-      float sum = 0.0f;
-      {
-      // pass 1 finds the row maximum, pass 2 re-reads the scores from TMEM for the exponentials
+      // pass 1 finds the row maximum, pass 2 re-reads the scores for the exponentials
       float mx = -INFINITY;
       for (int c = 0; c < nchunks; ++c) {
         uint32_t r[32];
@@ -266,40 +269,44 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           if (c * 32 + j < jmax) mx = fmaxf(mx, __uint_as_float(r[j]));
       }
       const float mx2 = (jmax > 0) ? mx * sl2 : 0.0f;
-      ok = attn_wait(p_empty, tphase ^ 1u, abort_flag, p, kStatusAttnSoftmax);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      float sum = 0.0f;
       for (int c = 0; c < nchunks; ++c) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(ts + c * 32, r);
         ptx::tmem_ld_wait();
-        float e[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const float x = ptx::ex2_approx(fmaf(__uint_as_float(r[j]), sl2, -mx2));
-          e[j] = (c * 32 + j < jmax) ? x : 0.0f;
-          sum += e[j];
+          const float e = (c * 32 + j < jmax) ? x : 0.0f;
+          sum += e;
+          r[j] = __float_as_uint(e);
         }
-        store_p(c, e);
+        ptx::tmem_st_32x32(ts + c * 32, r);
       }
-      }
+      ptx::tmem_st_wait();                            // P is in TMEM before the tensor core is told
       ptx::tc_fence_before_sync();
-      ptx::fence_proxy_async_smem();                 // P visible to the tensor core
       __syncwarp();
-      if (lane == 0) { ptx::mbar_arrive(s_empty(sb)); ptx::mbar_arrive(p_full); }
-      const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
-      // output: O / row sum
-      ok = attn_wait(o_full, tphase, abort_flag, p, kStatusAttnSoftmax);
+      if (lane == 0) ptx::mbar_arrive(p_full(i & 1));
+      return sum > 0.0f ? 1.0f / sum : 0.0f;
+    };
+    // output of unit i: O / row sum through the staging tile
+    auto output_unit = [&](int i, float inv) {
+      const int u = blockIdx.x + i * gridDim.x;
+      const int head = u / p.q_tiles, qt = u - head * p.q_tiles;
+      const int ob = i & 1;
+      ok = attn_wait(o_full(ob), out_phase(i), abort_flag, p, kStatusAttnSoftmax);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!ok) return;
       ptx::tc_fence_after_sync();
       const int m0 = qt * 128 + q * 32;
       for (int c = 0; c < p.d / 32; ++c) {
         uint32_t r[32];
-        ptx::tmem_ld_32x32(tmem_o + lane_off + c * 32, r);
+        ptx::tmem_ld_32x32(tmem_o(ob) + lane_off + c * 32, r);
         ptx::tmem_ld_wait();
         if (m0 >= p.tq) continue;
-        if (lane == 0) ptx::tma_store_wait_read<1>();
+        if (lane == 0) {                      // the staging tile about to be overwritten is read
+          if (nbufs == 2) ptx::tma_store_wait_read<1>(); else ptx::tma_store_wait_read<0>();
+        }
         __syncwarp();
         uint8_t* dst = staging_gen + sbuf * 4096 + lane * 128;
 #pragma unroll
@@ -313,11 +320,19 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ptx::tma_store_3d(&tmO, staging + sbuf * 4096, c * 32, m0, head);
           ptx::tma_store_commit();
         }
-        sbuf ^= 1;
+        if (nbufs == 2) sbuf ^= 1;
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(o_empty);
+      if (lane == 0) ptx::mbar_arrive(o_free(ob));
+    };
+
+    // While this group waits for and writes out O(i), the other group runs the softmax of
+    // unit i+1 and the tensor core the products around it.
+    for (int i = group; i < n_units && ok; i += 2) {
+      const float inv = softmax_unit(i);
+      if (!ok) break;
+      output_unit(i, inv);
     }
     if (lane == 0) ptx::tma_store_wait_all<0>();
   }

@@ -606,12 +606,11 @@ extern "C" int fastnn_b200_attention_forward(const float* q, const float* k, con
   if ((head_dim % 32) != 0 || head_dim > 128 || t_k > 256 || !(scale > 0.0f)) return -1;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return -1;
   const int tk_pad = ceil_div(t_k, 32) * 32;
-  int nsets = 2;                                   // double-buffer Q/K/V across units if it fits
+  // Q/K/V sets in flight per CTA: a set is held from its load until P.V has read V, so the loads
+  // of later units need sets of their own to run ahead; as many as fit, up to four.
+  int nsets = fnn::kAttnMaxSets;
   fnn::AttnSmem plan = fnn::attn_smem_plan(head_dim, tk_pad, nsets);
-  if (plan.total > kMaxDynSmem) {
-    nsets = 1;
-    plan = fnn::attn_smem_plan(head_dim, tk_pad, nsets);
-  }
+  while (plan.total > kMaxDynSmem && nsets > 1) plan = fnn::attn_smem_plan(head_dim, tk_pad, --nsets);
   if (plan.total > kMaxDynSmem) return -1;
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState* st = current_state();
@@ -642,7 +641,7 @@ extern "C" int fastnn_b200_attention_forward(const float* q, const float* k, con
   ok = ok && encode_map(&tmO, o, D, t_q, H, D * 4ull, D * 4ull * t_q, 32, 32);
   if (!ok) return -1;
   const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
-  fnn::attention_tf32_kernel<<<grid, fnn::kNumThreads, plan.total, static_cast<cudaStream_t>(stream)>>>(
+  fnn::attention_tf32_kernel<<<grid, fnn::kAttnThreads, plan.total, static_cast<cudaStream_t>(stream)>>>(
       tmQ, tmK, tmV, tmO, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   FNN_CUDA_OK(cudaGetLastError());

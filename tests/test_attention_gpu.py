@@ -39,6 +39,8 @@ def _check(got, want, tk, v, what):
     (2, 96, 64, 64),        # two 32-wide head-dim blocks
     (1, 40, 8, 32),         # t_k smaller than one block
     (5, 130, 96, 96),
+    (2, 128, 256, 64),      # longest key range: one score tile fills half of TMEM
+    (300, 128, 128, 32),    # more units than SMs: the per-CTA pipeline runs several deep
 ])
 def test_fused_attention_matches_reference_composition(gpu, shape, causal):
     f = gpu
