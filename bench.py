@@ -162,6 +162,8 @@ def run_ours(args, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     f.cuda_init(local_rank)
+    if args.policy:
+        f.set_policy(args.policy, 0, 0)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     scale = (1.0 / world) if (args.scaling == "strong" and world > 1) else 1.0
@@ -230,10 +232,13 @@ def run_ours(args, rank, world, local_rank):
 
     # per-GEMM device time (own events, after the headline region) for the roofline entry
     per_gemm = []
+    kernel_names = []
     for op in ops:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         reps = max(3, min(20, args.steps))
         launch(*op)
+        kernel_names.append({1: "gemm_simt_kernel", 2: "gemm_tf32_kernel",
+                             3: "gemm_tf32_pair_kernel"}.get(f.last_path()["path"], "?"))
         torch.cuda.synchronize()
         e0.record()
         for _ in range(reps):
@@ -358,13 +363,13 @@ def run_ours(args, rank, world, local_rank):
         ach = gemm_bytes(ts) / (top_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": ach / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth"}
-    roof["kernel"] = "gemm_tf32_kernel"
+    roof["kernel"] = kernel_names[top]
     roof["gemm"] = ("all launches of the step" if same_work else
                     f"{ts['label']} m{ts['m']} n{ts['n']} k{ts['k']} b{ts['batch']}")
     roof["ms_per_launch"] = top_ms
     roof["timing"] = ("timed region / launches" if same_work else
                       ("graph replay of that GEMM" if per_gemm_graph else "back-to-back launches of that GEMM"))
-    roof["traffic"] = TRAFFIC_BYTES.get((args.workload, ts["label"]))
+    roof["traffic"] = traffic_for(args.workload, kernel_names, [s["label"] for s in spec], same_work, top)
 
     line = {
         "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
@@ -397,13 +402,31 @@ def run_ours(args, rank, world, local_rank):
 
 
 # ncu-measured DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum, bytes) of
-# gemm_tf32_kernel, from the captures summarised in profiles/; keyed by (workload, GEMM label)
+# the GEMM kernels, from the captures summarised in profiles/; keyed by (workload, kernel, GEMM label)
 TRAFFIC_BYTES = {
-    ("square8192", "NN"): 2.278e9 + 0.255e9, ("square8192", "NT"): 2.278e9 + 0.253e9,
-    ("square8192", "TN"): 2.278e9 + 0.252e9,
-    ("square4096", "NN"): 2.94e8 + 0.50e8, ("square4096", "NT"): 2.96e8 + 0.46e8,
-    ("square4096", "TN"): 2.94e8 + 0.47e8,
+    ("square8192", "gemm_tf32_kernel", "NN"): 2.278e9 + 0.255e9,
+    ("square8192", "gemm_tf32_kernel", "NT"): 2.278e9 + 0.253e9,
+    ("square8192", "gemm_tf32_kernel", "TN"): 2.279e9 + 0.253e9,
+    ("square8192", "gemm_tf32_pair_kernel", "NN"): 2.280e9 + 0.255e9,
+    ("square8192", "gemm_tf32_pair_kernel", "NT"): 2.820e9 + 0.253e9,
+    ("square8192", "gemm_tf32_pair_kernel", "TN"): 2.281e9 + 0.252e9,
+    ("square4096", "gemm_tf32_pair_kernel", "NN"): 2.98e8 + 0.48e8,
+    ("square4096", "gemm_tf32_pair_kernel", "NT"): 2.97e8 + 0.47e8,
+    ("square4096", "gemm_tf32_pair_kernel", "TN"): 2.98e8 + 0.48e8,
+    ("square4096", "gemm_tf32_kernel", "NN"): 2.93e8 + 0.51e8,
+    ("square4096", "gemm_tf32_kernel", "NT"): 2.95e8 + 0.53e8,
+    ("square4096", "gemm_tf32_kernel", "TN"): 2.93e8 + 0.51e8,
 }
+
+
+def traffic_for(workload, kernels, labels, same_work, top):
+    """DRAM bytes per launch for the roofline entry: the mean over the step's launches when the
+    entry describes all of them, else the figure of the GEMM it names; None when not captured."""
+    idx = range(len(labels)) if same_work else [top]
+    vals = [TRAFFIC_BYTES.get((workload, kernels[i], labels[i])) for i in idx]
+    if any(v is None for v in vals):
+        return None
+    return sum(vals) / len(vals)
 
 
 # -------------------------------------------------------------------- CPU reference ---
@@ -661,6 +684,8 @@ def main():
     ap.add_argument("--workload", default="square8192")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--gather", action="store_true")
+    ap.add_argument("--policy", type=int, default=0,
+                    help="kernel choice for sweeps: 0 planner, 3 single CTAs only, 4 CTA pairs only")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)

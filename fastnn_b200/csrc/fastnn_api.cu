@@ -161,14 +161,17 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
       for (int s : splits) {
         if (s > 1 && num_kb / s < 2) break;
         const int kbps = ceil_div(num_kb, s);
-        // measured at 8192^3: a CTA pair with 256-wide tiles and two k-blocks per stage is ~5 %
-        // faster than single CTAs for a few launches, equal after ~0.2 s and ~8 % slower once the
-        // power cap has pulled the clock down (long runs) -- so single CTAs are the default and
-        // pairs are taken only on request (policy 4)
-        const double t_kb_scale = !pair ? 1.0 : ((bn == 256 && kbps >= 8) ? 1.05 : 1.12);
         const int real_split = ceil_div(num_kb, kbps);
         const long long units = 1ll * batch * tiles_m * tiles_n * real_split;
         const double waves = static_cast<double>((units + slots - 1) / slots);
+        // measured with hinted operand loads: a CTA pair with 256-wide tiles and two k-blocks per
+        // stage is 3-5 % faster than single CTAs in a burst (4096^3, 8192^3) and 1-3 % faster over
+        // 0.3 s and longer runs of 8192^3, but 3-5 % slower on 32768 x 16384 x 4096 under the power
+        // cap: its per-tile hand-over between the two CTAs costs more, its per-stage saving grows
+        // with K.  So the deepest problems (K >= 8192, many waves) take pairs, the rest single CTAs.
+        const double t_kb_scale =
+            !pair ? 1.0 : ((bn == 256 && kbps >= 256 && waves >= 4.0) ? 0.97
+                                                                       : ((bn == 256 && kbps >= 8) ? 1.05 : 1.12));
         // HBM time is stretched by idle SMs: a wave that fills only part of the machine still
         // takes a full wave
         const double imbalance = waves * slots * (pair ? 2 : 1) / ((pair ? 2.0 : 1.0) * units);
@@ -295,6 +298,21 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   p.alpha = g.alpha; p.beta = g.beta; p.bias = g.bias; p.act = g.act;
   p.status = st->status;
   p.spin_budget = st->spin_budget;
+  p.group_m = plan.pair ? fnn::kGroupM / 2 : fnn::kGroupM;     // 2048 rows of C either way
+  // Operand loads carry the evict-unchanged L2 policy.  A load with the default policy also
+  // demotes the line it hits, a second tag operation per sector: with the hint the L2 answers the
+  // same 24x-operand-bytes of tile reads with half the lookups (ncu at 4096^3: lts__throughput
+  // 61 % -> 34 %, cross-partition requests 15.3 M -> 4.5 M, DRAM bytes unchanged).  Measured at
+  // 8192^3 on single CTAs: +10 % in a burst, +19 % sustained under the power cap.
+  p.l2_a = 3; p.l2_b = 3; p.l2_c = 0;
+  if (const char* e = std::getenv("FASTNN_B200_GROUP_M")) {
+    const int v = std::atoi(e);
+    if (v >= 1 && v <= 1024) p.group_m = v;
+  }
+  if (const char* e = std::getenv("FASTNN_B200_L2")) {          // digits: C, A, B policy
+    const int v = std::atoi(e);
+    p.l2_c = (v / 100) % 10 % 5; p.l2_a = (v / 10) % 10 % 5; p.l2_b = v % 10 % 5;
+  }
 
   // output target: C itself, or the split-K workspace
   float* out = g.c;
@@ -828,6 +846,7 @@ extern "C" int fastnn_b200_gemm_splitk_static(int layout, const float* a, const 
   p.status = st->status;
   p.spin_budget = st->spin_budget;
   p.store_mode = 0;
+  p.group_m = fnn::kGroupM;
   p.c = st->scratch; p.ldc = n; p.c_batch_stride = 1ll * m * n;
   // With alpha = 1, beta = 0 and no bias the kernel's epilogue is the identity, so a single
   // split also lands in the scratch unchanged and the reduce pass copies it to C.

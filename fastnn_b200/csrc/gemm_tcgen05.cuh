@@ -66,6 +66,9 @@ struct GemmParams {
   int a_chunked;       // MN-major A through a 4-D map (32, k, m/32, batch): one box per stage
   int b_chunked;       // same for B; needs the M (N) extent to be a multiple of 32
   int store_mode;      // 0: TMA store through tmC, 1: predicated global stores
+  int group_m;         // tile rows per rasterisation group (>= 1)
+  int l2_a, l2_b;      // L2 eviction policy of the A / B loads (kinds of ptx::make_l2_policy)
+  int l2_c;            // and of the TMA stores of C
   float alpha, beta;
   const float* bias;   // [n] or null (ignored when split_k > 1: applied by the reduce pass)
   int act;
@@ -86,10 +89,10 @@ __device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u) {
   const int tiles = p.tiles_m * p.tiles_n;
   w.b = t / tiles;
   t -= w.b * tiles;
-  const int group_sz = kGroupM * p.tiles_n;
+  const int group_sz = p.group_m * p.tiles_n;
   const int g = t / group_sz;
-  const int first_m = g * kGroupM;
-  const int gm = min(p.tiles_m - first_m, kGroupM);
+  const int first_m = g * p.group_m;
+  const int gm = min(p.tiles_m - first_m, p.group_m);
   const int r = t - g * group_sz;
   w.mt = first_m + r % gm;
   w.nt = r / gm;
@@ -176,7 +179,9 @@ __device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const C
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
+        if (p.l2_c != 0) ptx::tma_store_3d_hint(tmC, staging + buf * 4096, col0, m0, cz,
+                                                 ptx::make_l2_policy(p.l2_c));
+        else ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
         ptx::tma_store_commit();
       }
       buf ^= 1;
@@ -246,6 +251,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint64_t pol_a = ptx::make_l2_policy(p.l2_a);
+      const uint64_t pol_b = ptx::make_l2_policy(p.l2_b);
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         const Unit w = decode_unit(p, u);
         const int m0 = w.mt * kBlockM;
@@ -261,21 +268,21 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           ptx::mbar_expect_tx(fb, stage_bytes);
           const int k0 = kb * kBlockK;
           if (!p.a_mn_major) {
-            ptx::tma_load_3d(sa, &tmA, fb, k0, m0, w.b);                       // 32 x 128 box
+            ptx::tma_load_3d_hint(sa, &tmA, fb, k0, m0, w.b, pol_a);           // 32 x 128 box
           } else if (p.a_chunked) {
-            ptx::tma_load_4d(sa, &tmA, fb, 0, k0, m0 >> 5, w.b);               // 32 x 32 x 4 box
+            ptx::tma_load_4d_hint(sa, &tmA, fb, 0, k0, m0 >> 5, w.b, pol_a);   // 32 x 32 x 4 box
           } else {
 #pragma unroll
             for (int c = 0; c < kBlockM / 32; ++c)
-              ptx::tma_load_3d(sa + c * kChunkBytes, &tmA, fb, m0 + 32 * c, k0, w.b);
+              ptx::tma_load_3d_hint(sa + c * kChunkBytes, &tmA, fb, m0 + 32 * c, k0, w.b, pol_a);
           }
           if (!p.b_mn_major) {
-            ptx::tma_load_3d(sb, &tmB, fb, k0, n0, w.b);                       // 32 x block_n box
+            ptx::tma_load_3d_hint(sb, &tmB, fb, k0, n0, w.b, pol_b);           // 32 x block_n box
           } else if (p.b_chunked) {
-            ptx::tma_load_4d(sb, &tmB, fb, 0, k0, n0 >> 5, w.b);               // 32 x 32 x bn/32
+            ptx::tma_load_4d_hint(sb, &tmB, fb, 0, k0, n0 >> 5, w.b, pol_b);   // 32 x 32 x bn/32
           } else {
             for (int c = 0; c < p.block_n / 32; ++c)
-              ptx::tma_load_3d(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b);
+              ptx::tma_load_3d_hint(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b, pol_b);
           }
           if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
         }

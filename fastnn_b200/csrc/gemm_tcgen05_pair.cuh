@@ -92,6 +92,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint64_t pol_a = ptx::make_l2_policy(p.l2_a);
+      const uint64_t pol_b = ptx::make_l2_policy(p.l2_b);
       for (int u = cluster_id; u < p.total_units && ok; u += num_clusters) {
         const Unit w = decode_unit_pair(p, u);
         const int m0 = w.mt * kPairBlockM + static_cast<int>(rank) * kBlockM;
@@ -109,21 +111,21 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           const uint32_t sb = sa + kStageABytes;
           const int k0 = (kb + r) * kBlockK;
           if (!p.a_mn_major) {
-            ptx::tma_load_3d_pair(sa, &tmA, fb, k0, m0, w.b);
+            ptx::tma_load_3d_pair(sa, &tmA, fb, k0, m0, w.b, pol_a);
           } else if (p.a_chunked) {
-            ptx::tma_load_4d_pair(sa, &tmA, fb, 0, k0, m0 >> 5, w.b);
+            ptx::tma_load_4d_pair(sa, &tmA, fb, 0, k0, m0 >> 5, w.b, pol_a);
           } else {
 #pragma unroll
             for (int c = 0; c < kBlockM / 32; ++c)
-              ptx::tma_load_3d_pair(sa + c * kChunkBytes, &tmA, fb, m0 + 32 * c, k0, w.b);
+              ptx::tma_load_3d_pair(sa + c * kChunkBytes, &tmA, fb, m0 + 32 * c, k0, w.b, pol_a);
           }
           if (!p.b_mn_major) {
-            ptx::tma_load_3d_pair(sb, &tmB, fb, k0, n0, w.b);         // box 32 x (block_n / 2)
+            ptx::tma_load_3d_pair(sb, &tmB, fb, k0, n0, w.b, pol_b);  // box 32 x (block_n / 2)
           } else if (p.b_chunked) {
-            ptx::tma_load_4d_pair(sb, &tmB, fb, 0, k0, n0 >> 5, w.b);
+            ptx::tma_load_4d_pair(sb, &tmB, fb, 0, k0, n0 >> 5, w.b, pol_b);
           } else {
             for (int c = 0; c < half_n / 32; ++c)
-              ptx::tma_load_3d_pair(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b);
+              ptx::tma_load_3d_pair(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b, pol_b);
           }
           }
           if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
