@@ -156,6 +156,9 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   if (warp == 0) {
     // ------------------------------------------------------------- producer ---
     if (lane == 0) {
+      // Q is read once; K and V are read once per query tile of the head
+      const uint64_t pol_q = ptx::make_l2_policy(1);
+      const uint64_t pol_kv = ptx::make_l2_policy(p.q_tiles > 1 ? 3 : 1);
       for (int i = 0; i < n_units; ++i) {
         const int u = blockIdx.x + i * gridDim.x;
         const int head = u / p.q_tiles, qt = u - head * p.q_tiles;
@@ -167,9 +170,9 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint32_t fb = full_bar(buf);
         ptx::mbar_expect_tx(fb, sm.set_bytes);
         for (int kb = 0; kb < kblocks; ++kb) {
-          ptx::tma_load_3d(sq + kb * 16384u, &tmQ, fb, kb * 32, qt * 128, head);
-          ptx::tma_load_3d(sk + kb * p.tk_pad * 128u, &tmK, fb, kb * 32, 0, head);
-          ptx::tma_load_3d(sv + kb * p.tk_pad * 128u, &tmV, fb, kb * 32, 0, head);
+          ptx::tma_load_3d_hint(sq + kb * 16384u, &tmQ, fb, kb * 32, qt * 128, head, pol_q);
+          ptx::tma_load_3d_hint(sk + kb * p.tk_pad * 128u, &tmK, fb, kb * 32, 0, head, pol_kv);
+          ptx::tma_load_3d_hint(sv + kb * p.tk_pad * 128u, &tmV, fb, kb * 32, 0, head, pol_kv);
         }
       }
     }

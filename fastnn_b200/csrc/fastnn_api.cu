@@ -216,6 +216,10 @@ struct GemmArgs {
   const float* bias;
   int act;
   cudaStream_t stream;
+  // backward epilogue (act 3 / 4): saved pre-activations and the optional column-sum output
+  const float* aux = nullptr;
+  long long ld_aux = 0;
+  float* colsum = nullptr;
 };
 
 bool tma_operands_ok(const GemmArgs& g) {
@@ -236,7 +240,7 @@ int launch_simt(const GemmArgs& g) {
   p.a_bs = g.sa; p.b_bs = g.sb; p.c_bs = g.sc; p.ldc = g.ldc;
   if (g.layout == FASTNN_B200_TN) { p.a_rs = 1; p.a_cs = g.lda; } else { p.a_rs = g.lda; p.a_cs = 1; }
   if (g.layout == FASTNN_B200_NT) { p.b_rs = 1; p.b_cs = g.ldb; } else { p.b_rs = g.ldb; p.b_cs = 1; }
-  p.alpha = g.alpha; p.beta = g.beta; p.act = g.act;
+  p.alpha = g.alpha; p.beta = g.beta; p.act = g.act > 2 ? 0 : g.act;
   const int gx = ceil_div(g.n, fnn::kSimtTile), gy = ceil_div(g.m, fnn::kSimtTile);
   if (gy > 65535) return -1;
   for (int b0 = 0; b0 < g.batch; b0 += 65535) {
@@ -244,6 +248,19 @@ int launch_simt(const GemmArgs& g) {
     q.a += b0 * p.a_bs; q.b += b0 * p.b_bs; q.c += b0 * p.c_bs;
     const int nb = g.batch - b0 < 65535 ? g.batch - b0 : 65535;
     fnn::gemm_simt_kernel<<<dim3(gx, gy, nb), 256, 0, g.stream>>>(q);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
+  FNN_CUDA_OK(cudaGetLastError());
+  // backward epilogue as two small passes (only batch 1 reaches here with aux / colsum set)
+  if (g.act > 2 && g.aux != nullptr) {
+    long long blocks = (1ll * g.m * g.n + 255) / 256;
+    if (blocks > 4096) blocks = 4096;
+    fnn::act_grad_inplace_kernel<<<static_cast<unsigned>(blocks), 256, 0, g.stream>>>(
+        g.c, g.aux, g.m, g.n, g.ldc, g.ld_aux, g.act);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
+  if (g.colsum != nullptr) {
+    fnn::colsum_kernel<<<ceil_div(g.n, 256), 256, 0, g.stream>>>(g.c, g.colsum, g.m, g.n, g.ldc);
     g_launches.fetch_add(1, std::memory_order_relaxed);
   }
   FNN_CUDA_OK(cudaGetLastError());
@@ -260,6 +277,9 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
                           pair_mode);
   if (pol.block_n > 0) plan.block_n = pol.block_n;
   if (pol.split_k > 0) plan.split_k = pol.split_k;
+  // the backward epilogue is not linear in the partial sums, and the column sums use the workspace
+  const bool backward = g.aux != nullptr || g.colsum != nullptr;
+  if (backward) plan.split_k = 1;
   if (plan.pair && (plan.block_n % 64) != 0) plan.block_n = ceil_div(plan.block_n, 64) * 64;
   const int num_kb = ceil_div(g.k, fnn::kBlockK);
   if (plan.split_k > num_kb) plan.split_k = num_kb;
@@ -332,6 +352,19 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     out_bs = static_cast<long long>(g.m) * g.n;
     out_z = static_cast<long long>(g.batch) * plan.split_k;
     p.bias = nullptr;
+  }
+  p.aux = g.aux; p.ld_aux = g.ld_aux;
+  const int slabs = ceil_div(g.m, 32);              // 32-row slabs of C, one partial row each
+  if (g.colsum != nullptr) {
+    const size_t need = sizeof(float) * static_cast<size_t>(slabs) * g.n;
+    Workspace& ws = st->workspaces[g.stream];
+    if (ws.bytes < need) {
+      if (ws.ptr) FNN_CUDA_OK(cudaFree(ws.ptr));
+      ws.ptr = nullptr; ws.bytes = 0;
+      FNN_CUDA_OK(cudaMalloc(&ws.ptr, need));
+      ws.bytes = need;
+    }
+    p.colsum = ws.ptr;
   }
   const bool tma_store = aligned16(out) && (out_ld & 3) == 0 && (out_z == 1 || (out_bs & 3) == 0) &&
                          (plan.split_k > 1 || g.beta == 0.0f) && out_ld < (1ll << 38) &&
@@ -417,6 +450,13 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
     FNN_CUDA_OK(cudaGetLastError());
   }
+  if (g.colsum != nullptr) {          // slab partials -> column sums, slabs added in order
+    long long blocks = ceil_div(g.n, 256);
+    fnn::splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, g.stream>>>(
+        p.colsum, g.colsum, nullptr, 1, g.n, 1, slabs, g.n, g.n, 1.0f, 0.0f, 0);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    FNN_CUDA_OK(cudaGetLastError());
+  }
   t_last = LastCall{plan.pair ? 3 : 2, plan.block_n, plan.split_k, grid};
   return 0;
 }
@@ -424,7 +464,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
 int gemm_dispatch(const GemmArgs& g) {
   if (g.layout < 0 || g.layout > 2) return -1;
   if (g.m < 0 || g.n < 0 || g.k < 0 || g.batch < 0) return -1;
-  if (g.act < 0 || g.act > 2) return -1;
+  if (g.act < 0 || g.act > 4 || (g.act > 2 && g.aux == nullptr)) return -1;
   if (g.m == 0 || g.n == 0 || g.batch == 0) return 0;          // nothing to write
   if (g.c == nullptr || (g.k > 0 && (g.a == nullptr || g.b == nullptr))) return -1;
   // leading dimensions must cover a row
@@ -611,6 +651,30 @@ extern "C" int fastnn_b200_linear_forward(int layout, const float* x, const floa
   GemmArgs g{layout, x, w, y, rows, out_features, in_features, 1, in_features, ldw, out_features,
              1ll * rows * in_features, 1ll * in_features * out_features, 1ll * rows * out_features,
              1.0f, 0.0f, bias, act, nullptr};
+  return gemm_dispatch(g);
+}
+
+extern "C" int fastnn_b200_linear_backward_input(int layout, const float* dy, const float* w,
+                                                 float* dx, int rows, int out_features,
+                                                 int in_features, int act, const float* pre,
+                                                 float* bias_grad, void* stream) {
+  if (layout != FASTNN_B200_NN && layout != FASTNN_B200_NT) return -1;
+  if (rows < 0 || out_features < 0 || in_features < 0 || act < 0 || act > 2) return -1;
+  if (act != 0 && pre == nullptr) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (rows == 0 || in_features == 0) {
+    if (bias_grad != nullptr && in_features > 0)
+      FNN_CUDA_OK(cudaMemsetAsync(bias_grad, 0, sizeof(float) * in_features, s));
+    return 0;
+  }
+  // NN takes W as Linear stores it, [out, in]; NT takes the transposed copy [in, out]
+  const long long ldw = (layout == FASTNN_B200_NN) ? in_features : out_features;
+  GemmArgs g{layout, dy, w, dx, rows, in_features, out_features, 1, out_features, ldw, in_features,
+             1ll * rows * out_features, 1ll * in_features * out_features, 1ll * rows * in_features,
+             1.0f, 0.0f, nullptr, act == 0 ? 0 : act + 2, s};
+  g.aux = act == 0 ? nullptr : pre;
+  g.ld_aux = in_features;
+  g.colsum = bias_grad;
   return gemm_dispatch(g);
 }
 

@@ -142,4 +142,26 @@ splitk_reduce_vec4_kernel(const float4* __restrict__ ws, float* __restrict__ c,
   }
 }
 
+// Backward epilogue for products that went through the SIMT kernel: c *= act'(aux) in place ...
+__global__ void __launch_bounds__(256)
+act_grad_inplace_kernel(float* __restrict__ c, const float* __restrict__ aux, int m, int n,
+                        long long ldc, long long ld_aux, int act) {
+  const long long total = static_cast<long long>(m) * n;
+  for (long long e = blockIdx.x * 256ll + threadIdx.x; e < total; e += 256ll * gridDim.x) {
+    const long long i = e / n;
+    const long long j = e - i * n;
+    c[i * ldc + j] *= apply_act_grad(aux[i * ld_aux + j], act);
+  }
+}
+
+// ... and its column sums, one thread per column, rows added in order.
+__global__ void __launch_bounds__(256)
+colsum_kernel(const float* __restrict__ c, float* __restrict__ out, int m, int n, long long ldc) {
+  const int j = blockIdx.x * 256 + threadIdx.x;
+  if (j >= n) return;
+  float s = 0.0f;
+  for (int i = 0; i < m; ++i) s += c[static_cast<long long>(i) * ldc + j];
+  out[j] = s;
+}
+
 }  // namespace fnn

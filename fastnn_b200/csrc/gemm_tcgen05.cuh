@@ -49,7 +49,10 @@ enum : unsigned int {
   kStatusMmaTmemTimeout = 0x104,
 };
 
-enum : int { kActNone = 0, kActRelu = 1, kActGelu = 2 };
+// 1, 2: forward activations.  3, 4: the output is multiplied by the activation's derivative at
+// aux[row, col] (the saved pre-activation), as FastNN's ReluBackward / GeluBackward do
+// (src/autograd/backward_ops.rs:136-160, 194-218; cuda/kernels.cu:244-252).
+enum : int { kActNone = 0, kActRelu = 1, kActGelu = 2, kActReluGrad = 3, kActGeluGrad = 4 };
 
 struct GemmParams {
   int m, n, k, batch;
@@ -72,6 +75,10 @@ struct GemmParams {
   float alpha, beta;
   const float* bias;   // [n] or null (ignored when split_k > 1: applied by the reduce pass)
   int act;
+  const float* aux;    // [m, n] pre-activations for act 3 / 4, row stride ld_aux
+  long long ld_aux;
+  float* colsum;       // null, or [ceil(m/32)][n] partial column sums of the output, one row per
+                       // 32-row slab (added up in slab order by a second kernel)
   float* c;            // direct-store target
   long long ldc, c_batch_stride;   // elements
   unsigned int* status;
@@ -103,6 +110,14 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   if (act == kActRelu) return fmaxf(x, 0.0f);
   if (act == kActGelu) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
   return x;
+}
+
+// d act / dx at the saved pre-activation x: 1 or 0 for ReLU; Phi(x) + x phi(x) for erf-GELU.
+__device__ __forceinline__ float apply_act_grad(float x, int act) {
+  if (act == kActReluGrad) return x > 0.0f ? 1.0f : 0.0f;
+  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752440f));
+  const float pdf = expf(-0.5f * x * x) * 0.3989422804014327f;
+  return cdf + x * pdf;
 }
 
 // Bounded wait.  Returns false when the CTA is aborting (this role's budget ran out, or
@@ -161,31 +176,67 @@ __device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const C
         for (int j = 0; j < 32; ++j)
           if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
       }
-      if (p.act != kActNone) {
+      if (p.act == kActRelu || p.act == kActGelu) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+      } else if (p.act == kActReluGrad || p.act == kActGeluGrad) {
+        const float* arow = p.aux + static_cast<long long>(row) * p.ld_aux + col0;
+        const bool vec = row < p.m && col0 + 32 <= p.n && (p.ld_aux & 3) == 0 &&
+                         (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0;
+        float x[32];
+        if (vec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(arow) + j);
+            x[4 * j] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            x[j] = (row < p.m && col0 + j < p.n) ? __ldg(arow + j) : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= apply_act_grad(x[j], p.act);
       }
     }
-    if (p.store_mode == 0) {
+    const bool want_colsum = p.colsum != nullptr && !raw;
+    if (want_colsum && row >= p.m) {               // rows past the end add nothing to a column
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+    }
+    if (p.store_mode == 0 || want_colsum) {
       // staging tile: 32 rows x 128 B, 16-byte chunk j of row r at chunk (j ^ (r & 7))
       if (lane == 0) ptx::tma_store_wait_read<1>();   // the tile used two stores ago is free
       __syncwarp();
-      uint8_t* dst_row = staging_gen + buf * 4096 + lane * 128;
+      uint8_t* tile = staging_gen + buf * 4096;
+      uint8_t* dst_row = tile + lane * 128;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float4 f = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         *reinterpret_cast<float4*>(dst_row + ((j ^ (lane & 7)) << 4)) = f;
       }
-      ptx::fence_proxy_async_smem();
+      if (p.store_mode == 0) ptx::fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
+      if (p.store_mode == 0 && lane == 0) {
         if (p.l2_c != 0) ptx::tma_store_3d_hint(tmC, staging + buf * 4096, col0, m0, cz,
                                                  ptx::make_l2_policy(p.l2_c));
         else ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
         ptx::tma_store_commit();
       }
+      if (want_colsum) {
+        // lane j adds up column j of the tile over its 32 rows in row order (no bank conflicts:
+        // the swizzle spreads one row's columns over all banks)
+        float s = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 32; ++r)
+          s += *reinterpret_cast<const float*>(tile + r * 128 + (((lane >> 2) ^ (r & 7)) << 4) +
+                                               ((lane & 3) << 2));
+        if (col0 + lane < p.n)
+          p.colsum[static_cast<long long>(m0 >> 5) * p.n + col0 + lane] = s;
+      }
       buf ^= 1;
-    } else if (row < p.m) {
+    }
+    if (p.store_mode != 0 && row < p.m) {
       float* crow = p.c + static_cast<long long>(cz) * p.c_batch_stride +
                     static_cast<long long>(row) * p.ldc;
 #pragma unroll

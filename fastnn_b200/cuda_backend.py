@@ -200,6 +200,37 @@ def linear_forward(x, w, bias=None, act=ACT_NONE, layout=NT, out=None):
     return y.view(*x.shape[:-1], out_f)
 
 
+def linear_backward_input(dy, w, pre=None, act=ACT_NONE, layout=NN, bias_grad=False, out=None,
+                          stream=0):
+    """dx = (dy . W) * act'(pre) and, when ``bias_grad`` is true, its sum over rows (the bias
+    gradient of the layer that produced ``pre``), in one GEMM launch: what FastNN's tape does
+    with matmul_nt + ReluBackward/GeluBackward (src/autograd/backward_ops.rs:136-160, 194-218)
+    + the row sum behind Linear's bias expand (src/nn/linear.rs:78-82).
+    layout NN: w is [out,in] as Linear stores it; NT: w is the transposed copy [in,out].
+    Returns dx, or (dx, bias_grad)."""
+    _check(dy, "dy"); _check(w, "w")
+    _ensure_ctx(dy)
+    dy2 = dy.reshape(-1, dy.shape[-1])
+    rows, out_f = int(dy2.shape[0]), int(dy2.shape[1])
+    in_f = int(w.shape[1] if layout == NN else w.shape[0])
+    if int(w.shape[0] if layout == NN else w.shape[1]) != out_f:
+        raise ValueError(f"Expected weight with {out_f} output features")
+    if act != ACT_NONE:
+        if pre is None:
+            raise ValueError("an activation derivative needs the saved pre-activation")
+        _check(pre, "pre")
+        if pre.numel() != rows * in_f:
+            raise ValueError("pre must be [rows, in_features]")
+    dx = _out((rows, in_f), dy, out)
+    db = torch.empty(in_f, dtype=torch.float32, device=dy.device) if bias_grad else None
+    if lib().fastnn_b200_linear_backward_input(layout, _ptr(dy2), _ptr(w), _ptr(dx), rows, out_f, in_f,
+                                               act, _ptr(pre if act != ACT_NONE else None), _ptr(db),
+                                               stream) != 0:
+        raise CudaError("CUDA linear_backward_input failed")
+    dx = dx.view(*dy.shape[:-1], in_f)
+    return (dx, db) if bias_grad else dx
+
+
 def gemm_ex(layout, a_ptr, b_ptr, c_ptr, m, n, k, batch, lda, ldb, ldc, sa, sb, sc,
             alpha=1.0, beta=0.0, bias_ptr=0, act=ACT_NONE, stream=0) -> None:
     """Raw general entry (pointers as integers, strides in elements)."""

@@ -107,6 +107,22 @@ FASTNN_B200_API int fastnn_b200_gemm_ex(int layout, const float* a, const float*
 FASTNN_B200_API int fastnn_b200_linear_forward(int layout, const float* x, const float* w, const float* bias,
                                float* y, int rows, int in_features, int out_features, int act);
 
+/* Backward of y = act(pre) . W2^T seen from the layer that produced `pre`, in one GEMM launch
+ * (plus one small reduce when bias_grad is wanted):
+ *   dx[rows,in] = ( dy[rows,out] . W ) * act'( pre[rows,in] )
+ *   bias_grad[in] = sum over rows of dx          (optional; pass NULL to skip)
+ * layout NN takes W as Linear stores it, [out,in]; layout NT takes the transposed copy [in,out]
+ * that Linear::forward materialises (src/nn/linear.rs:74) and MatmulBackward hands to matmul_nt.
+ * act: 0 none (pre may be NULL), 1 ReLU, 2 GELU(erf); the derivative is the one ReluBackward /
+ * GeluBackward apply (src/autograd/backward_ops.rs:136-160, 194-218; cuda/kernels.cu:244-252).
+ * Replaces matmul_nt + relu/gelu_backward + the sum over rows behind the bias expand
+ * (src/nn/linear.rs:78-82; FastNN's sum_axis allocates per call, cuda/kernels.cu:701-714).
+ * Rows are added in a fixed order, so bias_grad is deterministic. */
+FASTNN_B200_API int fastnn_b200_linear_backward_input(int layout, const float* dy, const float* w,
+                                                      float* dx, int rows, int out_features,
+                                                      int in_features, int act, const float* pre,
+                                                      float* bias_grad, void* stream);
+
 /* Fused attention core, per head h in [0, batch_heads):
  *   O[h] = softmax( scale * Q[h] . K[h]^T + mask ) . V[h]
  * q [batch_heads, t_q, head_dim], k and v [batch_heads, t_k, head_dim], o like q, all dense.

@@ -161,6 +161,38 @@ ORACLE_API int oracle_linear(const float* x, const float* w, const float* bias, 
 }
 
 /* ---------------------------------------------------------------------------
+ * Activation backward on CPU tensors, in place on the incoming gradient g[rows, n]:
+ *   ReluBackward (src/autograd/backward_ops.rs:152-156): g * (x > 0 ? 1 : 0)
+ *   GeluBackward (src/autograd/backward_ops.rs:208-214): g * (cdf + x * pdf) with
+ *     cdf = 0.5 (1 + erff(x / sqrt 2)), pdf = exp(-x^2 / 2) / sqrt(2 pi), all in f32
+ *     (same expression as cuda/kernels.cu:244-252).
+ * followed by the bias gradient the expand in Linear::forward (src/nn/linear.rs:78-82) implies:
+ * colsum[j] = sum over rows of g[i, j], rows added in order (sum_axis over axis 0).
+ * colsum may be null.  act: 0 none, 1 ReLU, 2 GELU.
+ * ------------------------------------------------------------------------- */
+ORACLE_API void oracle_act_backward_colsum(float* g, const float* x, float* colsum, size_t rows,
+                                           size_t n, int act) {
+  for (size_t i = 0; i < rows; ++i)
+    for (size_t j = 0; j < n; ++j) {
+      float d = 1.0f;
+      if (act == 1) d = x[i * n + j] > 0.0f ? 1.0f : 0.0f;
+      if (act == 2) {
+        const float v = x[i * n + j];
+        const float cdf = 0.5f * (1.0f + erff(v * 0.70710678118654752440f));
+        const float pdf = expf(-0.5f * v * v) * (1.0f / sqrtf(2.0f * 3.14159265358979323846f));
+        d = cdf + v * pdf;
+      }
+      g[i * n + j] = g[i * n + j] * d;
+    }
+  if (colsum)
+    for (size_t j = 0; j < n; ++j) {
+      float s = 0.0f;
+      for (size_t i = 0; i < rows; ++i) s += g[i * n + j];
+      colsum[j] = s;
+    }
+}
+
+/* ---------------------------------------------------------------------------
  * Attention probabilities used as the left operand of the batched P.V product:
  * scores*scale (src/nn/transformer.rs:94) + additive causal mask 0/-1e9
  * (src/nn/transformer.rs:22-27) -> row softmax (src/tensor/ops.rs:273-284).

@@ -14,7 +14,7 @@ from . import build_oracle as _b
 
 __all__ = [
     "rand_data", "matmul", "matmul_nt", "matmul_tn", "matmul_rows", "transpose",
-    "bias_act", "linear", "causal_softmax", "attention", "host_threads", "ACT_NONE", "ACT_RELU",
+    "bias_act", "linear", "linear_backward_input", "causal_softmax", "attention", "host_threads", "ACT_NONE", "ACT_RELU",
     "ACT_GELU", "ref_gpu_library_path",
 ]
 
@@ -179,6 +179,25 @@ def linear(x: np.ndarray, w: np.ndarray, bias, act: int = ACT_NONE) -> np.ndarra
     bp = _p(_f32(bias)) if bias is not None else ctypes.cast(None, _fp)
     assert _load().oracle_linear(_p(x), _p(w), bp, _p(y), batch, in_f, out_f, act) == 0
     return y
+
+
+def linear_backward_input(dy: np.ndarray, w: np.ndarray, pre, act: int = ACT_NONE):
+    """Gradient flowing into the previous layer's pre-activation, as FastNN's tape computes it
+    on CPU tensors: MatmulBackward's grad_a = matmul_nt(dy, W^T) for y = x . W^T
+    (i.e. dy[rows,out] . W[out,in]), then ReluBackward / GeluBackward against the saved
+    pre-activation ``pre[rows,in]``, then the row sum that is that layer's bias gradient.
+    Returns (dx[rows,in], colsum[in])."""
+    dy, w = _f32(dy), _f32(w)
+    dx = matmul(dy, w).copy()
+    rows, n = dx.shape
+    colsum = np.empty(n, dtype=np.float32)
+    lib = _load()
+    lib.oracle_act_backward_colsum.argtypes = [_fp, _fp, _fp, _sz, _sz, ctypes.c_int]
+    lib.oracle_act_backward_colsum.restype = None
+    pre32 = _f32(pre) if pre is not None else None        # kept alive across the call
+    xp = _p(pre32) if pre32 is not None else ctypes.cast(None, _fp)
+    lib.oracle_act_backward_colsum(_p(dx), xp, _p(colsum), rows, n, act if pre is not None else 0)
+    return dx, colsum
 
 
 def causal_softmax(scores: np.ndarray, scale: float) -> np.ndarray:

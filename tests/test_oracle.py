@@ -126,6 +126,28 @@ def test_linear_bias_relu_gelu():
     assert np.abs(g - want).max() < 1e-6
 
 
+def test_linear_backward_input_follows_the_tape():
+    """dx = matmul(dy, W) * act'(pre); the GELU derivative is the analytic one (checked against a
+    float64 finite difference of the forward GELU); the bias gradient is the sum over rows."""
+    from math import erf, sqrt
+    rng = np.random.default_rng(21)
+    dy = rng.standard_normal((7, 5), dtype=np.float32)
+    w = rng.standard_normal((5, 6), dtype=np.float32)
+    pre = rng.standard_normal((7, 6), dtype=np.float32)
+    base = oracle.matmul(dy, w)
+    dx, db = oracle.linear_backward_input(dy, w, None, oracle.ACT_NONE)
+    assert np.array_equal(dx, base)
+    assert np.allclose(db, base.astype(np.float64).sum(0), atol=1e-5)
+    dx, db = oracle.linear_backward_input(dy, w, pre, oracle.ACT_RELU)
+    assert np.array_equal(dx, base * (pre > 0))
+    dx, db = oracle.linear_backward_input(dy, w, pre, oracle.ACT_GELU)
+    gelu = lambda v: 0.5 * v * (1 + erf(v / sqrt(2)))
+    h = 1e-6
+    fd = np.array([[(gelu(v + h) - gelu(v - h)) / (2 * h) for v in row] for row in pre.astype(np.float64)])
+    assert np.abs(dx - base * fd).max() < 1e-4
+    assert np.allclose(db, dx.astype(np.float64).sum(0), atol=1e-5)
+
+
 def test_causal_softmax_rows():
     rng = np.random.default_rng(2)
     s = rng.standard_normal((3, 8, 8), dtype=np.float32)
