@@ -713,6 +713,78 @@ def run_attention_fused(args, local_rank):
         "algorithmic_bytes": byts}), flush=True)
 
 
+def run_linear_backward(args, local_rank):
+    """Extra arm: the fused backward epilogue on the configured transformer block's ff2 backward
+    (rows 8192, dy [rows,256], W2 [256,1024], saved pre-activation [rows,1024], GELU): one launch
+    (+ a small reduce) against this library's plain GEMM followed by the elementwise derivative
+    and the row sum as separate passes (torch ops standing in for FastNN's gelu_backward and
+    sum_axis kernels).  Device time from CUDA graphs over rotating operand copies."""
+    import torch
+    import fastnn_b200 as f
+    torch.cuda.set_device(local_rank)
+    f.cuda_init(local_rank)
+    rows, out_f, in_f = 8192, 256, 1024
+    gen = torch.Generator(device="cuda").manual_seed(4000)
+    byts = 4.0 * (rows * out_f + out_f * in_f + 2 * rows * in_f + in_f)
+    nring = ring_count(byts)
+    sets = []
+    for _ in range(nring):
+        dy = torch.randn(rows, out_f, device="cuda", generator=gen)
+        w = torch.randn(out_f, in_f, device="cuda", generator=gen) * 0.05
+        pre = torch.randn(rows, in_f, device="cuda", generator=gen)
+        sets.append((dy, w, pre, torch.empty(rows, in_f, device="cuda"), torch.empty(in_f, device="cuda")))
+    side = torch.cuda.Stream()
+    lib = f.lib()
+    import ctypes
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+
+    def fused(x, sp):
+        assert lib.fastnn_b200_linear_backward_input(NN, vp(x[0]), vp(x[1]), vp(x[3]), rows, out_f, in_f, 2,
+                                                     vp(x[2]), vp(x[4]), ctypes.c_void_p(sp)) == 0
+
+    def fused_no_bias_grad(x, sp):
+        assert lib.fastnn_b200_linear_backward_input(NN, vp(x[0]), vp(x[1]), vp(x[3]), rows, out_f, in_f, 2,
+                                                     vp(x[2]), ctypes.c_void_p(0), ctypes.c_void_p(sp)) == 0
+
+    def gemm_only(x, sp):
+        f.gemm_ex(NN, x[0].data_ptr(), x[1].data_ptr(), x[3].data_ptr(), rows, in_f, out_f, 1,
+                  out_f, in_f, in_f, 0, 0, 0, 1.0, 0.0, 0, 0, sp)
+
+    def unfused(x, sp):
+        gemm_only(x, sp)
+        p = x[2]
+        d = 0.5 * (1.0 + torch.erf(p * 0.7071067811865475)) + p * torch.exp(-0.5 * p * p) * 0.3989422804014327
+        x[3].mul_(d)
+        torch.sum(x[3], dim=0, out=x[4])
+
+    def graph_us(fn, reps=2 * nring):
+        with torch.cuda.stream(side):
+            fn(sets[0], side.cuda_stream)
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(reps):
+                fn(sets[i % nring], torch.cuda.current_stream().cuda_stream)
+        g.replay(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            g.replay()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (5 * reps) * 1e3
+
+    t_fused, t_gemm, t_unfused = graph_us(fused), graph_us(gemm_only), graph_us(unfused)
+    t_fused_nb = graph_us(fused_no_bias_grad)
+    peaks = load_peaks()
+    assert f.device_status() == 0
+    print(json.dumps({
+        "impl": "linear_backward", "rows": rows, "out_features": out_f, "in_features": in_f, "act": "gelu",
+        "fused_us": t_fused, "fused_gbs": byts / t_fused / 1e3, "fused_frac_of_hbm": byts / t_fused / 1e3 / peaks["hbm_gbs"],
+        "fused_without_bias_grad_us": t_fused_nb, "gemm_only_us": t_gemm, "unfused_us": t_unfused,
+        "note": "unfused = this library's GEMM + torch elementwise derivative (several kernels) + torch row sum",
+        "algorithmic_bytes": byts}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -737,6 +809,9 @@ def main():
     if args.workload == "attention_fused":
         if rank == 0:
             run_attention_fused(args, local_rank)
+    elif args.workload == "linear_backward":
+        if rank == 0:
+            run_linear_backward(args, local_rank)
     elif args.workload == "dw_ksharded":
         if world < 2:
             print(json.dumps({"impl": "dw_ksharded", "unavailable": "needs at least two ranks (torchrun)"}))

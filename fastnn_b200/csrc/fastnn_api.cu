@@ -166,11 +166,12 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
         const double waves = static_cast<double>((units + slots - 1) / slots);
         // measured with hinted operand loads: a CTA pair with 256-wide tiles and two k-blocks per
         // stage is 3-5 % faster than single CTAs in a burst (4096^3, 8192^3) and 1-3 % faster over
-        // 0.3 s and longer runs of 8192^3, but 3-5 % slower on 32768 x 16384 x 4096 under the power
-        // cap: its per-tile hand-over between the two CTAs costs more, its per-stage saving grows
-        // with K.  So the deepest problems (K >= 8192, many waves) take pairs, the rest single CTAs.
+        // 0.3 s and longer runs of 8192^3; on 32768 x 16384 x 4096 and its two gradient GEMMs under
+        // the power cap the two are within +-4 % of each other, the sign changing from box to box.
+        // Its per-tile hand-over between the two CTAs costs more and its per-stage saving grows
+        // with K, so deep many-wave problems (K >= 4096) take pairs, the rest single CTAs.
         const double t_kb_scale =
-            !pair ? 1.0 : ((bn == 256 && kbps >= 256 && waves >= 4.0) ? 0.97
+            !pair ? 1.0 : ((bn == 256 && kbps >= 128 && waves >= 4.0) ? 0.97
                                                                        : ((bn == 256 && kbps >= 8) ? 1.05 : 1.12));
         // HBM time is stretched by idle SMs: a wave that fills only part of the machine still
         // takes a full wave
@@ -426,7 +427,11 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   } else {
     grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
     const size_t smem = fnn::gemm_smem_bytes(plan.block_n, plan.stages);
-    fnn::gemm_tf32_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, p);
+    // bias, activation, derivative and column sums are a second pass over every output element by
+    // the epilogue warps alone: eight of them keep it under a short-K main loop
+    const bool epilogue_work = g.act != 0 || g.bias != nullptr || g.colsum != nullptr;
+    const int threads = (epilogue_work && plan.split_k == 1) ? fnn::kNumThreadsWide : fnn::kNumThreads;
+    fnn::gemm_tf32_kernel<<<grid, threads, smem, g.stream>>>(tmA, tmB, tmC, p);
   }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   FNN_CUDA_OK(cudaGetLastError());
@@ -451,9 +456,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     FNN_CUDA_OK(cudaGetLastError());
   }
   if (g.colsum != nullptr) {          // slab partials -> column sums, slabs added in order
-    long long blocks = ceil_div(g.n, 256);
-    fnn::splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, g.stream>>>(
-        p.colsum, g.colsum, nullptr, 1, g.n, 1, slabs, g.n, g.n, 1.0f, 0.0f, 0);
+    fnn::colsum_slabs_kernel<<<ceil_div(g.n, 32), 1024, 0, g.stream>>>(p.colsum, g.colsum, slabs, g.n);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     FNN_CUDA_OK(cudaGetLastError());
   }

@@ -154,6 +154,27 @@ act_grad_inplace_kernel(float* __restrict__ c, const float* __restrict__ aux, in
   }
 }
 
+// Adds the per-slab partial column sums [slabs][n] written by the GEMM epilogue.  A block owns 32
+// columns; thread (ty, tx) adds slabs ty, ty+32, ... of column tx, then the 32 partial sums of a
+// column are added in ty order: a fixed summation tree, so the result is reproducible.
+__global__ void __launch_bounds__(1024)
+colsum_slabs_kernel(const float* __restrict__ partials, float* __restrict__ out, int slabs, int n) {
+  __shared__ float part[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + tx;
+  float s = 0.0f;
+  if (j < n)
+    for (int r = ty; r < slabs; r += 32) s += partials[static_cast<long long>(r) * n + j];
+  part[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && j < n) {
+    float t = 0.0f;
+#pragma unroll
+    for (int r = 0; r < 32; ++r) t += part[r][tx];
+    out[j] = t;
+  }
+}
+
 // ... and its column sums, one thread per column, rows added in order.
 __global__ void __launch_bounds__(256)
 colsum_kernel(const float* __restrict__ c, float* __restrict__ out, int m, int n, long long ldc) {

@@ -30,7 +30,8 @@ constexpr int kBlockK = 32;           // floats per stage along K = one 128-byte
 constexpr int kUmmaK = 8;             // K of one tcgen05.mma kind::tf32
 constexpr int kMaxBlockN = 256;       // columns of one accumulator
 constexpr int kTmemCols = 512;        // two accumulators
-constexpr int kNumThreads = 192;      // 6 warps
+constexpr int kNumThreads = 192;      // 6 warps: producer, MMA issuer, four epilogue warps
+constexpr int kNumThreadsWide = 320;  // the same with eight epilogue warps (single-CTA kernel)
 constexpr int kEpilogueWarp0 = 2;
 constexpr int kStageABytes = kBlockM * kBlockK * 4;            // 16 KiB
 constexpr int kChunkBytes = 32 * kBlockK * 4;                  // one 32 x 32 MN-major box, 4 KiB
@@ -112,12 +113,29 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   return x;
 }
 
+// The epilogue warps are few, so the tensor-core kernels evaluate the Gaussian CDF branch-free
+// and short: erf(z) = 1 - P(t) exp(-z^2) with t = 1/(1 + 0.3275911 z), z = |x|/sqrt 2
+// (Abramowitz & Stegun 7.1.26, |error| <= 1.5e-7: two orders below the TF32 rounding of the
+// product it multiplies).  e returns exp(-x^2/2), which the derivative needs as the density.
+__device__ __forceinline__ float gelu_cdf_fast(float x, float* e_out = nullptr) {
+  const float z = fabsf(x) * 0.70710678118654752440f;
+  const float e = __expf(-z * z);
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float erf_abs = fmaf(-poly * t, e, 1.0f);
+  if (e_out != nullptr) *e_out = e;
+  return fmaf(0.5f, copysignf(erf_abs, x), 0.5f);
+}
+
 // d act / dx at the saved pre-activation x: 1 or 0 for ReLU; Phi(x) + x phi(x) for erf-GELU.
 __device__ __forceinline__ float apply_act_grad(float x, int act) {
   if (act == kActReluGrad) return x > 0.0f ? 1.0f : 0.0f;
-  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752440f));
-  const float pdf = expf(-0.5f * x * x) * 0.3989422804014327f;
-  return cdf + x * pdf;
+  float e;
+  const float cdf = gelu_cdf_fast(x, &e);
+  return fmaf(x * 0.3989422804014327f, e, cdf);
 }
 
 // Bounded wait.  Returns false when the CTA is aborting (this role's budget ran out, or
@@ -144,15 +162,50 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, vola
 // Drains one accumulator tile (this warp's 32 TMEM lanes x block_n columns): scale, bias,
 // activation, then either a swizzled staging tile + TMA store or predicated global stores.
 // m0 is the first output row of this warp, n0 the first column of the tile, cz the outer
-// (batch or batch*split) coordinate, cb the batch index used for the beta read.
+// (batch or batch*split) coordinate, cb the batch index used for the beta read.  The warp takes
+// the 32-column chunks c_first, c_first + c_step, ... of the tile and owns nbuf (1 or 2) staging
+// tiles of 4 KiB.
+// Bias, activation, the backward derivative at aux and the column sums run as a second,
+// column-wise pass over the staging tile: lane j then owns column j of all 32 rows, so the bias is
+// one register, the aux reads (L2-prefetched at the start of the tile) and any direct stores are
+// coalesced, and the column sum is a register.
 __device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const CUtensorMap* tmC,
                                                     uint32_t taddr0, uint32_t staging,
                                                     uint8_t* staging_gen, int& buf, int m0, int n0,
-                                                    int cz, int cb, bool raw, int lane) {
+                                                    int cz, int cb, bool raw, int lane,
+                                                    int c_first = 0, int c_step = 1, int nbuf = 2) {
   const int row = m0 + lane;
-  for (int c = 0; c < p.block_n / 32; ++c) {
+  const bool grad = !raw && (p.act == kActReluGrad || p.act == kActGeluGrad);
+  const bool want_colsum = p.colsum != nullptr && !raw;
+  const bool by_column = !raw && (p.bias != nullptr || p.act != kActNone || p.colsum != nullptr);
+  const int nchunks = p.block_n / 32;
+  // aux[m0 + r][first column of chunk c + lane], r = 0..31: one coalesced row segment per load
+  auto load_aux = [&](int c, float (&dst)[32]) {
+    const int col = n0 + c * 32 + lane;
+    const float* acol = p.aux + static_cast<long long>(m0) * p.ld_aux + col;
+    if (m0 + 32 <= p.m) {                        // whole slab: 32 back-to-back loads
+      if (col < p.n) {
+#pragma unroll
+        for (int r = 0; r < 32; ++r) dst[r] = __ldg(acol + r * p.ld_aux);
+      } else {
+#pragma unroll
+        for (int r = 0; r < 32; ++r) dst[r] = 0.0f;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < 32; ++r)
+        dst[r] = (col < p.n && m0 + r < p.m) ? __ldg(acol + r * p.ld_aux) : 0.0f;
+    }
+  };
+  for (int c = c_first; c < nchunks; c += c_step) {
     const int col0 = n0 + c * 32;
     if (col0 >= p.n) break;                      // warp-uniform
+    const bool col_ok = col0 + lane < p.n;
+    // aux of this chunk: the lines were prefetched into L2 when the tile's main loop started, and
+    // these loads have the TMEM read and the row-wise staging write to complete under
+    float x[32];
+    if (grad && m0 < p.m) load_aux(c, x);
+    const float bias_col = (by_column && p.bias != nullptr && col_ok) ? __ldg(p.bias + col0 + lane) : 0.0f;
     uint32_t r[32];
     ptx::tmem_ld_32x32(taddr0 + c * 32, r);
     ptx::tmem_ld_wait();
@@ -171,42 +224,12 @@ __device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const C
         for (int j = 0; j < 32; ++j)
           if (col0 + j < p.n) v[j] += p.beta * crow[col0 + j];
       }
-      if (p.bias != nullptr) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
-      }
-      if (p.act == kActRelu || p.act == kActGelu) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
-      } else if (p.act == kActReluGrad || p.act == kActGeluGrad) {
-        const float* arow = p.aux + static_cast<long long>(row) * p.ld_aux + col0;
-        const bool vec = row < p.m && col0 + 32 <= p.n && (p.ld_aux & 3) == 0 &&
-                         (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0;
-        float x[32];
-        if (vec) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 t = __ldg(reinterpret_cast<const float4*>(arow) + j);
-            x[4 * j] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            x[j] = (row < p.m && col0 + j < p.n) ? __ldg(arow + j) : 0.0f;
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] *= apply_act_grad(x[j], p.act);
-      }
     }
-    const bool want_colsum = p.colsum != nullptr && !raw;
-    if (want_colsum && row >= p.m) {               // rows past the end add nothing to a column
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = 0.0f;
-    }
-    if (p.store_mode == 0 || want_colsum) {
+    if (p.store_mode == 0 || by_column) {
       // staging tile: 32 rows x 128 B, 16-byte chunk j of row r at chunk (j ^ (r & 7))
-      if (lane == 0) ptx::tma_store_wait_read<1>();   // the tile used two stores ago is free
+      if (lane == 0) {                               // the tile about to be overwritten is read
+        if (nbuf == 2) ptx::tma_store_wait_read<1>(); else ptx::tma_store_wait_read<0>();
+      }
       __syncwarp();
       uint8_t* tile = staging_gen + buf * 4096;
       uint8_t* dst_row = tile + lane * 128;
@@ -215,28 +238,75 @@ __device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const C
         float4 f = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         *reinterpret_cast<float4*>(dst_row + ((j ^ (lane & 7)) << 4)) = f;
       }
-      if (p.store_mode == 0) ptx::fence_proxy_async_smem();
-      __syncwarp();
-      if (p.store_mode == 0 && lane == 0) {
-        if (p.l2_c != 0) ptx::tma_store_3d_hint(tmC, staging + buf * 4096, col0, m0, cz,
-                                                 ptx::make_l2_policy(p.l2_c));
-        else ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
-        ptx::tma_store_commit();
-      }
-      if (want_colsum) {
-        // lane j adds up column j of the tile over its 32 rows in row order (no bank conflicts:
-        // the swizzle spreads one row's columns over all banks)
-        float s = 0.0f;
+      float colsum = 0.0f;
+      if (by_column) {
+        // Second pass: lane j owns column j of the tile (no bank conflicts: the swizzle spreads
+        // one row's columns over all banks).  Bias is then one register, the derivative's
+        // operand a coalesced load, the column sum a register, direct stores coalesced.  All
+        // loads, then arithmetic, then all stores, so that nothing serialises on aliasing.
+        __syncwarp();
+        float t[32];
 #pragma unroll
-        for (int r = 0; r < 32; ++r)
-          s += *reinterpret_cast<const float*>(tile + r * 128 + (((lane >> 2) ^ (r & 7)) << 4) +
-                                               ((lane & 3) << 2));
-        if (col0 + lane < p.n)
-          p.colsum[static_cast<long long>(m0 >> 5) * p.n + col0 + lane] = s;
+        for (int rr = 0; rr < 32; ++rr)
+          t[rr] = *reinterpret_cast<const float*>(tile + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) +
+                                                  ((lane & 3) << 2));
+        // One dense unrolled loop per kind of work, chosen outside the loops: a per-element
+        // choice inside one unrolled loop scatters the few executed instructions over tens of
+        // KiB of code and the pass then runs at instruction-cache-miss speed (measured: 14x).
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) t[rr] += bias_col;
+        }
+        if (p.act == kActRelu) {
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) t[rr] = fmaxf(t[rr], 0.0f);
+        } else if (p.act == kActGelu) {
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) t[rr] *= gelu_cdf_fast(t[rr]);
+        } else if (p.act == kActReluGrad) {
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) t[rr] = x[rr] > 0.0f ? t[rr] : 0.0f;
+        } else if (p.act == kActGeluGrad) {
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) t[rr] *= apply_act_grad(x[rr], kActGeluGrad);
+        }
+        if (m0 + 32 > p.m) {                         // rows past the end add nothing to a column
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr)
+            if (m0 + rr >= p.m) t[rr] = 0.0f;
+        }
+        if (want_colsum) {
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) colsum += t[rr];
+        }
+        if (p.bias != nullptr || p.act != kActNone) {
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr)
+            *reinterpret_cast<float*>(tile + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) +
+                                      ((lane & 3) << 2)) = t[rr];
+        }
+        if (p.store_mode != 0 && col_ok) {
+          float* ccol = p.c + static_cast<long long>(cz) * p.c_batch_stride +
+                        static_cast<long long>(m0) * p.ldc + col0 + lane;
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr)
+            if (m0 + rr < p.m) ccol[rr * p.ldc] = t[rr];
+        }
       }
-      buf ^= 1;
-    }
-    if (p.store_mode != 0 && row < p.m) {
+      if (p.store_mode == 0) {
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (p.l2_c != 0) ptx::tma_store_3d_hint(tmC, staging + buf * 4096, col0, m0, cz,
+                                                   ptx::make_l2_policy(p.l2_c));
+          else ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
+          ptx::tma_store_commit();
+        }
+      }
+      // after the store has been issued: a global write ahead of the proxy fence would hold it up
+      if (want_colsum && col_ok) p.colsum[static_cast<long long>(m0 >> 5) * p.n + col0 + lane] = colsum;
+      if (nbuf == 2) buf ^= 1;
+    } else if (row < p.m) {
       float* crow = p.c + static_cast<long long>(cz) * p.c_batch_stride +
                     static_cast<long long>(row) * p.ldc;
 #pragma unroll
@@ -246,7 +316,7 @@ __device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const C
   }
 }
 
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(kNumThreadsWide, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -256,6 +326,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int n_epi_warps = static_cast<int>(blockDim.x >> 5) - kEpilogueWarp0;     // 4 or 8
 
   const uint32_t stage_b_bytes = static_cast<uint32_t>(p.block_n) * kBlockK * 4;
   const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
@@ -271,6 +342,36 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(bar_gen + 160);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 168);
 
+  // One pipeline stage of unit w: announce the bytes, then one box per operand (or per 32-wide
+  // chunk of an MN-major operand the chunked view does not cover).  Producer thread only.
+  auto issue_stage = [&](const Unit& w, int kb, int stage, uint64_t pol_a, uint64_t pol_b) {
+    const int m0 = w.mt * kBlockM;
+    const int n0 = w.nt * p.block_n;
+    const uint32_t sa = smem_base + stage * stage_bytes;
+    const uint32_t sb = sa + kStageABytes;
+    const uint32_t fb = full_bar(stage);
+    ptx::mbar_expect_tx(fb, stage_bytes);
+    const int k0 = kb * kBlockK;
+    if (!p.a_mn_major) {
+      ptx::tma_load_3d_hint(sa, &tmA, fb, k0, m0, w.b, pol_a);           // 32 x 128 box
+    } else if (p.a_chunked) {
+      ptx::tma_load_4d_hint(sa, &tmA, fb, 0, k0, m0 >> 5, w.b, pol_a);   // 32 x 32 x 4 box
+    } else {
+#pragma unroll
+      for (int c = 0; c < kBlockM / 32; ++c)
+        ptx::tma_load_3d_hint(sa + c * kChunkBytes, &tmA, fb, m0 + 32 * c, k0, w.b, pol_a);
+    }
+    if (!p.b_mn_major) {
+      ptx::tma_load_3d_hint(sb, &tmB, fb, k0, n0, w.b, pol_b);           // 32 x block_n box
+    } else if (p.b_chunked) {
+      ptx::tma_load_4d_hint(sb, &tmB, fb, 0, k0, n0 >> 5, w.b, pol_b);   // 32 x 32 x bn/32
+    } else {
+      for (int c = 0; c < p.block_n / 32; ++c)
+        ptx::tma_load_3d_hint(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b, pol_b);
+    }
+  };
+
+  int pre_issued = 0;                 // stages of the first unit loaded before the CTA-wide sync
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.num_stages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
@@ -278,7 +379,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
-      ptx::mbar_init(tempty_bar(a), 4);
+      ptx::mbar_init(tempty_bar(a), n_epi_warps);
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -286,6 +387,17 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     ptx::prefetch_tensormap(&tmA);
     ptx::prefetch_tensormap(&tmB);
     if (p.store_mode == 0) ptx::prefetch_tensormap(&tmC);
+    // This thread is also the producer: every stage is free, so the first unit's loads start
+    // now and their DRAM latency overlaps the TMEM allocation and the sync below.
+    if (static_cast<int>(blockIdx.x) < p.total_units) {
+      const uint64_t pol_a = ptx::make_l2_policy(p.l2_a);
+      const uint64_t pol_b = ptx::make_l2_policy(p.l2_b);
+      const Unit w = decode_unit(p, blockIdx.x);
+      const int kb0 = w.s * p.kb_per_split;
+      const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+      pre_issued = min(p.num_stages, kb1 - kb0);
+      for (int i = 0; i < pre_issued; ++i) issue_stage(w, kb0 + i, i, pol_a, pol_b);
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc_1cta(tmem_slot, kTmemCols);
@@ -306,34 +418,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint64_t pol_b = ptx::make_l2_policy(p.l2_b);
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         const Unit w = decode_unit(p, u);
-        const int m0 = w.mt * kBlockM;
-        const int n0 = w.nt * p.block_n;
         const int kb0 = w.s * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
-          ok = wait_barrier(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
-          if (!ok) break;
-          const uint32_t sa = smem_base + stage * stage_bytes;
-          const uint32_t sb = sa + kStageABytes;
-          const uint32_t fb = full_bar(stage);
-          ptx::mbar_expect_tx(fb, stage_bytes);
-          const int k0 = kb * kBlockK;
-          if (!p.a_mn_major) {
-            ptx::tma_load_3d_hint(sa, &tmA, fb, k0, m0, w.b, pol_a);           // 32 x 128 box
-          } else if (p.a_chunked) {
-            ptx::tma_load_4d_hint(sa, &tmA, fb, 0, k0, m0 >> 5, w.b, pol_a);   // 32 x 32 x 4 box
+          if (pre_issued > 0) {
+            --pre_issued;                         // loaded before the sync, into this same stage
           } else {
-#pragma unroll
-            for (int c = 0; c < kBlockM / 32; ++c)
-              ptx::tma_load_3d_hint(sa + c * kChunkBytes, &tmA, fb, m0 + 32 * c, k0, w.b, pol_a);
-          }
-          if (!p.b_mn_major) {
-            ptx::tma_load_3d_hint(sb, &tmB, fb, k0, n0, w.b, pol_b);           // 32 x block_n box
-          } else if (p.b_chunked) {
-            ptx::tma_load_4d_hint(sb, &tmB, fb, 0, k0, n0 >> 5, w.b, pol_b);   // 32 x 32 x bn/32
-          } else {
-            for (int c = 0; c < p.block_n / 32; ++c)
-              ptx::tma_load_3d_hint(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b, pol_b);
+            ok = wait_barrier(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
+            if (!ok) break;
+            issue_stage(w, kb, stage, pol_a, pol_b);
           }
           if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
         }
@@ -405,8 +498,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else {
     // -------------------------------------------------------------- epilogue ---
+    // Four epilogue warps, or eight when the epilogue carries an activation or its derivative
+    // (launch with kNumThreadsWide): the two warps of a TMEM lane quadrant then take alternate
+    // 32-column chunks of every tile and one staging tile each instead of two.
     const int q = warp & 3;                          // TMEM lane quadrant this warp may read
-    const uint32_t staging = staging_base + (warp - kEpilogueWarp0) * kStagingBytesPerWarp;
+    const int groups = n_epi_warps >> 2;             // 1 or 2
+    const int group = (warp - kEpilogueWarp0) >> 2;
+    const int nbuf = 2 / groups;
+    const uint32_t staging = staging_base + (warp - kEpilogueWarp0) * (kStagingBytesPerWarp / groups);
     uint8_t* staging_gen = smem_gen + (staging - smem_base);
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -417,6 +516,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const Unit w = decode_unit(p, u);
       const int m0 = w.mt * kBlockM + q * 32;
       const int n0 = w.nt * p.block_n;
+      if (p.aux != nullptr && !raw && m0 + lane < p.m) {
+        // the derivative's operand for this tile: into L2 while the main loop runs
+        const float* arow = p.aux + static_cast<long long>(m0 + lane) * p.ld_aux + n0;
+        for (int c = group; c < p.block_n / 32 && n0 + c * 32 < p.n; c += groups)
+          ptx::prefetch_l2(arow + c * 32);
+      }
       ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
       ok = __all_sync(0xffffffffu, ok);              // keep the warp converged for tcgen05.ld
       if (!ok) break;
@@ -424,7 +529,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                               static_cast<uint32_t>(acc * kMaxBlockN);
       const int cz = raw ? (w.b * p.split_k + w.s) : w.b;   // outer coordinate of the store
-      epilogue_drain_tile(p, &tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, w.b, raw, lane);
+      epilogue_drain_tile(p, &tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, w.b, raw, lane,
+                          group, groups, nbuf);
       // accumulator drained: hand it back to the MMA warp
       ptx::tc_fence_before_sync();
       __syncwarp();

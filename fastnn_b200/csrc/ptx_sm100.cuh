@@ -74,6 +74,10 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// Ask the L2 to fetch the line holding `p` (no register is tied up, nothing is returned).
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 // L2 eviction policy for a load or store: 0 normal, 1 evict-first (streamed once), 2 evict-last
 // (reused by later CTAs), 3 evict-unchanged (a hit leaves the line's priority alone), 4 evict-last
 // for half of the lines.
