@@ -159,21 +159,82 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, vola
   }
 }
 
-// Drains one accumulator tile (this warp's 32 TMEM lanes x block_n columns): scale, bias,
-// activation, then either a swizzled staging tile + TMA store or predicated global stores.
+// Drains one accumulator tile (this warp's 32 TMEM lanes x block_n columns) when nothing but
+// alpha / beta applies: a swizzled staging tile + TMA store, or predicated global stores.
 // m0 is the first output row of this warp, n0 the first column of the tile, cz the outer
 // (batch or batch*split) coordinate, cb the batch index used for the beta read.  The warp takes
 // the 32-column chunks c_first, c_first + c_step, ... of the tile and owns nbuf (1 or 2) staging
 // tiles of 4 KiB.
-// Bias, activation, the backward derivative at aux and the column sums run as a second,
-// column-wise pass over the staging tile: lane j then owns column j of all 32 rows, so the bias is
-// one register, the aux reads (L2-prefetched at the start of the tile) and any direct stores are
-// coalesced, and the column sum is a register.
-__device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const CUtensorMap* tmC,
-                                                    uint32_t taddr0, uint32_t staging,
-                                                    uint8_t* staging_gen, int& buf, int m0, int n0,
-                                                    int cz, int cb, bool raw, int lane,
-                                                    int c_first = 0, int c_step = 1, int nbuf = 2) {
+__device__ __forceinline__ void epilogue_drain_plain(const GemmParams& p, const CUtensorMap* tmC,
+                                                     uint32_t taddr0, uint32_t staging,
+                                                     uint8_t* staging_gen, int& buf, int m0, int n0,
+                                                     int cz, int cb, bool raw, int lane, int c_first,
+                                                     int c_step, int nbuf) {
+  const int row = m0 + lane;
+  for (int c = c_first; c < p.block_n / 32; c += c_step) {
+    const int col0 = n0 + c * 32;
+    if (col0 >= p.n) break;                      // warp-uniform
+    uint32_t r[32];
+    ptx::tmem_ld_32x32(taddr0 + c * 32, r);
+    ptx::tmem_ld_wait();
+    if (m0 >= p.m) continue;                     // warp-uniform: rows all out of range
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (!raw) {
+      if (p.alpha != 1.0f) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+      }
+      if (p.beta != 0.0f && row < p.m) {         // only reachable in direct-store mode
+        const float* crow = p.c + cb * p.c_batch_stride + static_cast<long long>(row) * p.ldc;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.n) v[j] += p.beta * crow[col0 + j];
+      }
+    }
+    if (p.store_mode == 0) {
+      // staging tile: 32 rows x 128 B, 16-byte chunk j of row r at chunk (j ^ (r & 7))
+      if (lane == 0) {                               // the tile about to be overwritten is read
+        if (nbuf == 2) ptx::tma_store_wait_read<1>(); else ptx::tma_store_wait_read<0>();
+      }
+      __syncwarp();
+      uint8_t* dst_row = staging_gen + buf * 4096 + lane * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 f = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        *reinterpret_cast<float4*>(dst_row + ((j ^ (lane & 7)) << 4)) = f;
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (p.l2_c != 0) ptx::tma_store_3d_hint(tmC, staging + buf * 4096, col0, m0, cz,
+                                                 ptx::make_l2_policy(p.l2_c));
+        else ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
+        ptx::tma_store_commit();
+      }
+      if (nbuf == 2) buf ^= 1;
+    } else if (row < p.m) {
+      float* crow = p.c + static_cast<long long>(cz) * p.c_batch_stride +
+                    static_cast<long long>(row) * p.ldc;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.n) crow[col0 + j] = v[j];
+    }
+  }
+}
+
+// The same with bias, activation, the backward derivative at aux and the column sums, which run
+// as a second, column-wise pass over the staging tile: lane j then owns column j of all 32 rows,
+// so the bias is one register, the aux reads (L2-prefetched at the start of the tile) and any
+// direct stores are coalesced, and the column sum is a register.  A loop of its own, apart from
+// the plain one: as branches inside one shared loop its code sat between the hot instructions of
+// the plain path and slowed every GEMM that skipped it by 5-18 %.
+__device__ __forceinline__ void epilogue_drain_by_column(const GemmParams& p, const CUtensorMap* tmC,
+                                                      uint32_t taddr0, uint32_t staging,
+                                                      uint8_t* staging_gen, int& buf, int m0, int n0,
+                                                      int cz, int cb, bool raw, int lane,
+                                                      int c_first, int c_step, int nbuf) {
   const int row = m0 + lane;
   const bool grad = !raw && (p.act == kActReluGrad || p.act == kActGeluGrad);
   const bool want_colsum = p.colsum != nullptr && !raw;
@@ -316,9 +377,24 @@ __device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const C
   }
 }
 
+__device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const CUtensorMap* tmC,
+                                                    uint32_t taddr0, uint32_t staging,
+                                                    uint8_t* staging_gen, int& buf, int m0, int n0,
+                                                    int cz, int cb, bool raw, int lane,
+                                                    int c_first = 0, int c_step = 1, int nbuf = 2) {
+  const bool by_column = !raw && (p.bias != nullptr || p.act != kActNone || p.colsum != nullptr);
+  if (by_column)
+    epilogue_drain_by_column(p, tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, cb, raw, lane,
+                             c_first, c_step, nbuf);
+  else
+    epilogue_drain_plain(p, tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, cb, raw, lane,
+                         c_first, c_step, nbuf);
+}
+
 __global__ void __launch_bounds__(kNumThreadsWide, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmC,
+                 const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 B.
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
