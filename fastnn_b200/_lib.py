@@ -42,6 +42,7 @@ SIGNATURES = {
                                  _f, _f, _vp, _i, _vp]),
     "fastnn_b200_linear_forward": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
     "fastnn_b200_linear_backward_input": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "fastnn_b200_rnn_gates_forward": (_i, [_vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "fastnn_b200_gemm_splitk_static": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "fastnn_b200_attention_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "fastnn_b200_reduce_partials": (_i, [_vp, _vp, _i, _i, _i, _ll, _f, _f, _vp, _i, _vp]),

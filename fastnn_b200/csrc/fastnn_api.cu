@@ -221,6 +221,11 @@ struct GemmArgs {
   const float* aux = nullptr;
   long long ld_aux = 0;
   float* colsum = nullptr;
+  // second operand pair of C = A.B + A2.B2 (same layout, m, n; batch 1) and a second bias
+  const float *a2 = nullptr, *b2 = nullptr;
+  int k2 = 0;
+  long long lda2 = 0, ldb2 = 0;
+  const float* bias2 = nullptr;
 };
 
 bool tma_operands_ok(const GemmArgs& g) {
@@ -273,16 +278,18 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   const bool no_chunk = std::getenv("FASTNN_B200_NO_CHUNKED") != nullptr;
   const bool a_mn = (g.layout == FASTNN_B200_TN) && ((g.m % 32) != 0 || no_chunk);
   const bool b_mn = (g.layout != FASTNN_B200_NT) && ((g.n % 32) != 0 || no_chunk);
-  const int pair_mode = pol.policy == 3 ? 1 : (pol.policy == 4 ? 2 : 0);
-  Plan plan = choose_plan(g.m, g.n, g.k, g.batch, st->num_sms, st->max_clusters, a_mn, b_mn,
-                          pair_mode);
+  const bool dual = g.a2 != nullptr;       // C = A.B + A2.B2: single-CTA kernel, one K range
+  const int pair_mode = dual ? 1 : (pol.policy == 3 ? 1 : (pol.policy == 4 ? 2 : 0));
+  Plan plan = choose_plan(g.m, g.n, g.k + (dual ? g.k2 : 0), g.batch, st->num_sms, st->max_clusters,
+                          a_mn, b_mn, pair_mode);
   if (pol.block_n > 0) plan.block_n = pol.block_n;
   if (pol.split_k > 0) plan.split_k = pol.split_k;
   // the backward epilogue is not linear in the partial sums, and the column sums use the workspace
   const bool backward = g.aux != nullptr || g.colsum != nullptr;
   if (backward) plan.split_k = 1;
   if (plan.pair && (plan.block_n % 64) != 0) plan.block_n = ceil_div(plan.block_n, 64) * 64;
-  const int num_kb = ceil_div(g.k, fnn::kBlockK);
+  const int num_kb1 = ceil_div(g.k, fnn::kBlockK);
+  const int num_kb = num_kb1 + (dual ? ceil_div(g.k2, fnn::kBlockK) : 0);
   if (plan.split_k > num_kb) plan.split_k = num_kb;
   const int kbps = ceil_div(num_kb, plan.split_k);
   plan.split_k = ceil_div(num_kb, kbps);
@@ -308,6 +315,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   p.tiles_m = ceil_div(g.m, plan.pair ? fnn::kPairBlockM : fnn::kBlockM);
   p.tiles_n = ceil_div(g.n, plan.block_n);
   p.num_kb = num_kb;
+  p.num_kb1 = num_kb1;
   p.split_k = plan.split_k;
   p.kb_per_split = kbps;
   p.kb_per_stage = kb_per_stage;
@@ -316,7 +324,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   p.total_units = static_cast<int>(units);
   p.a_mn_major = (g.layout == FASTNN_B200_TN) ? 1 : 0;
   p.b_mn_major = (g.layout == FASTNN_B200_NT) ? 0 : 1;
-  p.alpha = g.alpha; p.beta = g.beta; p.bias = g.bias; p.act = g.act;
+  p.alpha = g.alpha; p.beta = g.beta; p.bias = g.bias; p.bias2 = g.bias2; p.act = g.act;
   p.status = st->status;
   p.spin_budget = st->spin_budget;
   p.group_m = plan.pair ? fnn::kGroupM / 2 : fnn::kGroupM;     // 2048 rows of C either way
@@ -416,6 +424,13 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   } else {
     std::memset(&tmC, 0, sizeof(tmC));
   }
+  CUtensorMap tmA2 = tmA, tmB2 = tmB;
+  if (dual) {                                    // NT only: both operands of both pairs K-major
+    ok = ok && encode_map(&tmA2, g.a2, g.k2, g.m, 1, g.lda2 * 4ull, g.lda2 * 4ull * g.m,
+                          fnn::kBlockK, fnn::kBlockM);
+    ok = ok && encode_map(&tmB2, g.b2, g.k2, g.n, 1, g.ldb2 * 4ull, g.ldb2 * 4ull * g.n,
+                          fnn::kBlockK, b_cols);
+  }
   if (!ok) return -1;
 
   int grid;
@@ -431,7 +446,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     // the epilogue warps alone: eight of them keep it under a short-K main loop
     const bool epilogue_work = g.act != 0 || g.bias != nullptr || g.colsum != nullptr;
     const int threads = (epilogue_work && plan.split_k == 1) ? fnn::kNumThreadsWide : fnn::kNumThreads;
-    fnn::gemm_tf32_kernel<<<grid, threads, smem, g.stream>>>(tmA, tmB, tmC, p);
+    fnn::gemm_tf32_kernel<<<grid, threads, smem, g.stream>>>(tmA, tmB, tmC, tmA2, tmB2, p);
   }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   FNN_CUDA_OK(cudaGetLastError());
@@ -439,7 +454,8 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   if (plan.split_k > 1) {
     const long long total = 1ll * g.m * g.n * g.batch;
     const bool vec = (g.n & 3) == 0 && aligned16(g.c) && (g.ldc & 3) == 0 && (g.sc & 3) == 0 &&
-                     (g.bias == nullptr || aligned16(g.bias));
+                     (g.bias == nullptr || aligned16(g.bias)) &&
+                     (g.bias2 == nullptr || aligned16(g.bias2));
     long long work = vec ? total / 4 : total;
     long long blocks = (work + 255) / 256;
     const long long cap = 8ll * st->num_sms;
@@ -448,10 +464,11 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     if (vec)
       fnn::splitk_reduce_vec4_kernel<<<static_cast<unsigned>(blocks), 256, 0, g.stream>>>(
           reinterpret_cast<const float4*>(out), g.c, g.bias, g.m, g.n, g.batch, plan.split_k, g.ldc,
-          g.sc, g.alpha, g.beta, g.act);
+          g.sc, g.alpha, g.beta, g.act, g.bias2);
     else
       fnn::splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, g.stream>>>(
-          out, g.c, g.bias, g.m, g.n, g.batch, plan.split_k, g.ldc, g.sc, g.alpha, g.beta, g.act);
+          out, g.c, g.bias, g.m, g.n, g.batch, plan.split_k, g.ldc, g.sc, g.alpha, g.beta, g.act,
+          g.bias2);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     FNN_CUDA_OK(cudaGetLastError());
   }
@@ -483,6 +500,27 @@ int gemm_dispatch(const GemmArgs& g) {
   if (pol.policy >= 2 && !can_tma) return -1;
   if (pol.policy == 1 || !can_tma) return launch_simt(g);
   return launch_tcgen05(st, g, pol);
+}
+
+// C = A.B^T + A2.B2^T + bias + bias2 (NT, batch 1).  One launch with both K ranges in one
+// accumulator when TMA can address all four operands, else two dependent launches.
+int dual_dispatch(GemmArgs g) {
+  const bool pair2_ok = g.k2 >= 1 && aligned16(g.a2) && aligned16(g.b2) && (g.lda2 & 3) == 0 &&
+                        (g.ldb2 & 3) == 0;
+  bool fused = false;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    fused = g_policy.policy != 1 && tma_operands_ok(g) && pair2_ok;
+  }
+  if (fused) return gemm_dispatch(g);
+  GemmArgs first = g;
+  first.a2 = first.b2 = nullptr; first.k2 = 0; first.bias2 = nullptr;
+  int rc = gemm_dispatch(first);
+  if (rc != 0) return rc;
+  GemmArgs second = first;
+  second.a = g.a2; second.b = g.b2; second.k = g.k2; second.lda = g.lda2; second.ldb = g.ldb2;
+  second.beta = 1.0f; second.bias = g.bias2;
+  return gemm_dispatch(second);
 }
 
 }  // namespace
@@ -679,6 +717,28 @@ extern "C" int fastnn_b200_linear_backward_input(int layout, const float* dy, co
   g.ld_aux = in_features;
   g.colsum = bias_grad;
   return gemm_dispatch(g);
+}
+
+extern "C" int fastnn_b200_rnn_gates_forward(const float* x_t, long long ld_x, const float* h,
+                                             const float* w_ih, const float* w_hh,
+                                             const float* b_ih, const float* b_hh, float* gates,
+                                             int batch, int input_size, int hidden_size,
+                                             int gate_rows, void* stream) {
+  if (batch < 0 || input_size < 0 || hidden_size < 0 || gate_rows < 0) return -1;
+  if (batch == 0 || gate_rows == 0) return 0;
+  if (ld_x < input_size) return -1;
+  if (gates == nullptr) return -1;
+  if ((input_size > 0 && (x_t == nullptr || w_ih == nullptr)) ||
+      (hidden_size > 0 && (h == nullptr || w_hh == nullptr)))
+    return -1;
+  const float* b1 = b_ih != nullptr ? b_ih : b_hh;          // a single bias goes first
+  const float* b2 = b_ih != nullptr ? b_hh : nullptr;
+  GemmArgs g{FASTNN_B200_NT, x_t, w_ih, gates, batch, gate_rows, input_size, 1,
+             ld_x, input_size, gate_rows, 0, 0, 0, 1.0f, 0.0f, b1, 0,
+             static_cast<cudaStream_t>(stream)};
+  g.a2 = h; g.b2 = w_hh; g.k2 = hidden_size; g.lda2 = hidden_size; g.ldb2 = hidden_size;
+  g.bias2 = b2;
+  return dual_dispatch(g);
 }
 
 extern "C" int fastnn_b200_attention_forward(const float* q, const float* k, const float* v, float* o,
@@ -902,6 +962,7 @@ extern "C" int fastnn_b200_gemm_splitk_static(int layout, const float* a, const 
   p.tiles_m = ceil_div(m, fnn::kBlockM);
   p.tiles_n = ceil_div(n, block_n);
   p.num_kb = num_kb;
+  p.num_kb1 = num_kb;
   p.split_k = split_k + 0;
   p.kb_per_split = kbps;
   const long long units = 1ll * p.tiles_m * p.tiles_n * split_k;
@@ -933,7 +994,7 @@ extern "C" int fastnn_b200_gemm_splitk_static(int layout, const float* a, const 
   if (!ok) return -1;
   const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
   fnn::gemm_tf32_kernel<<<grid, fnn::kNumThreads, fnn::gemm_smem_bytes(block_n, p.num_stages), s>>>(
-      tmA, tmB, tmC, p);
+      tmA, tmB, tmC, tmA, tmB, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   FNN_CUDA_OK(cudaGetLastError());
   long long blocks = (1ll * m * n / 4 + 255) / 256;

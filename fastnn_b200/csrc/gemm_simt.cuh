@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, float* __restrict__ c, const float* __restrict__ bias,
                      int m, int n, int batch, int split, long long ldc, long long c_bs, float alpha,
-                     float beta, int act) {
+                     float beta, int act, const float* __restrict__ bias2 = nullptr) {
   const long long per = static_cast<long long>(m) * n;
   const long long total = per * batch;
   for (long long e = blockIdx.x * 256ll + threadIdx.x; e < total; e += 256ll * gridDim.x) {
@@ -103,6 +103,7 @@ splitk_reduce_kernel(const float* __restrict__ ws, float* __restrict__ c, const 
     float* dst = c + b * c_bs + static_cast<long long>(i) * ldc + j;
     if (beta != 0.0f) v += beta * *dst;
     if (bias != nullptr) v += bias[j];
+    if (bias2 != nullptr) v += bias2[j];
     *dst = apply_act(v, act);
   }
 }
@@ -111,7 +112,8 @@ splitk_reduce_kernel(const float* __restrict__ ws, float* __restrict__ c, const 
 __global__ void __launch_bounds__(256)
 splitk_reduce_vec4_kernel(const float4* __restrict__ ws, float* __restrict__ c,
                           const float* __restrict__ bias, int m, int n, int batch, int split,
-                          long long ldc, long long c_bs, float alpha, float beta, int act) {
+                          long long ldc, long long c_bs, float alpha, float beta, int act,
+                          const float* __restrict__ bias2 = nullptr) {
   const int n4 = n >> 2;
   const long long per4 = static_cast<long long>(m) * n4;
   const long long total = per4 * batch;
@@ -134,6 +136,10 @@ splitk_reduce_vec4_kernel(const float4* __restrict__ ws, float* __restrict__ c,
     }
     if (bias != nullptr) {
       const float4 bb = *reinterpret_cast<const float4*>(bias + 4 * j4);
+      v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
+    }
+    if (bias2 != nullptr) {
+      const float4 bb = *reinterpret_cast<const float4*>(bias2 + 4 * j4);
       v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
     }
     v.x = apply_act(v.x, act); v.y = apply_act(v.y, act);

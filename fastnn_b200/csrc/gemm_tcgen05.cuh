@@ -60,7 +60,8 @@ struct GemmParams {
   int block_n;         // 32..256, multiple of 32
   int num_stages;
   int tiles_m, tiles_n;
-  int num_kb;          // ceil(k / 32)
+  int num_kb;          // 32-deep k-blocks in all: ceil(k / 32), or that of both operand pairs
+  int num_kb1;         // k-blocks read through the first pair of tensor maps (= num_kb normally)
   int split_k;         // >= 1
   int kb_per_split;
   int kb_per_stage;    // 32-deep k-blocks per pipeline stage (CTA-pair kernel only; else 1)
@@ -75,6 +76,7 @@ struct GemmParams {
   int l2_c;            // and of the TMA stores of C
   float alpha, beta;
   const float* bias;   // [n] or null (ignored when split_k > 1: applied by the reduce pass)
+  const float* bias2;  // a second [n] vector added with it, or null (tensor-core kernels only)
   int act;
   const float* aux;    // [m, n] pre-activations for act 3 / 4, row stride ld_aux
   long long ld_aux;
@@ -266,7 +268,8 @@ __device__ __forceinline__ void epilogue_drain_by_column(const GemmParams& p, co
     // these loads have the TMEM read and the row-wise staging write to complete under
     float x[32];
     if (grad && m0 < p.m) load_aux(c, x);
-    const float bias_col = (by_column && p.bias != nullptr && col_ok) ? __ldg(p.bias + col0 + lane) : 0.0f;
+    float bias_col = (p.bias != nullptr && col_ok) ? __ldg(p.bias + col0 + lane) : 0.0f;
+    if (p.bias2 != nullptr && col_ok) bias_col += __ldg(p.bias2 + col0 + lane);
     uint32_t r[32];
     ptx::tmem_ld_32x32(taddr0 + c * 32, r);
     ptx::tmem_ld_wait();
@@ -393,8 +396,8 @@ __device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const C
 
 __global__ void __launch_bounds__(kNumThreadsWide, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC,
-                 const __grid_constant__ GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmA2,
+                 const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 B.
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -427,23 +430,28 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t sb = sa + kStageABytes;
     const uint32_t fb = full_bar(stage);
     ptx::mbar_expect_tx(fb, stage_bytes);
-    const int k0 = kb * kBlockK;
+    // k-blocks [0, num_kb1) come from the first operand pair, the rest from the second
+    // (C = A1.B1 + A2.B2 in one accumulator); an ordinary GEMM has num_kb1 = num_kb.
+    const bool second = kb >= p.num_kb1;
+    const CUtensorMap* mA = second ? &tmA2 : &tmA;
+    const CUtensorMap* mB = second ? &tmB2 : &tmB;
+    const int k0 = (second ? kb - p.num_kb1 : kb) * kBlockK;
     if (!p.a_mn_major) {
-      ptx::tma_load_3d_hint(sa, &tmA, fb, k0, m0, w.b, pol_a);           // 32 x 128 box
+      ptx::tma_load_3d_hint(sa, mA, fb, k0, m0, w.b, pol_a);             // 32 x 128 box
     } else if (p.a_chunked) {
-      ptx::tma_load_4d_hint(sa, &tmA, fb, 0, k0, m0 >> 5, w.b, pol_a);   // 32 x 32 x 4 box
+      ptx::tma_load_4d_hint(sa, mA, fb, 0, k0, m0 >> 5, w.b, pol_a);     // 32 x 32 x 4 box
     } else {
 #pragma unroll
       for (int c = 0; c < kBlockM / 32; ++c)
-        ptx::tma_load_3d_hint(sa + c * kChunkBytes, &tmA, fb, m0 + 32 * c, k0, w.b, pol_a);
+        ptx::tma_load_3d_hint(sa + c * kChunkBytes, mA, fb, m0 + 32 * c, k0, w.b, pol_a);
     }
     if (!p.b_mn_major) {
-      ptx::tma_load_3d_hint(sb, &tmB, fb, k0, n0, w.b, pol_b);           // 32 x block_n box
+      ptx::tma_load_3d_hint(sb, mB, fb, k0, n0, w.b, pol_b);             // 32 x block_n box
     } else if (p.b_chunked) {
-      ptx::tma_load_4d_hint(sb, &tmB, fb, 0, k0, n0 >> 5, w.b, pol_b);   // 32 x 32 x bn/32
+      ptx::tma_load_4d_hint(sb, mB, fb, 0, k0, n0 >> 5, w.b, pol_b);     // 32 x 32 x bn/32
     } else {
       for (int c = 0; c < p.block_n / 32; ++c)
-        ptx::tma_load_3d_hint(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b, pol_b);
+        ptx::tma_load_3d_hint(sb + c * kChunkBytes, mB, fb, n0 + 32 * c, k0, w.b, pol_b);
     }
   };
 
@@ -463,6 +471,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     ptx::prefetch_tensormap(&tmA);
     ptx::prefetch_tensormap(&tmB);
     if (p.store_mode == 0) ptx::prefetch_tensormap(&tmC);
+    if (p.num_kb1 < p.num_kb) {
+      ptx::prefetch_tensormap(&tmA2);
+      ptx::prefetch_tensormap(&tmB2);
+    }
     // This thread is also the producer: every stage is free, so the first unit's loads start
     // now and their DRAM latency overlaps the TMEM allocation and the sync below.
     if (static_cast<int>(blockIdx.x) < p.total_units) {

@@ -231,6 +231,31 @@ def linear_backward_input(dy, w, pre=None, act=ACT_NONE, layout=NN, bias_grad=Fa
     return (dx, db) if bias_grad else dx
 
 
+def rnn_gates_forward(x_t, h, w_ih, w_hh, b_ih=None, b_hh=None, out=None, stream=0):
+    """gates = x_t . W_ih^T + h . W_hh^T + b_ih + b_hh in one launch: the gate pre-activations of
+    LSTM::forward (src/nn/rnn.rs:72-77) and of the plain RNN cell.  x_t [batch,input] may be a
+    strided view x[:, t, :] of x[batch,seq,input]; h [batch,hidden]; W_ih [G,input]; W_hh [G,hidden]."""
+    for name, t in (("h", h), ("w_ih", w_ih), ("w_hh", w_hh)):
+        _check(t, name)
+    if x_t.dtype != torch.float32 or not x_t.is_cuda or x_t.dim() != 2 or x_t.stride(1) != 1:
+        raise ValueError("x_t must be a float32 CUDA matrix with contiguous rows")
+    _ensure_ctx(h)
+    batch, in_f = int(x_t.shape[0]), int(x_t.shape[1])
+    hid = int(h.shape[1])
+    g_rows = int(w_ih.shape[0])
+    if tuple(w_ih.shape) != (g_rows, in_f) or tuple(w_hh.shape) != (g_rows, hid) or int(h.shape[0]) != batch:
+        raise ValueError("rnn_gates_forward shape mismatch")
+    for b in (b_ih, b_hh):
+        if b is not None:
+            _check(b, "bias")
+    gates = _out((batch, g_rows), h, out)
+    ld_x = int(x_t.stride(0)) if batch > 1 else max(in_f, 1)
+    if lib().fastnn_b200_rnn_gates_forward(_ptr(x_t), ld_x, _ptr(h), _ptr(w_ih), _ptr(w_hh), _ptr(b_ih),
+                                           _ptr(b_hh), _ptr(gates), batch, in_f, hid, g_rows, stream) != 0:
+        raise CudaError("CUDA rnn_gates_forward failed")
+    return gates
+
+
 def gemm_ex(layout, a_ptr, b_ptr, c_ptr, m, n, k, batch, lda, ldb, ldc, sa, sb, sc,
             alpha=1.0, beta=0.0, bias_ptr=0, act=ACT_NONE, stream=0) -> None:
     """Raw general entry (pointers as integers, strides in elements)."""

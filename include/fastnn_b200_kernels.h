@@ -123,6 +123,21 @@ FASTNN_B200_API int fastnn_b200_linear_backward_input(int layout, const float* d
                                                       int in_features, int act, const float* pre,
                                                       float* bias_grad, void* stream);
 
+/* Gate pre-activations of one recurrent step in one launch:
+ *   gates[batch, gate_rows] = x_t[batch,input] . W_ih[gate_rows,input]^T
+ *                           + h[batch,hidden]  . W_hh[gate_rows,hidden]^T + b_ih + b_hh
+ * i.e. FastNN's  x_t.matmul(W_ih^T) + h.matmul(W_hh^T) + bias + bias2  of LSTM::forward
+ * (src/nn/rnn.rs:72-77; gate_rows = 4 * hidden) and of the plain RNN cell (gate_rows = hidden):
+ * two transposes, two GEMMs and three elementwise adds there.  Both products accumulate in the
+ * same tensor-memory tile (the K loop runs over input, then hidden).  x_t may be a strided
+ * view: row b of x_t starts at x_t + b * ld_x (ld_x = seq_len * input for x[batch,seq,input]).
+ * Either bias may be NULL.  Operands TMA cannot address are served by two dependent launches. */
+FASTNN_B200_API int fastnn_b200_rnn_gates_forward(const float* x_t, long long ld_x, const float* h,
+                                                  const float* w_ih, const float* w_hh,
+                                                  const float* b_ih, const float* b_hh, float* gates,
+                                                  int batch, int input_size, int hidden_size,
+                                                  int gate_rows, void* stream);
+
 /* Fused attention core, per head h in [0, batch_heads):
  *   O[h] = softmax( scale * Q[h] . K[h]^T + mask ) . V[h]
  * q [batch_heads, t_q, head_dim], k and v [batch_heads, t_k, head_dim], o like q, all dense.

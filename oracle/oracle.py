@@ -14,7 +14,7 @@ from . import build_oracle as _b
 
 __all__ = [
     "rand_data", "matmul", "matmul_nt", "matmul_tn", "matmul_rows", "transpose",
-    "bias_act", "linear", "linear_backward_input", "causal_softmax", "attention", "host_threads", "ACT_NONE", "ACT_RELU",
+    "bias_act", "linear", "linear_backward_input", "rnn_gates", "causal_softmax", "attention", "host_threads", "ACT_NONE", "ACT_RELU",
     "ACT_GELU", "ref_gpu_library_path",
 ]
 
@@ -198,6 +198,20 @@ def linear_backward_input(dy: np.ndarray, w: np.ndarray, pre, act: int = ACT_NON
     xp = _p(pre32) if pre32 is not None else ctypes.cast(None, _fp)
     lib.oracle_act_backward_colsum(_p(dx), xp, _p(colsum), rows, n, act if pre is not None else 0)
     return dx, colsum
+
+
+def rnn_gates(x_t: np.ndarray, h: np.ndarray, w_ih: np.ndarray, w_hh: np.ndarray, b_ih, b_hh) -> np.ndarray:
+    """Gate pre-activations of one recurrent step as LSTM::forward forms them on CPU tensors
+    (src/nn/rnn.rs:72-77): x_t.matmul(W_ih^T), h.matmul(W_hh^T), then three f32 adds in the order
+    gates_i + gates_h + bias_ih + bias_hh."""
+    gi = matmul(_f32(x_t), transpose(_f32(w_ih)))
+    gh = matmul(_f32(h), transpose(_f32(w_hh)))
+    g = gi + gh
+    if b_ih is not None:
+        g = g + _f32(b_ih)[None, :]
+    if b_hh is not None:
+        g = g + _f32(b_hh)[None, :]
+    return g.astype(np.float32)
 
 
 def causal_softmax(scores: np.ndarray, scale: float) -> np.ndarray:

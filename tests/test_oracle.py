@@ -148,6 +148,21 @@ def test_linear_backward_input_follows_the_tape():
     assert np.allclose(db, dx.astype(np.float64).sum(0), atol=1e-5)
 
 
+def test_rnn_gates_are_the_two_products_plus_both_biases():
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((5, 7), dtype=np.float32)
+    h = rng.standard_normal((5, 3), dtype=np.float32)
+    w_ih = rng.standard_normal((12, 7), dtype=np.float32)
+    w_hh = rng.standard_normal((12, 3), dtype=np.float32)
+    b1 = rng.standard_normal(12, dtype=np.float32)
+    b2 = rng.standard_normal(12, dtype=np.float32)
+    g = oracle.rnn_gates(x, h, w_ih, w_hh, b1, b2)
+    want = x.astype(np.float64) @ w_ih.T.astype(np.float64) + h.astype(np.float64) @ w_hh.T + b1 + b2
+    assert g.dtype == np.float32 and np.abs(g - want).max() < 1e-5
+    assert np.array_equal(oracle.rnn_gates(x, h, w_ih, w_hh, None, None),
+                          oracle.matmul_nt(x, w_ih) + oracle.matmul_nt(h, w_hh))
+
+
 def test_causal_softmax_rows():
     rng = np.random.default_rng(2)
     s = rng.standard_normal((3, 8, 8), dtype=np.float32)
