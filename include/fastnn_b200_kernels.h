@@ -195,6 +195,14 @@ FASTNN_B200_API int fastnn_b200_gemm_splitk_static(int layout, const float* a, c
                                                    float* c, int m, int n, int k, int split_k,
                                                    void* stream);
 
+/* Stream-ordered forms of fastnn_cuda_memcpy_h2d / _d2h (cuda/kernels.cu:79-88, which are
+ * synchronous): the copy is enqueued on `stream` and the call returns.  With pinned host memory a
+ * caller can then run the upload of the next GEMM's operands, the GEMM (fastnn_b200_gemm_ex on a
+ * second stream) and the download of the previous result at the same time; PCIe is full duplex.
+ * The caller orders the streams with its own events. */
+FASTNN_B200_API int fastnn_b200_memcpy_h2d_async(float* dst, const float* src, size_t size, void* stream);
+FASTNN_B200_API int fastnn_b200_memcpy_d2h_async(float* dst, const float* src, size_t size, void* stream);
+
 /* Kernel selection for tests and sweeps.  policy: 0 = automatic (tcgen05 path whenever the
  * operands meet TMA's 16-byte alignment rules, SIMT path otherwise), 1 = SIMT path only,
  * 2 = tcgen05 path only (calls that cannot use it fail with -1), 3 = tcgen05 with single-CTA
