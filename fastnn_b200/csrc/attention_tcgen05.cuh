@@ -95,6 +95,8 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // the next kernel of the stream may set itself up on SMs this grid has left
+  ptx::grid_dep_launch_dependents();
 
   const AttnSmem sm = attn_smem_plan(p.d, p.tk_pad, p.nsets);
   const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.nsets) * sm.set_bytes;
@@ -156,6 +158,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   if (warp == 0) {
     // ------------------------------------------------------------- producer ---
     if (lane == 0) {
+      ptx::grid_dep_wait();          // earlier kernels of the stream are complete from here on
       // Q is read once; K and V are read once per query tile of the head
       const uint64_t pol_q = ptx::make_l2_policy(1);
       const uint64_t pol_kv = ptx::make_l2_policy(p.q_tiles > 1 ? 3 : 1);
@@ -233,6 +236,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
   } else {
     // ------------------------------------------------- softmax + output warps ---
+    ptx::grid_dep_wait();            // before the first store of O
     // Two groups of four warps; group g takes this CTA's units g, g+2, ...  A warp may touch the
     // TMEM lane quarter (warp index mod 4) only, so each group covers all 128 rows.
     const int group = (warp - 2) >> 2;

@@ -446,7 +446,29 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     // the epilogue warps alone: eight of them keep it under a short-K main loop
     const bool epilogue_work = g.act != 0 || g.bias != nullptr || g.colsum != nullptr;
     const int threads = (epilogue_work && plan.split_k == 1) ? fnn::kNumThreadsWide : fnn::kNumThreads;
-    fnn::gemm_tf32_kernel<<<grid, threads, smem, g.stream>>>(tmA, tmB, tmC, tmA2, tmB2, p);
+    static const bool pdl = [] {
+      const char* e = std::getenv("FASTNN_B200_PDL");
+      return e == nullptr || std::atoi(e) != 0;
+    }();
+    if (pdl) {
+      // programmatic dependent launch: this grid's CTAs may start on SMs the previous kernel of
+      // the stream has left; the kernel waits for that kernel's completion before it touches
+      // global memory (griddepcontrol.wait), so only its set-up overlaps
+      cudaLaunchConfig_t cfg;
+      std::memset(&cfg, 0, sizeof(cfg));
+      cfg.gridDim = dim3(grid, 1, 1);
+      cfg.blockDim = dim3(threads, 1, 1);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = g.stream;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr.val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::gemm_tf32_kernel, tmA, tmB, tmC, tmA2, tmB2, p));
+    } else {
+      fnn::gemm_tf32_kernel<<<grid, threads, smem, g.stream>>>(tmA, tmB, tmC, tmA2, tmB2, p);
+    }
   }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   FNN_CUDA_OK(cudaGetLastError());
@@ -798,8 +820,22 @@ extern "C" int fastnn_b200_attention_forward(const float* q, const float* k, con
   ok = ok && encode_map(&tmO, o, D, t_q, H, D * 4ull, D * 4ull * t_q, 32, 32);
   if (!ok) return -1;
   const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
-  fnn::attention_tf32_kernel<<<grid, fnn::kAttnThreads, plan.total, static_cast<cudaStream_t>(stream)>>>(
-      tmQ, tmK, tmV, tmO, p);
+  {
+    // launched as a programmatic dependent, like the single-CTA GEMM: set-up overlaps the tail of
+    // the previous kernel of the stream, global memory is touched only after griddepcontrol.wait
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(fnn::kAttnThreads, 1, 1);
+    cfg.dynamicSmemBytes = plan.total;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::attention_tf32_kernel, tmQ, tmK, tmV, tmO, p));
+  }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   FNN_CUDA_OK(cudaGetLastError());
   t_last = LastCall{4, tk_pad, 1, grid};

@@ -406,6 +406,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_epi_warps = static_cast<int>(blockDim.x >> 5) - kEpilogueWarp0;     // 4 or 8
+  // The next kernel of the stream may take over SMs as this grid's CTAs finish: its set-up
+  // (barriers, TMEM, tensor-map prefetch) then overlaps this grid's last tiles.
+  ptx::grid_dep_launch_dependents();
 
   const uint32_t stage_b_bytes = static_cast<uint32_t>(p.block_n) * kBlockK * 4;
   const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
@@ -475,6 +478,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       ptx::prefetch_tensormap(&tmA2);
       ptx::prefetch_tensormap(&tmB2);
     }
+    // Everything above touched no global data; from here on the kernels before this one in
+    // the stream must be complete (a no-op unless launched as a programmatic dependent).
+    ptx::grid_dep_wait();
     // This thread is also the producer: every stage is free, so the first unit's loads start
     // now and their DRAM latency overlaps the TMEM allocation and the sync below.
     if (static_cast<int>(blockIdx.x) < p.total_units) {
@@ -589,6 +595,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // Four epilogue warps, or eight when the epilogue carries an activation or its derivative
     // (launch with kNumThreadsWide): the two warps of a TMEM lane quadrant then take alternate
     // 32-column chunks of every tile and one staging tile each instead of two.
+    ptx::grid_dep_wait();                            // before the first read or write of global data
     const int q = warp & 3;                          // TMEM lane quadrant this warp may read
     const int groups = n_epi_warps >> 2;             // 1 or 2
     const int group = (warp - kEpilogueWarp0) >> 2;

@@ -74,6 +74,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// Programmatic dependent launch.  launch_dependents: the next kernel of the stream, if it was
+// launched with programmatic stream serialisation, may start its CTAs wherever this grid has
+// freed an SM.  wait: block until the grids this one depends on have completed and their memory
+// is visible (returns at once for an ordinary launch).
+__device__ __forceinline__ void grid_dep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 // Ask the L2 to fetch the line holding `p` (no register is tied up, nothing is returned).
 __device__ __forceinline__ void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
