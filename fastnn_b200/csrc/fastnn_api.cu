@@ -483,14 +483,26 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     const long long cap = 8ll * st->num_sms;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
+    // also a programmatic dependent: its launch overlaps the GEMM's last tiles, and it waits for
+    // the GEMM's completion (griddepcontrol.wait) before it reads a partial sum
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = g.stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const float* ws_f = out;
     if (vec)
-      fnn::splitk_reduce_vec4_kernel<<<static_cast<unsigned>(blocks), 256, 0, g.stream>>>(
-          reinterpret_cast<const float4*>(out), g.c, g.bias, g.m, g.n, g.batch, plan.split_k, g.ldc,
-          g.sc, g.alpha, g.beta, g.act, g.bias2);
+      FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::splitk_reduce_vec4_kernel,
+                                     reinterpret_cast<const float4*>(ws_f), g.c, g.bias, g.m, g.n, g.batch,
+                                     plan.split_k, g.ldc, g.sc, g.alpha, g.beta, g.act, g.bias2));
     else
-      fnn::splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, g.stream>>>(
-          out, g.c, g.bias, g.m, g.n, g.batch, plan.split_k, g.ldc, g.sc, g.alpha, g.beta, g.act,
-          g.bias2);
+      FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::splitk_reduce_kernel, ws_f, g.c, g.bias, g.m, g.n,
+                                     g.batch, plan.split_k, g.ldc, g.sc, g.alpha, g.beta, g.act, g.bias2));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     FNN_CUDA_OK(cudaGetLastError());
   }

@@ -89,6 +89,8 @@ __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, float* __restrict__ c, const float* __restrict__ bias,
                      int m, int n, int batch, int split, long long ldc, long long c_bs, float alpha,
                      float beta, int act, const float* __restrict__ bias2 = nullptr) {
+  ptx::grid_dep_launch_dependents();     // see gemm_tf32_kernel: no-ops for an ordinary launch
+  ptx::grid_dep_wait();
   const long long per = static_cast<long long>(m) * n;
   const long long total = per * batch;
   for (long long e = blockIdx.x * 256ll + threadIdx.x; e < total; e += 256ll * gridDim.x) {
@@ -114,6 +116,8 @@ splitk_reduce_vec4_kernel(const float4* __restrict__ ws, float* __restrict__ c,
                           const float* __restrict__ bias, int m, int n, int batch, int split,
                           long long ldc, long long c_bs, float alpha, float beta, int act,
                           const float* __restrict__ bias2 = nullptr) {
+  ptx::grid_dep_launch_dependents();
+  ptx::grid_dep_wait();
   const int n4 = n >> 2;
   const long long per4 = static_cast<long long>(m) * n4;
   const long long total = per4 * batch;
