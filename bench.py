@@ -844,6 +844,60 @@ def run_linear_backward(args, local_rank):
         "algorithmic_bytes": byts}), flush=True)
 
 
+def run_conv2d(args, local_rank):
+    """Extra arm: Conv2d forward as an implicit GEMM (batch 32, 64 -> 128 channels, 56 x 56, 3 x 3,
+    padding 1, bias) against FastNN's own CUDA entry (im2col + cuBLAS per image, from oracle/_ref
+    when built) and cuDNN through torch with TF32 allowed.  Device time, CUDA events around 20
+    calls after warm-up (the reference entry takes no stream, so no graph)."""
+    import ctypes
+    import torch
+    import fastnn_b200 as f
+    import oracle
+    torch.cuda.set_device(local_rank)
+    f.cuda_init(local_rank)
+    n, ci, co, h, w, kh, kw, pad = 32, 64, 128, 56, 56, 3, 3, 1
+    gen = torch.Generator(device="cuda").manual_seed(5000)
+    x = torch.randn(n, ci, h, w, device="cuda", generator=gen)
+    wt = torch.randn(co, ci, kh, kw, device="cuda", generator=gen) * 0.05
+    b = torch.randn(co, device="cuda", generator=gen)
+    y = torch.empty(n, co, h, w, device="cuda")
+    flops = 2.0 * n * h * w * co * ci * kh * kw
+
+    def timed(fn, reps=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    ours = timed(lambda: f.conv2d_forward(x, wt, b, padding=(pad, pad), out=y))
+    torch.backends.cudnn.allow_tf32 = True
+    cudnn = timed(lambda: torch.nn.functional.conv2d(x, wt, b, padding=pad))
+    want = torch.nn.functional.conv2d(x, wt, b, padding=pad)
+    rel = float((y - want).norm() / want.norm())
+    ref_us = None
+    path = oracle.ref_gpu_library_path()
+    if path is not None:
+        ref = ctypes.CDLL(path)
+        assert ref.fastnn_cuda_init(local_rank) == 0
+        vp, ci_t = ctypes.c_void_p, ctypes.c_int
+        y2 = torch.empty_like(y)
+        ref_us = timed(lambda: ref.fastnn_cuda_conv2d_forward(
+            vp(x.data_ptr()), vp(wt.data_ptr()), vp(0), vp(y2.data_ptr()), ci_t(n), ci_t(ci), ci_t(co),
+            ci_t(h), ci_t(w), ci_t(kh), ci_t(kw), ci_t(1), ci_t(1), ci_t(pad), ci_t(pad)), reps=3)
+    assert f.device_status() == 0
+    print(json.dumps({
+        "impl": "conv2d", "shape": f"N{n} C{ci}->{co} {h}x{w} k{kh}x{kw} p{pad}", "ours_us": ours,
+        "ours_tflops": flops / ours / 1e6, "cudnn_tf32_us": cudnn, "cudnn_tflops": flops / cudnn / 1e6,
+        "fastnn_cuda_entry_us_without_bias": ref_us, "rel_diff_vs_cudnn": rel,
+        "note": "FastNN's entry adds bias through one host copy and one launch per channel; timed without bias"}),
+        flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -871,6 +925,9 @@ def main():
     elif args.workload == "linear_backward":
         if rank == 0:
             run_linear_backward(args, local_rank)
+    elif args.workload == "conv2d":
+        if rank == 0:
+            run_conv2d(args, local_rank)
     elif args.workload == "dw_ksharded":
         if world < 2:
             print(json.dumps({"impl": "dw_ksharded", "unavailable": "needs at least two ranks (torchrun)"}))

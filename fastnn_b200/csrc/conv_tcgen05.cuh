@@ -1,0 +1,299 @@
+// Conv2d forward as an implicit GEMM on the tcgen05 main loop (sm_100a).
+//
+//   out[n, co, oh, ow] = bias[co] + sum over (ci, ki, kj) of
+//                        w[co, ci, ki, kj] * x[n, ci, oh*sh + ki - ph, ow*sw + kj - pw]
+// FastNN's Conv2d::forward runs these loops on the CPU (src/nn/conv.rs:97-123); its unbound CUDA
+// entry builds an im2col matrix per image and calls cuBLAS (cuda/kernels.cu:836-946).  Here the
+// im2col matrix never exists: as a GEMM  D[position, co] = A[position, k] . W[co, k]^T  with
+// position = (n, oh, ow) and k = (ci, ki, kj),
+//   warps 6-9  gather A: thread r owns output position r of the tile and reads its 32 inputs of
+//              the current k-block (consecutive lanes = consecutive ow, so each load instruction
+//              is one coalesced row segment; padding and the K tail are zeros) and writes them as
+//              row r of a K-major 128B-swizzled stage, exactly what TMA would have produced;
+//   warp 0     loads the weight tile W[co-tile, k-block] by TMA (weights are [co, k] row-major,
+//              i.e. already K-major; the host pads k to a multiple of 4 when TMA needs it);
+//   warp 1     one lane issues tcgen05.mma kind::tf32 (M = 128 positions, N = block_n channels);
+//   warps 2-5  drain the accumulator: lane = position, column = channel, so for one channel a
+//              warp's 32 lanes write 32 consecutive NCHW elements (coalesced), bias (+ReLU) fused.
+// One persistent CTA per SM, two accumulators in TMEM, every wait bounded as in the GEMM kernels.
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace fnn {
+
+struct ConvParams {
+  int batch, ci, co, h, w, kh, kw, sh, sw, ph, pw, oh, ow;
+  int k;               // ci * kh * kw
+  int num_kb;          // ceil(k / 32)
+  long long positions; // batch * oh * ow
+  int tiles_p, tiles_n, total_units;
+  int block_n, num_stages;
+  const float* x;
+  const float* bias;   // [co] or null
+  float* out;
+  int act;             // 0 none, 1 ReLU
+  unsigned int* status;
+  long long spin_budget;
+};
+
+enum : unsigned int { kStatusConvGather = 0x301 };
+constexpr int kConvThreads = 320;     // producer, MMA issuer, 4 epilogue warps, 4 gather warps
+constexpr int kConvGatherWarp0 = 6;
+
+__device__ __forceinline__ bool conv_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          const ConvParams& p, unsigned int code) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int it = 0;
+  while (true) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if ((++it & 63) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > p.spin_budget) {
+        atomicCAS(p.status, 0u, code);
+        *abort_flag = 1;
+        __threadfence_block();
+        return false;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kConvThreads, 1)
+conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ ConvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  ptx::grid_dep_launch_dependents();
+
+  const uint32_t stage_b_bytes = static_cast<uint32_t>(p.block_n) * kBlockK * 4;
+  const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
+  const uint32_t bar_base = smem_base + p.num_stages * stage_bytes;
+  // barriers: full[8] @0, empty[8] @64, tmem_full[2] @128, tmem_empty[2] @144 | tmem slot @160 | abort @168
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 64u + 8u * s; };
+  auto tfull_bar = [&](int a) { return bar_base + 128u + 8u * a; };
+  auto tempty_bar = [&](int a) { return bar_base + 144u + 8u * a; };
+  const uint32_t tmem_slot = bar_base + 160u;
+  uint8_t* bar_gen = smem_gen + (bar_base - smem_base);
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(bar_gen + 160);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 168);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.num_stages; ++s) {
+      ptx::mbar_init(full_bar(s), 1 + 4);      // the weight load's expect_tx + four gather warps
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+    ptx::prefetch_tensormap(&tmW);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_1cta(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish_1cta();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_gen;
+  // unit u -> (position tile, channel tile); channel tiles of one position tile are neighbours
+  auto tile_p = [&](int u) { return u / p.tiles_n; };
+  auto tile_n = [&](int u) { return u % p.tiles_n; };
+
+  if (warp == 0) {
+    // ------------------------------------------------------- weight producer ---
+    if (lane == 0) {
+      ptx::grid_dep_wait();
+      const uint64_t pol = ptx::make_l2_policy(3);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+        const int n0 = tile_n(u) * p.block_n;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
+          if (!ok) break;
+          const uint32_t sb = smem_base + stage * stage_bytes + kStageABytes;
+          ptx::mbar_expect_tx(full_bar(stage), stage_b_bytes);
+          ptx::tma_load_3d_hint(sb, &tmW, full_bar(stage), kb * kBlockK, n0, 0, pol);
+          if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------------------- MMA issuer ---
+    if (lane == 0) {
+      const uint32_t idesc = ptx::idesc_tf32(kBlockM, p.block_n, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+        ok = conv_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBlockN);
+        uint32_t first = 0u;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = conv_wait(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint32_t sb = sa + kStageABytes;
+#pragma unroll
+          for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
+            const uint64_t da = ptx::smem_desc_sw128(sa + ks * 32u, 16u, 1024u);
+            const uint64_t db = ptx::smem_desc_sw128(sb + ks * 32u, 16u, 1024u);
+            ptx::mma_tf32_1cta(tmem_d, da, db, idesc, first);
+            first = 1u;
+          }
+          ptx::mma_commit_1cta(empty_bar(stage));
+          if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::mma_commit_1cta(tfull_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else if (warp < kConvGatherWarp0) {
+    // -------------------------------------------------------------- epilogue ---
+    ptx::grid_dep_wait();
+    const int q = warp & 3;
+    const long long plane = static_cast<long long>(p.oh) * p.ow;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+      const long long pos = static_cast<long long>(tile_p(u)) * kBlockM + q * 32 + lane;
+      const int n0 = tile_n(u) * p.block_n;
+      const bool row_ok = pos < p.positions;
+      const long long img = row_ok ? pos / plane : 0;
+      const long long rem = row_ok ? pos - img * plane : 0;
+      float* obase = p.out + (img * p.co) * plane + rem;          // + channel * plane
+      ok = conv_wait(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                              static_cast<uint32_t>(acc * kMaxBlockN);
+      for (int c = 0; c < p.block_n / 32; ++c) {
+        const int co0 = n0 + c * 32;
+        if (co0 >= p.co) break;
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr0 + c * 32, r);
+        ptx::tmem_ld_wait();
+        if (co0 + 32 <= p.co) {                      // whole chunk: no per-channel bound checks
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldg(p.bias + co0 + j));
+          }
+          if (p.act == kActRelu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(fmaxf(__uint_as_float(r[j]), 0.0f));
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) obase[(co0 + j) * plane] = __uint_as_float(r[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (co0 + j < p.co && row_ok) {
+              float v = __uint_as_float(r[j]);
+              if (p.bias != nullptr) v += __ldg(p.bias + co0 + j);
+              if (p.act == kActRelu) v = fmaxf(v, 0.0f);
+              obase[(co0 + j) * plane] = v;
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  } else {
+    // ---------------------------------------------------------------- gather ---
+    ptx::grid_dep_wait();
+    const int r = (warp - kConvGatherWarp0) * 32 + lane;          // row of the A stage = position
+    const long long plane = static_cast<long long>(p.oh) * p.ow;
+    const int khw = p.kh * p.kw;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+      const long long pos = static_cast<long long>(tile_p(u)) * kBlockM + r;
+      const bool row_ok = pos < p.positions;
+      const long long img = row_ok ? pos / plane : 0;
+      const int rem = row_ok ? static_cast<int>(pos - img * plane) : 0;
+      const int oy = rem / p.ow, ox = rem - oy * p.ow;
+      const int iy0 = oy * p.sh - p.ph, ix0 = ox * p.sw - p.pw;
+      const float* xb = p.x + img * p.ci * p.h * p.w;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        ok = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        // (ci, ki, kj) of the k-block's first k, then stepped: k is the same in every lane
+        int k = kb * kBlockK;
+        int ci = k / khw;
+        int rk = k - ci * khw;
+        int ki = rk / p.kw;
+        int kj = rk - ki * p.kw;
+        float e[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int iy = iy0 + ki, ix = ix0 + kj;
+          const bool in = row_ok && (k + i) < p.k && iy >= 0 && iy < p.h && ix >= 0 && ix < p.w;
+          e[i] = in ? __ldg(xb + (static_cast<long long>(ci) * p.h + iy) * p.w + ix) : 0.0f;
+          if (++kj == p.kw) { kj = 0; if (++ki == p.kh) { ki = 0; ++ci; } }
+        }
+        uint8_t* row = smem_gen + stage * stage_bytes + r * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<float4*>(row + ((j ^ (r & 7)) << 4)) =
+              make_float4(e[4 * j], e[4 * j + 1], e[4 * j + 2], e[4 * j + 3]);
+        ptx::fence_proxy_async_smem();               // generic writes -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(full_bar(stage));
+        if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) { }
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc_1cta(tmem_base, kTmemCols);
+  }
+}
+
+// weights [co, k] -> [co, k_pad] with zero fill, for k that TMA cannot stride over (k % 4 != 0)
+__global__ void __launch_bounds__(256)
+pad_weights_kernel(const float* __restrict__ w, float* __restrict__ wp, int co, int k, int k_pad) {
+  const long long total = static_cast<long long>(co) * k_pad;
+  for (long long e = blockIdx.x * 256ll + threadIdx.x; e < total; e += 256ll * gridDim.x) {
+    const long long c = e / k_pad;
+    const int kk = static_cast<int>(e - c * k_pad);
+    wp[e] = kk < k ? w[c * k + kk] : 0.0f;
+  }
+}
+
+inline size_t conv_smem_bytes(int block_n, int num_stages) {
+  return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + block_n * kBlockK * 4) + kBarrierBytes;
+}
+
+}  // namespace fnn

@@ -18,6 +18,7 @@
 #include "gemm_tcgen05.cuh"
 #include "gemm_tcgen05_pair.cuh"
 #include "attention_tcgen05.cuh"
+#include "conv_tcgen05.cuh"
 
 namespace {
 
@@ -785,6 +786,107 @@ extern "C" int fastnn_b200_rnn_gates_forward(const float* x_t, long long ld_x, c
   g.a2 = h; g.b2 = w_hh; g.k2 = hidden_size; g.lda2 = hidden_size; g.ldb2 = hidden_size;
   g.bias2 = b2;
   return dual_dispatch(g);
+}
+
+extern "C" int fastnn_b200_conv2d_forward(const float* input, const float* weight, const float* bias,
+                                          float* output, int batch_size, int in_channels,
+                                          int out_channels, int input_h, int input_w, int kernel_h,
+                                          int kernel_w, int stride_h, int stride_w, int pad_h,
+                                          int pad_w, int act, void* stream) {
+  if (batch_size < 0 || in_channels < 1 || out_channels < 1 || input_h < 1 || input_w < 1 ||
+      kernel_h < 1 || kernel_w < 1 || stride_h < 1 || stride_w < 1 || pad_h < 0 || pad_w < 0 ||
+      act < 0 || act > 1)
+    return -1;
+  if (input_h + 2 * pad_h < kernel_h || input_w + 2 * pad_w < kernel_w) return -1;
+  if (batch_size == 0) return 0;
+  if (input == nullptr || weight == nullptr || output == nullptr) return -1;
+  const int oh = (input_h + 2 * pad_h - kernel_h) / stride_h + 1;      // cuda/kernels.cu:903-904
+  const int ow = (input_w + 2 * pad_w - kernel_w) / stride_w + 1;
+  const long long k_ll = 1ll * in_channels * kernel_h * kernel_w;
+  const long long positions = 1ll * batch_size * oh * ow;
+  if (k_ll > (1ll << 30) || positions > (1ll << 40)) return -1;
+  const int k = static_cast<int>(k_ll);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState* st = current_state();
+  if (st == nullptr) return -1;
+  static bool attr_set[kMaxDevices] = {};
+  int dev = 0;
+  FNN_CUDA_OK(cudaGetDevice(&dev));
+  if (!attr_set[dev]) {
+    FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kMaxDynSmem)));
+    attr_set[dev] = true;
+  }
+  // weights are [co, k] row-major: K-major for the tensor core as they stand.  TMA needs 16-byte
+  // rows; otherwise (k = 27 for a 3x3 kernel on RGB) a zero-padded copy goes to the workspace.
+  const float* wsrc = weight;
+  long long w_ld = k;
+  if ((k & 3) != 0 || !aligned16(weight)) {
+    const int k_pad = ceil_div(k, fnn::kBlockK) * fnn::kBlockK;
+    const size_t need = sizeof(float) * static_cast<size_t>(out_channels) * k_pad;
+    Workspace& ws = st->workspaces[s];
+    if (ws.bytes < need) {
+      if (ws.ptr) FNN_CUDA_OK(cudaFree(ws.ptr));
+      ws.ptr = nullptr; ws.bytes = 0;
+      FNN_CUDA_OK(cudaMalloc(&ws.ptr, need));
+      ws.bytes = need;
+    }
+    long long blocks = (1ll * out_channels * k_pad + 255) / 256;
+    if (blocks > 1024) blocks = 1024;
+    fnn::pad_weights_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(weight, ws.ptr, out_channels, k, k_pad);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    wsrc = ws.ptr;
+    w_ld = k_pad;
+  }
+  fnn::ConvParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.batch = batch_size; p.ci = in_channels; p.co = out_channels; p.h = input_h; p.w = input_w;
+  p.kh = kernel_h; p.kw = kernel_w; p.sh = stride_h; p.sw = stride_w; p.ph = pad_h; p.pw = pad_w;
+  p.oh = oh; p.ow = ow; p.k = k; p.num_kb = ceil_div(k, fnn::kBlockK); p.positions = positions;
+  p.block_n = out_channels >= fnn::kMaxBlockN ? fnn::kMaxBlockN : ceil_div(out_channels, 32) * 32;
+  const long long tiles_p = (positions + fnn::kBlockM - 1) / fnn::kBlockM;
+  p.tiles_n = ceil_div(out_channels, p.block_n);
+  if (tiles_p * p.tiles_n > 0x7fffffffll) return -1;
+  p.tiles_p = static_cast<int>(tiles_p);
+  p.total_units = static_cast<int>(tiles_p * p.tiles_n);
+  const size_t stage = fnn::kStageABytes + static_cast<size_t>(p.block_n) * fnn::kBlockK * 4;
+  int stages = static_cast<int>((kMaxDynSmem - 1024 - fnn::kBarrierBytes) / stage);
+  p.num_stages = stages > fnn::kMaxStages ? fnn::kMaxStages : stages;
+  p.x = input; p.bias = bias; p.out = output; p.act = act;
+  p.status = st->status; p.spin_budget = st->spin_budget;
+  CUtensorMap tmW;
+  if (!encode_map(&tmW, wsrc, static_cast<uint64_t>(w_ld == k ? k : w_ld), out_channels, 1, w_ld * 4ull,
+                  w_ld * 4ull * out_channels, fnn::kBlockK, p.block_n))
+    return -1;
+  const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(fnn::kConvThreads, 1, 1);
+  cfg.dynamicSmemBytes = fnn::conv_smem_bytes(p.block_n, p.num_stages);
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::conv2d_tf32_kernel, tmW, p));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  t_last = LastCall{5, p.block_n, 1, grid};
+  return 0;
+}
+
+// FastNN's own entry (cuda/kernels.cu:896-946): same arguments, default stream, no activation.
+extern "C" int fastnn_cuda_conv2d_forward(const float* input, const float* weight, const float* bias,
+                                          float* output, int batch_size, int in_channels,
+                                          int out_channels, int input_h, int input_w, int kernel_h,
+                                          int kernel_w, int stride_h, int stride_w, int pad_h,
+                                          int pad_w) {
+  return fastnn_b200_conv2d_forward(input, weight, bias, output, batch_size, in_channels, out_channels,
+                                    input_h, input_w, kernel_h, kernel_w, stride_h, stride_w, pad_h,
+                                    pad_w, 0, nullptr);
 }
 
 extern "C" int fastnn_b200_attention_forward(const float* q, const float* k, const float* v, float* o,

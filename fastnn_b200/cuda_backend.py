@@ -231,6 +231,28 @@ def linear_backward_input(dy, w, pre=None, act=ACT_NONE, layout=NN, bias_grad=Fa
     return (dx, db) if bias_grad else dx
 
 
+def conv2d_forward(x, weight, bias=None, stride=(1, 1), padding=(0, 0), act=ACT_NONE, out=None, stream=0):
+    """Conv2d::forward (src/nn/conv.rs:80-125) on NCHW tensors as one implicit-GEMM launch:
+    x [N,Cin,H,W], weight [Cout,Cin,KH,KW], bias [Cout] or None; zero padding; act 0 none, 1 ReLU."""
+    _check(x, "x"); _check(weight, "weight")
+    _ensure_ctx(x)
+    if x.dim() != 4 or weight.dim() != 4 or int(weight.shape[1]) != int(x.shape[1]):
+        raise ValueError("Conv2d expects 4D input [N, C, H, W] and weight [Cout, C, KH, KW]")
+    n, ci, h, w = (int(v) for v in x.shape)
+    co, _, kh, kw = (int(v) for v in weight.shape)
+    (sh, sw), (ph, pw) = stride, padding
+    if h + 2 * ph < kh or w + 2 * pw < kw:
+        raise ValueError("kernel larger than the padded input")
+    oh, ow = (h + 2 * ph - kh) // sh + 1, (w + 2 * pw - kw) // sw + 1
+    if bias is not None:
+        _check(bias, "bias")
+    y = _out((n, co, oh, ow), x, out)
+    if lib().fastnn_b200_conv2d_forward(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), n, ci, co, h, w, kh, kw,
+                                        sh, sw, ph, pw, act, stream) != 0:
+        raise CudaError("CUDA conv2d_forward failed")
+    return y
+
+
 def rnn_gates_forward(x_t, h, w_ih, w_hh, b_ih=None, b_hh=None, out=None, stream=0):
     """gates = x_t . W_ih^T + h . W_hh^T + b_ih + b_hh in one launch: the gate pre-activations of
     LSTM::forward (src/nn/rnn.rs:72-77) and of the plain RNN cell.  x_t [batch,input] may be a

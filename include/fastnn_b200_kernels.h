@@ -138,6 +138,27 @@ FASTNN_B200_API int fastnn_b200_rnn_gates_forward(const float* x_t, long long ld
                                                   int batch, int input_size, int hidden_size,
                                                   int gate_rows, void* stream);
 
+/* Conv2d forward, NCHW, as an implicit GEMM (no im2col matrix in memory):
+ *   output[n, co, oh, ow] = bias[co] + sum over (ci, ki, kj) of
+ *       weight[co, ci, ki, kj] * input[n, ci, oh*stride_h + ki - pad_h, ow*stride_w + kj - pad_w]
+ * with out_h = (input_h + 2 pad_h - kernel_h) / stride_h + 1 (likewise out_w), zero padding, no
+ * dilation or groups: Conv2d::forward (src/nn/conv.rs:80-125).  fastnn_cuda_conv2d_forward has
+ * the signature of FastNN's own CUDA entry (cuda/kernels.cu:896-946: im2col + cuBLAS per image,
+ * bias added one channel at a time through host copies) and replaces it; the _b200_ form adds a
+ * fused activation (0 none, 1 ReLU) and a stream.  bias may be NULL.  All images go in one
+ * launch (plus a small weight-padding launch when in_channels*kernel_h*kernel_w is not a
+ * multiple of 4). */
+FASTNN_B200_API int fastnn_cuda_conv2d_forward(const float* input, const float* weight, const float* bias,
+                                               float* output, int batch_size, int in_channels,
+                                               int out_channels, int input_h, int input_w,
+                                               int kernel_h, int kernel_w, int stride_h, int stride_w,
+                                               int pad_h, int pad_w);
+FASTNN_B200_API int fastnn_b200_conv2d_forward(const float* input, const float* weight, const float* bias,
+                                               float* output, int batch_size, int in_channels,
+                                               int out_channels, int input_h, int input_w,
+                                               int kernel_h, int kernel_w, int stride_h, int stride_w,
+                                               int pad_h, int pad_w, int act, void* stream);
+
 /* Fused attention core, per head h in [0, batch_heads):
  *   O[h] = softmax( scale * Q[h] . K[h]^T + mask ) . V[h]
  * q [batch_heads, t_q, head_dim], k and v [batch_heads, t_k, head_dim], o like q, all dense.

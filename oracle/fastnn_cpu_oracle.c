@@ -193,6 +193,34 @@ ORACLE_API void oracle_act_backward_colsum(float* g, const float* x, float* cols
 }
 
 /* ---------------------------------------------------------------------------
+ * Conv2d::forward on CPU tensors, src/nn/conv.rs:97-123: for every (b, oc, oh, ow) the sum
+ * starts at bias[oc] (0 without bias) and adds input * weight over ic, ki, kj in that nesting
+ * order, skipping taps that fall into the zero padding.  NCHW, f32 throughout.
+ * ------------------------------------------------------------------------- */
+ORACLE_API void oracle_conv2d_forward(const float* x, const float* w, const float* bias, float* out,
+                                      size_t batch, size_t ci, size_t co, size_t h, size_t wd,
+                                      size_t kh, size_t kw, size_t sh, size_t sw, size_t ph, size_t pw) {
+  const size_t oh_n = (h + 2 * ph - kh) / sh + 1;
+  const size_t ow_n = (wd + 2 * pw - kw) / sw + 1;
+  for (size_t b = 0; b < batch; ++b)
+    for (size_t oc = 0; oc < co; ++oc)
+      for (size_t oh = 0; oh < oh_n; ++oh)
+        for (size_t ow = 0; ow < ow_n; ++ow) {
+          float sum = bias ? bias[oc] : 0.0f;
+          for (size_t ic = 0; ic < ci; ++ic)
+            for (size_t ki = 0; ki < kh; ++ki)
+              for (size_t kj = 0; kj < kw; ++kj) {
+                const long ih = (long)(oh * sh + ki) - (long)ph;
+                const long iw = (long)(ow * sw + kj) - (long)pw;
+                if (ih >= 0 && ih < (long)h && iw >= 0 && iw < (long)wd)
+                  sum += x[((b * ci + ic) * h + (size_t)ih) * wd + (size_t)iw] *
+                         w[((oc * ci + ic) * kh + ki) * kw + kj];
+              }
+          out[((b * co + oc) * oh_n + oh) * ow_n + ow] = sum;
+        }
+}
+
+/* ---------------------------------------------------------------------------
  * Attention probabilities used as the left operand of the batched P.V product:
  * scores*scale (src/nn/transformer.rs:94) + additive causal mask 0/-1e9
  * (src/nn/transformer.rs:22-27) -> row softmax (src/tensor/ops.rs:273-284).

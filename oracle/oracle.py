@@ -14,7 +14,7 @@ from . import build_oracle as _b
 
 __all__ = [
     "rand_data", "matmul", "matmul_nt", "matmul_tn", "matmul_rows", "transpose",
-    "bias_act", "linear", "linear_backward_input", "rnn_gates", "causal_softmax", "attention", "host_threads", "ACT_NONE", "ACT_RELU",
+    "bias_act", "linear", "linear_backward_input", "rnn_gates", "conv2d", "causal_softmax", "attention", "host_threads", "ACT_NONE", "ACT_RELU",
     "ACT_GELU", "ref_gpu_library_path",
 ]
 
@@ -198,6 +198,24 @@ def linear_backward_input(dy: np.ndarray, w: np.ndarray, pre, act: int = ACT_NON
     xp = _p(pre32) if pre32 is not None else ctypes.cast(None, _fp)
     lib.oracle_act_backward_colsum(_p(dx), xp, _p(colsum), rows, n, act if pre is not None else 0)
     return dx, colsum
+
+
+def conv2d(x: np.ndarray, w: np.ndarray, bias, stride=(1, 1), padding=(0, 0)) -> np.ndarray:
+    """``Conv2d::forward`` on CPU tensors (src/nn/conv.rs:97-123): x [N,Cin,H,W], w [Cout,Cin,KH,KW]."""
+    x, w = _f32(x), _f32(w)
+    n, ci, h, wd = x.shape
+    co, ci2, kh, kw = w.shape
+    assert ci == ci2
+    (sh, sw), (ph, pw) = stride, padding
+    oh, ow = (h + 2 * ph - kh) // sh + 1, (wd + 2 * pw - kw) // sw + 1
+    out = np.empty((n, co, oh, ow), dtype=np.float32)
+    b32 = _f32(bias) if bias is not None else None
+    bp = _p(b32) if b32 is not None else ctypes.cast(None, _fp)
+    lib = _load()
+    lib.oracle_conv2d_forward.argtypes = [_fp, _fp, _fp, _fp] + [_sz] * 11
+    lib.oracle_conv2d_forward.restype = None
+    lib.oracle_conv2d_forward(_p(x), _p(w), bp, _p(out), n, ci, co, h, wd, kh, kw, sh, sw, ph, pw)
+    return out
 
 
 def rnn_gates(x_t: np.ndarray, h: np.ndarray, w_ih: np.ndarray, w_hh: np.ndarray, b_ih, b_hh) -> np.ndarray:

@@ -1,0 +1,90 @@
+"""GPU: Conv2d forward as an implicit GEMM against the CPU loops of Conv2d::forward
+(src/nn/conv.rs:97-123).
+
+Tolerance: the GEMM bar with K = Cin*KH*KW: relative Frobenius <= 5e-3,
+max-abs <= 1e-2 sqrt(K) max|x| max|w|."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(n, ci, co, h, w, kh, kw, seed, bias=True):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n, ci, h, w), dtype=np.float32)
+    wt = (rng.standard_normal((co, ci, kh, kw), dtype=np.float32) * 0.2).astype(np.float32)
+    b = rng.standard_normal(co, dtype=np.float32) if bias else None
+    return x, wt, b
+
+
+def _check(got, want, k, x, wt, what):
+    assert got.shape == want.shape, what
+    assert np.isfinite(got).all(), what
+    err = got.astype(np.float64) - want
+    assert np.linalg.norm(err) / np.linalg.norm(want) <= 5e-3, what
+    assert np.abs(err).max() <= 1e-2 * np.sqrt(k) * np.abs(x).max() * np.abs(wt).max(), what
+
+
+@pytest.mark.parametrize("cfg", [
+    # n, ci, co, h, w, kh, kw, stride, padding
+    (2, 3, 16, 32, 32, 3, 3, (1, 1), (1, 1)),        # RGB stem: K = 27, padded weights
+    (4, 16, 32, 28, 28, 3, 3, (1, 1), (1, 1)),       # K = 144
+    (2, 8, 24, 17, 19, 5, 3, (2, 1), (2, 0)),        # ragged sizes, rectangular kernel, mixed stride / padding
+    (3, 32, 64, 14, 14, 1, 1, (1, 1), (0, 0)),       # pointwise
+    (1, 4, 300, 9, 9, 3, 3, (2, 2), (0, 0)),         # more channels than one tile is wide
+    (8, 64, 128, 16, 16, 3, 3, (1, 1), (1, 1)),      # K = 576, several position tiles per image
+    (1, 1, 1, 5, 5, 5, 5, (1, 1), (0, 0)),           # one output element
+])
+def test_conv2d_matches_the_cpu_loops(gpu, cfg):
+    import torch
+    f = gpu
+    n, ci, co, h, w, kh, kw, stride, padding = cfg
+    x, wt, b = _case(n, ci, co, h, w, kh, kw, sum(cfg[:7]))
+    want = oracle.conv2d(x, wt, b, stride, padding)
+    got = f.conv2d_forward(torch.from_numpy(x).cuda(), torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda(),
+                           stride=stride, padding=padding)
+    torch.cuda.synchronize()
+    assert f.last_path()["path"] == 5
+    _check(got.cpu().numpy(), want, ci * kh * kw, x, wt, str(cfg))
+    assert f.device_status() == 0
+
+
+def test_conv2d_without_bias_with_relu_and_through_the_reference_symbol(gpu):
+    import torch
+    f = gpu
+    x, wt, b = _case(2, 6, 20, 12, 12, 3, 3, 5)
+    xd, wd, bd = (torch.from_numpy(t).cuda() for t in (x, wt, b))
+    want = oracle.conv2d(x, wt, None, (1, 1), (1, 1))
+    _check(f.conv2d_forward(xd, wd, None, padding=(1, 1)).cpu().numpy(), want, 54, x, wt, "no bias")
+    relu = f.conv2d_forward(xd, wd, bd, padding=(1, 1), act=f.ACT_RELU).cpu().numpy()
+    want_b = oracle.conv2d(x, wt, b, (1, 1), (1, 1))
+    _check(relu, np.maximum(want_b, 0), 54, x, wt, "relu")
+    assert (relu >= 0).all()
+    # FastNN's own entry point name and argument list
+    out = torch.full((2, 20, 12, 12), float("nan"), device="cuda")
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    assert f.lib().fastnn_cuda_conv2d_forward(vp(xd), vp(wd), vp(bd), vp(out), 2, 6, 20, 12, 12, 3, 3,
+                                              1, 1, 1, 1) == 0
+    torch.cuda.synchronize()
+    _check(out.cpu().numpy(), want_b, 54, x, wt, "reference symbol")
+
+
+def test_conv2d_is_deterministic_and_rejects_bad_arguments(gpu):
+    import torch
+    f = gpu
+    x, wt, b = _case(4, 16, 48, 20, 20, 3, 3, 9)
+    t = [torch.from_numpy(a).cuda() for a in (x, wt, b)]
+    a = f.conv2d_forward(*t, padding=(1, 1))
+    c = f.conv2d_forward(*t, padding=(1, 1))
+    assert torch.equal(a, c)
+    lib = f.lib()
+    p, null = ctypes.c_void_p(t[0].data_ptr()), ctypes.c_void_p(0)
+    assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 0, 4, 8, 8, 3, 3, 1, 1, 0, 0, 0, None) == -1   # channels
+    assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 4, 4, 2, 2, 3, 3, 1, 1, 0, 0, 0, None) == -1   # kernel > input
+    assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 4, 4, 8, 8, 3, 3, 0, 1, 0, 0, 0, None) == -1   # stride
+    assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 4, 4, 8, 8, 3, 3, 1, 1, 0, 0, 2, None) == -1   # act
+    assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 0, 4, 4, 8, 8, 3, 3, 1, 1, 0, 0, 0, None) == 0    # empty batch

@@ -163,6 +163,28 @@ def test_rnn_gates_are_the_two_products_plus_both_biases():
                           oracle.matmul_nt(x, w_ih) + oracle.matmul_nt(h, w_hh))
 
 
+def test_conv2d_loops_against_a_direct_float64_sum():
+    rng = np.random.default_rng(41)
+    x = rng.standard_normal((2, 3, 7, 6), dtype=np.float32)
+    w = rng.standard_normal((4, 3, 3, 2), dtype=np.float32)
+    b = rng.standard_normal(4, dtype=np.float32)
+    got = oracle.conv2d(x, w, b, (2, 1), (1, 0))
+    xp = np.pad(x.astype(np.float64), ((0, 0), (0, 0), (1, 1), (0, 0)))
+    oh, ow = (7 + 2 - 3) // 2 + 1, (6 - 2) // 1 + 1
+    assert got.shape == (2, 4, oh, ow)
+    want = np.zeros((2, 4, oh, ow))
+    for i in range(oh):
+        for j in range(ow):
+            patch = xp[:, :, 2 * i:2 * i + 3, j:j + 2]
+            want[:, :, i, j] = np.einsum("nchw,ochw->no", patch, w.astype(np.float64)) + b
+    assert np.abs(got - want).max() < 1e-5
+    # a 1x1 kernel is a matmul over channels
+    w1 = rng.standard_normal((5, 3, 1, 1), dtype=np.float32)
+    y = oracle.conv2d(x, w1, None)
+    ref = np.einsum("nchw,oc->nohw", x.astype(np.float64), w1[:, :, 0, 0].astype(np.float64))
+    assert np.abs(y - ref).max() < 1e-5
+
+
 def test_causal_softmax_rows():
     rng = np.random.default_rng(2)
     s = rng.standard_normal((3, 8, 8), dtype=np.float32)
