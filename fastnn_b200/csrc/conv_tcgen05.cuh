@@ -6,10 +6,12 @@
 // entry builds an im2col matrix per image and calls cuBLAS (cuda/kernels.cu:836-946).  Here the
 // im2col matrix never exists: as a GEMM  D[position, co] = A[position, k] . W[co, k]^T  with
 // position = (n, oh, ow) and k = (ci, ki, kj),
-//   warps 6-9  gather A: thread r owns output position r of the tile and reads its 32 inputs of
-//              the current k-block (consecutive lanes = consecutive ow, so each load instruction
-//              is one coalesced row segment; padding and the K tail are zeros) and writes them as
-//              row r of a K-major 128B-swizzled stage, exactly what TMA would have produced;
+//   warps 6-21 gather A: a thread owns one output position of the tile and a quarter of the
+//              k-block; it reads its 8 inputs (consecutive lanes = consecutive ow, so each load
+//              instruction is one coalesced row segment; padding and the K tail are zeros), one
+//              k-block ahead of the one it writes, into row r of a K-major 128B-swizzled stage,
+//              exactly what TMA would have produced.  Measured: the gather, not the tensor
+//              core, sets the pace (about 1800 cycles per k-block against 256-512 of MMA work);
 //   warp 0     loads the weight tile W[co-tile, k-block] by TMA (weights are [co, k] row-major,
 //              i.e. already K-major; the host pads k to a multiple of 4 when TMA needs it);
 //   warp 1     one lane issues tcgen05.mma kind::tf32 (M = 128 positions, N = block_n channels);
@@ -37,7 +39,9 @@ struct ConvParams {
 };
 
 enum : unsigned int { kStatusConvGather = 0x301 };
-constexpr int kConvThreads = 320;     // producer, MMA issuer, 4 epilogue warps, 4 gather warps
+constexpr int kConvGatherWarps = 16;
+constexpr int kConvThreads = 32 * (6 + kConvGatherWarps);   // producer, MMA issuer, 4 epilogue warps, gather warps
+constexpr int kConvKPerThread = kBlockK / (kConvGatherWarps / 4);   // k's of a stage row one gather thread fills
 constexpr int kConvGatherWarp0 = 6;
 
 __device__ __forceinline__ bool conv_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
@@ -83,7 +87,7 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.num_stages; ++s) {
-      ptx::mbar_init(full_bar(s), 1 + 4);      // the weight load's expect_tx + four gather warps
+      ptx::mbar_init(full_bar(s), 1 + kConvGatherWarps);   // the weight load's expect_tx + gather warps
       ptx::mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -222,10 +226,24 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------------- gather ---
+    // Eight warps: warp g fills rows (g & 3) * 32 + lane, k sub-range (g >> 2) * 16 .. + 16 of the
+    // stage.  The gather is bound by instruction issue, so the per-element work is cut to a
+    // shuffle, a mask test, one add and the load:
+    //  * per unit a thread builds a bit mask over the kernel taps (ki * kw + kj) that fall inside
+    //    the image for its position, and the pointer to tap (0, 0) of channel 0;
+    //  * per k-block lane i decodes the warp's i-th k once -- offset ci*H*W + ki*W + kj and tap
+    //    index, stepped from the previous k-block without a division -- and the element loop
+    //    broadcasts it by shuffle.
     ptx::grid_dep_wait();
-    const int r = (warp - kConvGatherWarp0) * 32 + lane;          // row of the A stage = position
+    const int g = warp - kConvGatherWarp0;
+    const int r = (g & 3) * 32 + lane;                            // row of the A stage = position
+    const int part = g >> 2;                                      // which k sub-range of the row
     const long long plane = static_cast<long long>(p.oh) * p.ow;
     const int khw = p.kh * p.kw;
+    const int hw = p.h * p.w;
+    const int step_ci = kBlockK / khw, step_rk = kBlockK % khw;   // k advances by 32 per k-block
+    const int inv_kw = (65536 + p.kw - 1) / p.kw;                 // rk / kw for rk < 64, exactly
+    constexpr int kPastK = 63;                                    // tap index of a k past the end
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -236,29 +254,50 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int rem = row_ok ? static_cast<int>(pos - img * plane) : 0;
       const int oy = rem / p.ow, ox = rem - oy * p.ow;
       const int iy0 = oy * p.sh - p.ph, ix0 = ox * p.sw - p.pw;
-      const float* xb = p.x + img * p.ci * p.h * p.w;
-      for (int kb = 0; kb < p.num_kb; ++kb) {
-        ok = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        // (ci, ki, kj) of the k-block's first k, then stepped: k is the same in every lane
-        int k = kb * kBlockK;
-        int ci = k / khw;
-        int rk = k - ci * khw;
-        int ki = rk / p.kw;
-        int kj = rk - ki * p.kw;
-        float e[32];
+      unsigned long long tapmask = 0;                             // bit kPastK stays clear
+      if (row_ok) {
+        for (int ki = 0; ki < p.kh; ++ki)
+          for (int kj = 0; kj < p.kw; ++kj)
+            if (static_cast<unsigned>(iy0 + ki) < static_cast<unsigned>(p.h) &&
+                static_cast<unsigned>(ix0 + kj) < static_cast<unsigned>(p.w))
+              tapmask |= 1ull << (ki * p.kw + kj);
+      }
+      // never dereferenced for a tap outside the image
+      const float* xp = p.x + img * p.ci * hw + static_cast<long long>(iy0) * p.w + ix0;
+      // this lane's k of the first k-block
+      int ci = (part * kConvKPerThread + (lane & (kConvKPerThread - 1))) / khw;
+      int rk = (part * kConvKPerThread + (lane & (kConvKPerThread - 1))) - ci * khw;
+      // The loads of k-block kb + 1 are issued before k-block kb is written out, so their latency
+      // (L2, mostly) runs under the write, the fence and the wait for the next free stage.
+      float nxt[kConvKPerThread];
+      auto issue_loads = [&](int kb) {
+        const int kk = kb * kBlockK + part * kConvKPerThread + (lane & (kConvKPerThread - 1));
+        const int ki = (rk * inv_kw) >> 16;
+        const int packed = kk < p.k ? (((ci * hw + ki * p.w + (rk - ki * p.kw)) << 6) | rk) : kPastK;
+        ci += step_ci; rk += step_rk;
+        if (rk >= khw) { rk -= khw; ++ci; }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int iy = iy0 + ki, ix = ix0 + kj;
-          const bool in = row_ok && (k + i) < p.k && iy >= 0 && iy < p.h && ix >= 0 && ix < p.w;
-          e[i] = in ? __ldg(xb + (static_cast<long long>(ci) * p.h + iy) * p.w + ix) : 0.0f;
-          if (++kj == p.kw) { kj = 0; if (++ki == p.kh) { ki = 0; ++ci; } }
+        for (int i = 0; i < kConvKPerThread; ++i) {
+          const int t = __shfl_sync(0xffffffffu, packed, i);
+          const bool in = (tapmask >> (t & 63)) & 1ull;
+          nxt[i] = in ? __ldg(xp + (t >> 6)) : 0.0f;
         }
+      };
+      issue_loads(0);
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        float e[kConvKPerThread];
+#pragma unroll
+        for (int i = 0; i < kConvKPerThread; ++i) e[i] = nxt[i];
+        if (kb + 1 < p.num_kb) issue_loads(kb + 1);
+        // one lane per warp polls; the shuffle orders the other lanes' writes after its observation
+        int okw = 1;
+        if (lane == 0) okw = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
+        if (!ok) break;
         uint8_t* row = smem_gen + stage * stage_bytes + r * 128;
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<float4*>(row + ((j ^ (r & 7)) << 4)) =
+        for (int j = 0; j < kConvKPerThread / 4; ++j)
+          *reinterpret_cast<float4*>(row + (((part * (kConvKPerThread / 4) + j) ^ (r & 7)) << 4)) =
               make_float4(e[4 * j], e[4 * j + 1], e[4 * j + 2], e[4 * j + 3]);
         ptx::fence_proxy_async_smem();               // generic writes -> visible to the tensor core
         __syncwarp();

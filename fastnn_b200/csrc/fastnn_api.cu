@@ -798,6 +798,8 @@ extern "C" int fastnn_b200_conv2d_forward(const float* input, const float* weigh
       act < 0 || act > 1)
     return -1;
   if (input_h + 2 * pad_h < kernel_h || input_w + 2 * pad_w < kernel_w) return -1;
+  // the gather packs (offset inside the image, tap index) into 32 bits and keeps a 64-bit tap mask
+  if (1ll * kernel_h * kernel_w > 63 || 1ll * in_channels * input_h * input_w >= (1ll << 25)) return -1;
   if (batch_size == 0) return 0;
   if (input == nullptr || weight == nullptr || output == nullptr) return -1;
   const int oh = (input_h + 2 * pad_h - kernel_h) / stride_h + 1;      // cuda/kernels.cu:903-904

@@ -88,3 +88,16 @@ def test_conv2d_is_deterministic_and_rejects_bad_arguments(gpu):
     assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 4, 4, 8, 8, 3, 3, 0, 1, 0, 0, 0, None) == -1   # stride
     assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 4, 4, 8, 8, 3, 3, 1, 1, 0, 0, 2, None) == -1   # act
     assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 0, 4, 4, 8, 8, 3, 3, 1, 1, 0, 0, 0, None) == 0    # empty batch
+    assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 4, 4, 16, 16, 8, 8, 1, 1, 0, 0, 0, None) == -1  # 64 taps
+    assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 2048, 4, 128, 128, 3, 3, 1, 1, 0, 0, 0, None) == -1  # image >= 2^25
+
+
+def test_conv2d_with_a_seven_by_seven_kernel_and_stride_two(gpu):
+    """49 taps (the tap mask's upper half) and a tile that spans images."""
+    import torch
+    f = gpu
+    x, wt, b = _case(3, 3, 64, 37, 41, 7, 7, 13)
+    want = oracle.conv2d(x, wt, b, (2, 2), (3, 3))
+    got = f.conv2d_forward(torch.from_numpy(x).cuda(), torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda(),
+                           stride=(2, 2), padding=(3, 3))
+    _check(got.cpu().numpy(), want, 3 * 49, x, wt, "7x7 stride 2")
