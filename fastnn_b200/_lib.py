@@ -47,6 +47,10 @@ SIGNATURES = {
     "fastnn_b200_memcpy_d2h_async": (_i, [_vp, _vp, ctypes.c_size_t, _vp]),
     "fastnn_cuda_conv2d_forward": (_i, [_vp, _vp, _vp, _vp] + [_i] * 11),
     "fastnn_b200_conv2d_forward": (_i, [_vp, _vp, _vp, _vp] + [_i] * 12 + [_vp]),
+    "fastnn_cuda_conv2d_backward_data": (_i, [_vp, _vp, _vp] + [_i] * 13),
+    "fastnn_b200_conv2d_backward_data": (_i, [_vp, _vp, _vp] + [_i] * 13 + [_vp]),
+    "fastnn_cuda_conv2d_backward_weight": (_i, [_vp, _vp, _vp] + [_i] * 13),
+    "fastnn_b200_conv2d_backward_weight": (_i, [_vp, _vp, _vp] + [_i] * 13 + [_vp]),
     "fastnn_b200_gemm_splitk_static": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "fastnn_b200_attention_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "fastnn_b200_reduce_partials": (_i, [_vp, _vp, _i, _i, _i, _ll, _f, _f, _vp, _i, _vp]),

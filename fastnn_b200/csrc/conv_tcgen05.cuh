@@ -331,6 +331,57 @@ pad_weights_kernel(const float* __restrict__ w, float* __restrict__ wp, int co, 
   }
 }
 
+// w [ic, oc, kh, kw] -> wp [oc, k_pad] with k = (ic, a, b) and wp[oc][(ic*kh + a)*kw + b] =
+// w[ic][oc][kh-1-a][kw-1-b], zero fill past k: the weights of the convolution that maps an output
+// gradient back to the input gradient.
+__global__ void __launch_bounds__(256)
+flip_weights_kernel(const float* __restrict__ w, float* __restrict__ wp, int ic, int oc, int kh, int kw,
+                    int k_pad) {
+  const int khw = kh * kw;
+  const int k = ic * khw;
+  const long long total = static_cast<long long>(oc) * k_pad;
+  for (long long e = blockIdx.x * 256ll + threadIdx.x; e < total; e += 256ll * gridDim.x) {
+    const int o = static_cast<int>(e / k_pad);
+    const int kk = static_cast<int>(e - static_cast<long long>(o) * k_pad);
+    float v = 0.0f;
+    if (kk < k) {
+      const int i = kk / khw;
+      const int r = kk - i * khw;
+      const int a = r / kw, b = r - a * kw;
+      v = w[((static_cast<long long>(i) * oc + o) * kh + (kh - 1 - a)) * kw + (kw - 1 - b)];
+    }
+    wp[e] = v;
+  }
+}
+
+// Explicit im2col for the weight gradient: col[(n * P + p) * ld + k] = the input under tap k of output
+// position p of image n (0 in the padding and for k in [K, ld)).  Same index rule as
+// kernel_im2col of FastNN (cuda/kernels.cu:836-861), but position-major and for all images at once.
+__global__ void __launch_bounds__(256)
+im2col_rows_kernel(const float* __restrict__ x, float* __restrict__ col, int batch, int ci, int h, int w,
+                   int kh, int kw, int sh, int sw, int ph, int pw, int oh, int ow, int ld) {
+  const int khw = kh * kw;
+  const int k_all = ci * khw;
+  const long long plane = static_cast<long long>(oh) * ow;
+  const long long total = static_cast<long long>(batch) * plane * ld;
+  for (long long e = blockIdx.x * 256ll + threadIdx.x; e < total; e += 256ll * gridDim.x) {
+    const long long row = e / ld;
+    const int k = static_cast<int>(e - row * ld);
+    float v = 0.0f;
+    if (k < k_all) {
+      const long long n = row / plane;
+      const int rem = static_cast<int>(row - n * plane);
+      const int oy = rem / ow, ox = rem - oy * ow;
+      const int c = k / khw;
+      const int r = k - c * khw;
+      const int ki = r / kw, kj = r - ki * kw;
+      const int iy = oy * sh - ph + ki, ix = ox * sw - pw + kj;
+      if (iy >= 0 && iy < h && ix >= 0 && ix < w) v = x[((n * ci + c) * h + iy) * w + ix];
+    }
+    col[e] = v;
+  }
+}
+
 inline size_t conv_smem_bytes(int block_n, int num_stages) {
   return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + block_n * kBlockK * 4) + kBarrierBytes;
 }

@@ -44,6 +44,7 @@ struct DeviceState {
   unsigned int* status = nullptr;   // device word written by a kernel whose wait ran out
   long long spin_budget = 0;        // clock ticks one wait may last
   std::map<cudaStream_t, Workspace> workspaces;   // split-K partials, one per stream
+  std::map<cudaStream_t, Workspace> conv_ws;      // im2col matrix + per-image partials of conv dW
 };
 
 std::mutex g_mutex;
@@ -227,6 +228,7 @@ struct GemmArgs {
   int k2 = 0;
   long long lda2 = 0, ldb2 = 0;
   const float* bias2 = nullptr;
+  int force_split_k = 0;     // > 0: overrides the planner's K split (callers that own the workspace)
 };
 
 bool tma_operands_ok(const GemmArgs& g) {
@@ -288,6 +290,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   // the backward epilogue is not linear in the partial sums, and the column sums use the workspace
   const bool backward = g.aux != nullptr || g.colsum != nullptr;
   if (backward) plan.split_k = 1;
+  if (g.force_split_k > 0) plan.split_k = g.force_split_k;
   if (plan.pair && (plan.block_n % 64) != 0) plan.block_n = ceil_div(plan.block_n, 64) * 64;
   const int num_kb1 = ceil_div(g.k, fnn::kBlockK);
   const int num_kb = num_kb1 + (dual ? ceil_div(g.k2, fnn::kBlockK) : 0);
@@ -788,11 +791,14 @@ extern "C" int fastnn_b200_rnn_gates_forward(const float* x_t, long long ld_x, c
   return dual_dispatch(g);
 }
 
-extern "C" int fastnn_b200_conv2d_forward(const float* input, const float* weight, const float* bias,
-                                          float* output, int batch_size, int in_channels,
-                                          int out_channels, int input_h, int input_w, int kernel_h,
-                                          int kernel_w, int stride_h, int stride_w, int pad_h,
-                                          int pad_w, int act, void* stream) {
+// The implicit-GEMM convolution.  flip_transpose = false: `weight` is [out, in, kh, kw].
+// flip_transpose = true: `weight` is [in, out, kh, kw] and is used with both kernel axes
+// reversed -- the form in which the gradient with respect to the input of a stride-1
+// convolution is itself a convolution of the output gradient.
+static int conv_forward_impl(const float* input, const float* weight, const float* bias, float* output,
+                             int batch_size, int in_channels, int out_channels, int input_h,
+                             int input_w, int kernel_h, int kernel_w, int stride_h, int stride_w,
+                             int pad_h, int pad_w, int act, void* stream, bool flip_transpose) {
   if (batch_size < 0 || in_channels < 1 || out_channels < 1 || input_h < 1 || input_w < 1 ||
       kernel_h < 1 || kernel_w < 1 || stride_h < 1 || stride_w < 1 || pad_h < 0 || pad_w < 0 ||
       act < 0 || act > 1)
@@ -825,7 +831,7 @@ extern "C" int fastnn_b200_conv2d_forward(const float* input, const float* weigh
   // rows; otherwise (k = 27 for a 3x3 kernel on RGB) a zero-padded copy goes to the workspace.
   const float* wsrc = weight;
   long long w_ld = k;
-  if ((k & 3) != 0 || !aligned16(weight)) {
+  if (flip_transpose || (k & 3) != 0 || !aligned16(weight)) {
     const int k_pad = ceil_div(k, fnn::kBlockK) * fnn::kBlockK;
     const size_t need = sizeof(float) * static_cast<size_t>(out_channels) * k_pad;
     Workspace& ws = st->workspaces[s];
@@ -837,7 +843,11 @@ extern "C" int fastnn_b200_conv2d_forward(const float* input, const float* weigh
     }
     long long blocks = (1ll * out_channels * k_pad + 255) / 256;
     if (blocks > 1024) blocks = 1024;
-    fnn::pad_weights_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(weight, ws.ptr, out_channels, k, k_pad);
+    if (flip_transpose)
+      fnn::flip_weights_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+          weight, ws.ptr, in_channels, out_channels, kernel_h, kernel_w, k_pad);
+    else
+      fnn::pad_weights_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(weight, ws.ptr, out_channels, k, k_pad);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     wsrc = ws.ptr;
     w_ld = k_pad;
@@ -878,6 +888,133 @@ extern "C" int fastnn_b200_conv2d_forward(const float* input, const float* weigh
   g_launches.fetch_add(1, std::memory_order_relaxed);
   t_last = LastCall{5, p.block_n, 1, grid};
   return 0;
+}
+
+extern "C" int fastnn_b200_conv2d_forward(const float* input, const float* weight, const float* bias,
+                                          float* output, int batch_size, int in_channels,
+                                          int out_channels, int input_h, int input_w, int kernel_h,
+                                          int kernel_w, int stride_h, int stride_w, int pad_h,
+                                          int pad_w, int act, void* stream) {
+  return conv_forward_impl(input, weight, bias, output, batch_size, in_channels, out_channels, input_h,
+                           input_w, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, act, stream,
+                           false);
+}
+
+// grad_input[n, ci, iy, ix] = sum over (co, ki, kj) of grad_output[n, co, iy + ph - ki, ix + pw - kj]
+// * weight[co, ci, ki, kj] for a stride-1 convolution: with ki' = kh-1-ki this is the forward
+// kernel run on grad_output (co channels in, ci out) with the kernel reversed and padding
+// kh-1-ph.  Strides other than 1 are not covered (-1).
+extern "C" int fastnn_b200_conv2d_backward_data(const float* grad_output, const float* weight,
+                                                float* grad_input, int batch_size, int in_channels,
+                                                int out_channels, int input_h, int input_w,
+                                                int output_h, int output_w, int kernel_h,
+                                                int kernel_w, int stride_h, int stride_w, int pad_h,
+                                                int pad_w, void* stream) {
+  if (stride_h != 1 || stride_w != 1) return -1;
+  if (kernel_h < 1 || kernel_w < 1 || pad_h < 0 || pad_w < 0 || pad_h > kernel_h - 1 ||
+      pad_w > kernel_w - 1)
+    return -1;
+  if (output_h != input_h + 2 * pad_h - kernel_h + 1 || output_w != input_w + 2 * pad_w - kernel_w + 1)
+    return -1;
+  return conv_forward_impl(grad_output, weight, nullptr, grad_input, batch_size, out_channels,
+                           in_channels, output_h, output_w, kernel_h, kernel_w, 1, 1,
+                           kernel_h - 1 - pad_h, kernel_w - 1 - pad_w, 0, stream, true);
+}
+
+// FastNN's own entry (cuda/kernels.cu:949-987): same arguments, default stream.
+extern "C" int fastnn_cuda_conv2d_backward_data(const float* grad_output, const float* weight,
+                                                float* grad_input, int batch_size, int in_channels,
+                                                int out_channels, int input_h, int input_w,
+                                                int output_h, int output_w, int kernel_h,
+                                                int kernel_w, int stride_h, int stride_w, int pad_h,
+                                                int pad_w) {
+  return fastnn_b200_conv2d_backward_data(grad_output, weight, grad_input, batch_size, in_channels,
+                                          out_channels, input_h, input_w, output_h, output_w, kernel_h,
+                                          kernel_w, stride_h, stride_w, pad_h, pad_w, nullptr);
+}
+
+// grad_weight[co, k] = sum over images n and positions p of grad_output[n, co, p] * col[n, p, k].
+// First version, explicit: one im2col launch for all images (position-major), one batched GEMM
+// grad_output[n] . col[n] into per-image partials, one fixed-order sum over the images.
+extern "C" int fastnn_b200_conv2d_backward_weight(const float* input, const float* grad_output,
+                                                  float* grad_weight, int batch_size, int in_channels,
+                                                  int out_channels, int input_h, int input_w,
+                                                  int output_h, int output_w, int kernel_h,
+                                                  int kernel_w, int stride_h, int stride_w, int pad_h,
+                                                  int pad_w, void* stream) {
+  if (batch_size < 0 || in_channels < 1 || out_channels < 1 || input_h < 1 || input_w < 1 ||
+      kernel_h < 1 || kernel_w < 1 || stride_h < 1 || stride_w < 1 || pad_h < 0 || pad_w < 0)
+    return -1;
+  if (input_h + 2 * pad_h < kernel_h || input_w + 2 * pad_w < kernel_w) return -1;
+  if (output_h != (input_h + 2 * pad_h - kernel_h) / stride_h + 1 ||
+      output_w != (input_w + 2 * pad_w - kernel_w) / stride_w + 1)
+    return -1;
+  if (grad_weight == nullptr) return -1;
+  const long long k_ll = 1ll * in_channels * kernel_h * kernel_w;
+  const long long plane = 1ll * output_h * output_w;
+  if (k_ll > (1ll << 24) || plane > (1ll << 24) || 1ll * batch_size * plane * k_ll > (1ll << 34)) return -1;
+  const int k = static_cast<int>(k_ll);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (batch_size == 0) {
+    FNN_CUDA_OK(cudaMemsetAsync(grad_weight, 0, sizeof(float) * out_channels * k_ll, s));
+    return 0;
+  }
+  if (input == nullptr || grad_output == nullptr) return -1;
+  const int ld = ceil_div(k, 4) * 4;                     // 16-byte rows for TMA
+  const size_t col_floats = static_cast<size_t>(batch_size) * plane * ld;
+  const size_t part_floats = static_cast<size_t>(batch_size) * out_channels * k;
+  float* col = nullptr;
+  int num_sms = 0;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState* st = current_state();
+    if (st == nullptr) return -1;
+    num_sms = st->num_sms;
+    Workspace& ws = st->conv_ws[s];
+    const size_t need = sizeof(float) * (col_floats + part_floats + 64);
+    if (ws.bytes < need) {
+      if (ws.ptr) FNN_CUDA_OK(cudaFree(ws.ptr));
+      ws.ptr = nullptr; ws.bytes = 0;
+      FNN_CUDA_OK(cudaMalloc(&ws.ptr, need));
+      ws.bytes = need;
+    }
+    col = ws.ptr;
+  }
+  float* partials = col + ((col_floats + 63) / 64) * 64;  // keeps the 16-byte alignment
+  long long blocks = (static_cast<long long>(col_floats) + 255) / 256;
+  if (blocks > 16ll * num_sms) blocks = 16ll * num_sms;
+  fnn::im2col_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+      input, col, batch_size, in_channels, input_h, input_w, kernel_h, kernel_w, stride_h, stride_w, pad_h,
+      pad_w, output_h, output_w, ld);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  FNN_CUDA_OK(cudaGetLastError());
+  // per image: partial[n][co, k] = grad_output[n][co, P] . col[n][P, k]
+  GemmArgs g{FASTNN_B200_NN, grad_output, col, partials, out_channels, k, static_cast<int>(plane),
+             batch_size, plane, ld, k, 1ll * out_channels * plane, plane * ld, 1ll * out_channels * k,
+             1.0f, 0.0f, nullptr, 0, s};
+  g.force_split_k = 1;
+  const int rc = gemm_dispatch(g);
+  if (rc != 0) return rc;
+  const long long total = 1ll * out_channels * k;
+  long long rblocks = (total + 255) / 256;
+  if (rblocks > 8ll * num_sms) rblocks = 8ll * num_sms;
+  fnn::splitk_reduce_kernel<<<static_cast<unsigned>(rblocks), 256, 0, s>>>(
+      partials, grad_weight, nullptr, out_channels, k, 1, batch_size, k, total, 1.0f, 0.0f, 0);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  FNN_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// FastNN's own entry (cuda/kernels.cu:989-1026): same arguments, default stream.
+extern "C" int fastnn_cuda_conv2d_backward_weight(const float* input, const float* grad_output,
+                                                  float* grad_weight, int batch_size, int in_channels,
+                                                  int out_channels, int input_h, int input_w,
+                                                  int output_h, int output_w, int kernel_h,
+                                                  int kernel_w, int stride_h, int stride_w, int pad_h,
+                                                  int pad_w) {
+  return fastnn_b200_conv2d_backward_weight(input, grad_output, grad_weight, batch_size, in_channels,
+                                            out_channels, input_h, input_w, output_h, output_w, kernel_h,
+                                            kernel_w, stride_h, stride_w, pad_h, pad_w, nullptr);
 }
 
 // FastNN's own entry (cuda/kernels.cu:896-946): same arguments, default stream, no activation.

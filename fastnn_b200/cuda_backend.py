@@ -253,6 +253,28 @@ def conv2d_forward(x, weight, bias=None, stride=(1, 1), padding=(0, 0), act=ACT_
     return y
 
 
+def conv2d_backward(x, weight, grad_output, stride=(1, 1), padding=(0, 0), stream=0):
+    """Conv2dBackward (src/autograd/backward_ops.rs:753-770): returns (grad_input, grad_weight) for
+    x [N,Cin,H,W], weight [Cout,Cin,KH,KW], grad_output [N,Cout,OH,OW].  grad_input needs stride 1
+    (CudaError otherwise); grad_weight takes any stride."""
+    _check(x, "x"); _check(weight, "weight"); _check(grad_output, "grad_output")
+    _ensure_ctx(x)
+    n, ci, h, w = (int(v) for v in x.shape)
+    co, _, kh, kw = (int(v) for v in weight.shape)
+    (sh, sw), (ph, pw) = stride, padding
+    oh, ow = (h + 2 * ph - kh) // sh + 1, (w + 2 * pw - kw) // sw + 1
+    if tuple(grad_output.shape) != (n, co, oh, ow):
+        raise ValueError("grad_output must be [N, Cout, OH, OW]")
+    gi = torch.empty_like(x)
+    gw = torch.empty_like(weight)
+    args = (n, ci, co, h, w, oh, ow, kh, kw, sh, sw, ph, pw, stream)
+    if lib().fastnn_b200_conv2d_backward_data(_ptr(grad_output), _ptr(weight), _ptr(gi), *args) != 0:
+        raise CudaError("CUDA conv2d_backward_data failed")
+    if lib().fastnn_b200_conv2d_backward_weight(_ptr(x), _ptr(grad_output), _ptr(gw), *args) != 0:
+        raise CudaError("CUDA conv2d_backward_weight failed")
+    return gi, gw
+
+
 def rnn_gates_forward(x_t, h, w_ih, w_hh, b_ih=None, b_hh=None, out=None, stream=0):
     """gates = x_t . W_ih^T + h . W_hh^T + b_ih + b_hh in one launch: the gate pre-activations of
     LSTM::forward (src/nn/rnn.rs:72-77) and of the plain RNN cell.  x_t [batch,input] may be a

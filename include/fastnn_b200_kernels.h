@@ -159,6 +159,42 @@ FASTNN_B200_API int fastnn_b200_conv2d_forward(const float* input, const float* 
                                                int kernel_h, int kernel_w, int stride_h, int stride_w,
                                                int pad_h, int pad_w, int act, void* stream);
 
+/* Gradients of that convolution, Conv2dBackward (src/autograd/backward_ops.rs:753-770):
+ *   grad_input[n, ci, ih, iw]  += grad_output[n, co, oh, ow] * weight[co, ci, ki, kj]
+ *   grad_weight[co, ci, ki, kj] += grad_output[n, co, oh, ow] * input[n, ci, ih, iw]
+ * over all (n, co, oh, ow, ci, ki, kj) with ih = oh*stride_h + ki - pad_h inside the image
+ * (likewise iw); both outputs are overwritten, not accumulated into.  The fastnn_cuda_ names keep
+ * FastNN's argument lists (cuda/kernels.cu:949-987 and 989-1026: col2im / im2col + cuBLAS per
+ * image); the _b200_ forms add a stream.
+ * backward_data runs the implicit-GEMM forward kernel on grad_output with the kernel reversed and
+ * channels swapped; it covers stride 1 with pad <= kernel - 1 and returns -1 otherwise.
+ * backward_weight is explicit in this version: one im2col launch for all images, one batched
+ * GEMM into per-image partials, one fixed-order sum (deterministic); any stride. */
+FASTNN_B200_API int fastnn_cuda_conv2d_backward_data(const float* grad_output, const float* weight,
+                                                     float* grad_input, int batch_size, int in_channels,
+                                                     int out_channels, int input_h, int input_w,
+                                                     int output_h, int output_w, int kernel_h,
+                                                     int kernel_w, int stride_h, int stride_w,
+                                                     int pad_h, int pad_w);
+FASTNN_B200_API int fastnn_b200_conv2d_backward_data(const float* grad_output, const float* weight,
+                                                     float* grad_input, int batch_size, int in_channels,
+                                                     int out_channels, int input_h, int input_w,
+                                                     int output_h, int output_w, int kernel_h,
+                                                     int kernel_w, int stride_h, int stride_w,
+                                                     int pad_h, int pad_w, void* stream);
+FASTNN_B200_API int fastnn_cuda_conv2d_backward_weight(const float* input, const float* grad_output,
+                                                       float* grad_weight, int batch_size,
+                                                       int in_channels, int out_channels, int input_h,
+                                                       int input_w, int output_h, int output_w,
+                                                       int kernel_h, int kernel_w, int stride_h,
+                                                       int stride_w, int pad_h, int pad_w);
+FASTNN_B200_API int fastnn_b200_conv2d_backward_weight(const float* input, const float* grad_output,
+                                                       float* grad_weight, int batch_size,
+                                                       int in_channels, int out_channels, int input_h,
+                                                       int input_w, int output_h, int output_w,
+                                                       int kernel_h, int kernel_w, int stride_h,
+                                                       int stride_w, int pad_h, int pad_w, void* stream);
+
 /* Fused attention core, per head h in [0, batch_heads):
  *   O[h] = softmax( scale * Q[h] . K[h]^T + mask ) . V[h]
  * q [batch_heads, t_q, head_dim], k and v [batch_heads, t_k, head_dim], o like q, all dense.

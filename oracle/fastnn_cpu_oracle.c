@@ -220,6 +220,37 @@ ORACLE_API void oracle_conv2d_forward(const float* x, const float* w, const floa
         }
 }
 
+/* Conv2dBackward on CPU tensors, src/autograd/backward_ops.rs:753-770: one pass over
+ * (b, oc, oh, ow, ic, ki, kj) adding go * w into grad_input and go * input into grad_weight
+ * (both start at zero).  gi or gw may be null. */
+ORACLE_API void oracle_conv2d_backward(const float* x, const float* w, const float* go, float* gi,
+                                       float* gw, size_t batch, size_t ci, size_t co, size_t h,
+                                       size_t wd, size_t kh, size_t kw, size_t sh, size_t sw, size_t ph,
+                                       size_t pw) {
+  const size_t oh_n = (h + 2 * ph - kh) / sh + 1;
+  const size_t ow_n = (wd + 2 * pw - kw) / sw + 1;
+  if (gi) for (size_t i = 0; i < batch * ci * h * wd; ++i) gi[i] = 0.0f;
+  if (gw) for (size_t i = 0; i < co * ci * kh * kw; ++i) gw[i] = 0.0f;
+  for (size_t b = 0; b < batch; ++b)
+    for (size_t oc = 0; oc < co; ++oc)
+      for (size_t oh = 0; oh < oh_n; ++oh)
+        for (size_t ow = 0; ow < ow_n; ++ow) {
+          const float g = go[((b * co + oc) * oh_n + oh) * ow_n + ow];
+          for (size_t ic = 0; ic < ci; ++ic)
+            for (size_t ki = 0; ki < kh; ++ki)
+              for (size_t kj = 0; kj < kw; ++kj) {
+                const long ih = (long)(oh * sh + ki) - (long)ph;
+                const long iw = (long)(ow * sw + kj) - (long)pw;
+                if (ih >= 0 && ih < (long)h && iw >= 0 && iw < (long)wd) {
+                  const size_t wi = ((oc * ci + ic) * kh + ki) * kw + kj;
+                  const size_t ii = ((b * ci + ic) * h + (size_t)ih) * wd + (size_t)iw;
+                  if (gi) gi[ii] += g * w[wi];
+                  if (gw) gw[wi] += g * x[ii];
+                }
+              }
+        }
+}
+
 /* ---------------------------------------------------------------------------
  * Attention probabilities used as the left operand of the batched P.V product:
  * scores*scale (src/nn/transformer.rs:94) + additive causal mask 0/-1e9

@@ -14,7 +14,7 @@ from . import build_oracle as _b
 
 __all__ = [
     "rand_data", "matmul", "matmul_nt", "matmul_tn", "matmul_rows", "transpose",
-    "bias_act", "linear", "linear_backward_input", "rnn_gates", "conv2d", "causal_softmax", "attention", "host_threads", "ACT_NONE", "ACT_RELU",
+    "bias_act", "linear", "linear_backward_input", "rnn_gates", "conv2d", "conv2d_backward", "causal_softmax", "attention", "host_threads", "ACT_NONE", "ACT_RELU",
     "ACT_GELU", "ref_gpu_library_path",
 ]
 
@@ -216,6 +216,20 @@ def conv2d(x: np.ndarray, w: np.ndarray, bias, stride=(1, 1), padding=(0, 0)) ->
     lib.oracle_conv2d_forward.restype = None
     lib.oracle_conv2d_forward(_p(x), _p(w), bp, _p(out), n, ci, co, h, wd, kh, kw, sh, sw, ph, pw)
     return out
+
+
+def conv2d_backward(x: np.ndarray, w: np.ndarray, go: np.ndarray, stride=(1, 1), padding=(0, 0)):
+    """``Conv2dBackward`` on CPU tensors (src/autograd/backward_ops.rs:753-770): (grad_input, grad_weight)."""
+    x, w, go = _f32(x), _f32(w), _f32(go)
+    n, ci, h, wd = x.shape
+    co, _, kh, kw = w.shape
+    (sh, sw), (ph, pw) = stride, padding
+    gi, gw = np.empty_like(x), np.empty_like(w)
+    lib = _load()
+    lib.oracle_conv2d_backward.argtypes = [_fp] * 5 + [_sz] * 11
+    lib.oracle_conv2d_backward.restype = None
+    lib.oracle_conv2d_backward(_p(x), _p(w), _p(go), _p(gi), _p(gw), n, ci, co, h, wd, kh, kw, sh, sw, ph, pw)
+    return gi, gw
 
 
 def rnn_gates(x_t: np.ndarray, h: np.ndarray, w_ih: np.ndarray, w_hh: np.ndarray, b_ih, b_hh) -> np.ndarray:

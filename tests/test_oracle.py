@@ -185,6 +185,24 @@ def test_conv2d_loops_against_a_direct_float64_sum():
     assert np.abs(y - ref).max() < 1e-5
 
 
+def test_conv2d_backward_is_the_adjoint_of_the_forward_loops():
+    """<grad_input, x'> = <go, conv(x', w)> and <grad_weight, w'> = <go, conv(x, w')> for any x', w'."""
+    rng = np.random.default_rng(43)
+    x = rng.standard_normal((2, 3, 8, 7), dtype=np.float32)
+    w = rng.standard_normal((4, 3, 3, 2), dtype=np.float32)
+    stride, padding = (2, 1), (1, 0)
+    go = rng.standard_normal(oracle.conv2d(x, w, None, stride, padding).shape, dtype=np.float32)
+    gi, gw = oracle.conv2d_backward(x, w, go, stride, padding)
+    x2 = rng.standard_normal(x.shape, dtype=np.float32)
+    w2 = rng.standard_normal(w.shape, dtype=np.float32)
+    lhs_i = float((gi.astype(np.float64) * x2).sum())
+    rhs_i = float((go.astype(np.float64) * oracle.conv2d(x2, w, None, stride, padding)).sum())
+    lhs_w = float((gw.astype(np.float64) * w2).sum())
+    rhs_w = float((go.astype(np.float64) * oracle.conv2d(x, w2, None, stride, padding)).sum())
+    assert abs(lhs_i - rhs_i) <= 1e-3 * max(1.0, abs(rhs_i))
+    assert abs(lhs_w - rhs_w) <= 1e-3 * max(1.0, abs(rhs_w))
+
+
 def test_causal_softmax_rows():
     rng = np.random.default_rng(2)
     s = rng.standard_normal((3, 8, 8), dtype=np.float32)
