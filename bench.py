@@ -889,8 +889,28 @@ def run_conv2d(args, local_rank):
         ref_us = timed(lambda: ref.fastnn_cuda_conv2d_forward(
             vp(x.data_ptr()), vp(wt.data_ptr()), vp(0), vp(y2.data_ptr()), ci_t(n), ci_t(ci), ci_t(co),
             ci_t(h), ci_t(w), ci_t(kh), ci_t(kw), ci_t(1), ci_t(1), ci_t(pad), ci_t(pad)), reps=3)
+    # gradients: ours against FastNN's CUDA entries (col2im / im2col + cuBLAS per image) and cuDNN
+    go = torch.randn(n, co, h, w, device="cuda", generator=gen)
+    gi, gw = torch.empty_like(x), torch.empty_like(wt)
+    lib = f.lib()
+    vpp = lambda t: ctypes.c_void_p(t.data_ptr())
+    dims = (n, ci, co, h, w, h, w, kh, kw, 1, 1, pad, pad)
+    bwd_data = timed(lambda: lib.fastnn_b200_conv2d_backward_data(vpp(go), vpp(wt), vpp(gi), *dims, None))
+    bwd_weight = timed(lambda: lib.fastnn_b200_conv2d_backward_weight(vpp(x), vpp(go), vpp(gw), *dims, None))
+    cudnn_bwd = timed(lambda: torch.ops.aten.convolution_backward(
+        go, x, wt, None, [1, 1], [pad, pad], [1, 1], False, [0, 0], 1, [True, True, False]))
+    ref_bd = ref_bw = None
+    if path is not None:
+        ci_t = ctypes.c_int
+        idims = [ci_t(v) for v in dims]
+        gi2, gw2 = torch.empty_like(x), torch.empty_like(wt)
+        ref_bd = timed(lambda: ref.fastnn_cuda_conv2d_backward_data(vpp(go), vpp(wt), vpp(gi2), *idims), reps=3)
+        ref_bw = timed(lambda: ref.fastnn_cuda_conv2d_backward_weight(vpp(x), vpp(go), vpp(gw2), *idims), reps=3)
     assert f.device_status() == 0
     print(json.dumps({
+        "backward_data_us": bwd_data, "backward_weight_us": bwd_weight,
+        "cudnn_backward_both_us": cudnn_bwd, "fastnn_cuda_backward_data_us": ref_bd,
+        "fastnn_cuda_backward_weight_us": ref_bw,
         "impl": "conv2d", "shape": f"N{n} C{ci}->{co} {h}x{w} k{kh}x{kw} p{pad}", "ours_us": ours,
         "ours_tflops": flops / ours / 1e6, "cudnn_tf32_us": cudnn, "cudnn_tflops": flops / cudnn / 1e6,
         "fastnn_cuda_entry_us_without_bias": ref_us, "rel_diff_vs_cudnn": rel,
