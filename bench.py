@@ -171,8 +171,8 @@ def run_ours(args, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     f.cuda_init(local_rank)
-    if args.policy:
-        f.set_policy(args.policy, 0, 0)
+    if args.policy or args.block_n or args.split_k:
+        f.set_policy(args.policy, args.block_n, args.split_k)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     scale = (1.0 / world) if (args.scaling == "strong" and world > 1) else 1.0
@@ -250,12 +250,15 @@ def run_ours(args, rank, world, local_rank):
     # per-GEMM device time (own events, after the headline region) for the roofline entry
     per_gemm = []
     kernel_names = []
+    plans = {}
     for op in ops:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         reps = max(3, min(20, args.steps))
         launch(*op)
-        kernel_names.append({1: "gemm_simt_kernel", 2: "gemm_tf32_kernel",
-                             3: "gemm_tf32_pair_kernel"}.get(f.last_path()["path"], "?"))
+        lp = f.last_path()
+        kernel_names.append({1: "gemm_simt_kernel", 2: "gemm_tf32_kernel", 3: "gemm_tf32_pair_kernel",
+                             6: "gemm_tf32_clusterk_kernel"}.get(lp["path"], "?"))
+        plans[op[0]["label"]] = f"{kernel_names[-1]} bn{lp['block_n']} k/{lp['split_k']} ctas{lp['num_ctas']}"
         torch.cuda.synchronize()
         e0.record()
         for _ in range(reps):
@@ -468,6 +471,7 @@ def run_ours(args, rank, world, local_rank):
                          "copies totalling >= 384 MB between reuses" % (sum(gemm_bytes(s) for s in spec) / 1e6))},
         "per_gemm_ms": {s["label"]: t for s, t in zip(spec, per_gemm)},
         "per_gemm_tflops": {s["label"]: gemm_flops(s) / (t * 1e-3) / 1e12 for s, t in zip(spec, per_gemm)},
+        "plans": plans,
         "per_gemm_graph_us": ({s["label"]: t * 1e3 for s, t in zip(spec, per_gemm_graph)}
                               if per_gemm_graph else None),
         "per_gemm_graph_gbs": ({s["label"]: gemm_bytes(s) / (t * 1e-3) / 1e9
@@ -500,6 +504,16 @@ TRAFFIC_BYTES = {
     ("square4096", "gemm_tf32_kernel", "NN"): 2.93e8 + 0.51e8,
     ("square4096", "gemm_tf32_kernel", "NT"): 2.95e8 + 0.53e8,
     ("square4096", "gemm_tf32_kernel", "TN"): 2.93e8 + 0.51e8,
+    # HBM-bound shapes: reads equal the operand bytes; the outputs (8-34 MB) stay in L2 as dirty
+    # lines past the end of the launch, so the captured write side is 0
+    ("char_lm", "gemm_tf32_kernel", "qkv fwd"): 9257728, ("char_lm", "gemm_tf32_kernel", "qkv dX"): 26034176,
+    ("char_lm", "gemm_tf32_kernel", "qkv dW"): 33636096, ("char_lm", "gemm_tf32_kernel", "o fwd"): 8732416,
+    ("char_lm", "gemm_tf32_kernel", "o dX"): 8732160, ("char_lm", "gemm_tf32_kernel", "o dW"): 16859136,
+    ("char_lm", "gemm_tf32_kernel", "ff1 fwd"): 9519360, ("char_lm", "gemm_tf32_kernel", "ff1 dX"): 34684672,
+    ("char_lm", "gemm_tf32_kernel", "ff1 dW"): 42024448 + 768, ("char_lm", "gemm_tf32_kernel", "ff2 fwd"): 34685440,
+    ("char_lm", "gemm_tf32_kernel", "ff2 dX"): 9519104, ("char_lm", "gemm_tf32_kernel", "ff2 dW"): 42025216 + 1536,
+    ("attention", "gemm_tf32_kernel", "S=Q.K^T"): 16859136, ("attention", "gemm_tf32_kernel", "O=P.V"): 42024960,
+    ("mnist_l1", "gemm_tf32_clusterk_kernel", "layer1"): 2459904,
 }
 
 
@@ -928,7 +942,10 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--gather", action="store_true")
     ap.add_argument("--policy", type=int, default=0,
-                    help="kernel choice for sweeps: 0 planner, 3 single CTAs only, 4 CTA pairs only")
+                    help="kernel choice for sweeps: 0 planner, 3 single CTAs only, 4 CTA pairs only, "
+                         "5 K-split clusters (--split-k = cluster size), 6 planner without them")
+    ap.add_argument("--block-n", type=int, default=0, help="tile width for sweeps (0 = planner)")
+    ap.add_argument("--split-k", type=int, default=0, help="K split for sweeps (0 = planner)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)

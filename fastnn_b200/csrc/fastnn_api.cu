@@ -26,6 +26,7 @@ using fnn::GemmParams;
 
 constexpr int kMaxDevices = 16;
 constexpr size_t kMaxDynSmem = 232448;   // 227 KiB, the sm_100 per-CTA limit
+constexpr size_t kCkHalfSmem = 112 * 1024;   // two such CTAs share an SM
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -41,6 +42,9 @@ struct DeviceState {
   bool ready = false;
   int num_sms = 0;
   int max_clusters = 0;             // co-resident CTA pairs of the pair kernel
+  int ck_slots[5] = {0, 0, 0, 0, 0};  // co-resident CTAs of the cluster split-K kernel at cluster
+                                    // size 2^i (index 0 unused); 0 = that size cannot launch
+  int ck_slots_half[5] = {0, 0, 0, 0, 0};   // the same when a CTA asks for at most kCkHalfSmem
   unsigned int* status = nullptr;   // device word written by a kernel whose wait ran out
   long long spin_budget = 0;        // clock ticks one wait may last
   std::map<cudaStream_t, Workspace> workspaces;   // split-K partials, one per stream
@@ -121,7 +125,14 @@ bool encode_map4(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, u
 struct Plan {
   int block_n, split_k, stages;
   bool pair;                        // 256 x block_n tiles on CTA pairs (cta_group::2)
+  bool cluster_k = false;           // the K slices of a tile are the CTAs of one cluster
 };
+
+inline int log2_exact(int v) {      // 1 -> 0, 2 -> 1, 4 -> 2, 8 -> 3, 16 -> 4, anything else -1
+  for (int i = 0; i <= 4; ++i)
+    if (v == (1 << i)) return i;
+  return -1;
+}
 
 // Cycle model used to pick the tile shape and the K split.  Per 32-deep k-block (four MMAs) a
 // CTA is bound either by the tensor pipe (block_n / 2 cycles at 4096 dense TF32 flop/clk/SM) or by
@@ -130,7 +141,9 @@ struct Plan {
 // extent not a multiple of 32, so the single-box chunked view does not apply).  A CTA pair
 // computes 256 x block_n with each CTA reading only half of B.
 Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, bool a_mn,
-                 bool b_mn, int pair_mode /* 0 auto, 1 never, 2 always */) {
+                 bool b_mn, int pair_mode /* 0 auto, 1 never, 2 always */,
+                 const int* ck_slots = nullptr /* DeviceState::ck_slots, or null: no cluster split-K */,
+                 const int* ck_slots_half = nullptr) {
   const int num_kb = ceil_div(k, fnn::kBlockK);
   const int n32 = ceil_div(n, 32) * 32;
   const double out_bytes = 4.0 * m * n * batch;
@@ -193,6 +206,39 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
           best.block_n = bn;
           best.split_k = real_split;
           best.pair = pair != 0;
+          best.cluster_k = false;
+        }
+      }
+      // The same K splits with the slices of a tile as one cluster (single CTAs, portable cluster
+      // sizes): no partial tiles in global memory and no reduce launch; instead each CTA drains
+      // its accumulator to shared memory and reads 512 * bn bytes from its cluster peers.
+      for (int lg = 1; lg <= 3 && pair == 0 && ck_slots != nullptr; ++lg) {
+        const int sk = 1 << lg;
+        if (ck_slots[lg] < sk || num_kb < 2 * sk) continue;
+        const long long units = 1ll * batch * tiles_m * tiles_n * sk;
+        // a short slice needs few stages: such CTAs fit two to an SM
+        const size_t stage_b = fnn::kStageABytes + static_cast<size_t>(bn) * fnn::kBlockK * 4;
+        const size_t partial = static_cast<size_t>(fnn::kBlockM) * fnn::cluster_partial_pitch(bn);
+        size_t st_need = static_cast<size_t>(ceil_div(num_kb, sk) < 2 ? 2 : ceil_div(num_kb, sk));
+        if (st_need * stage_b < partial) st_need = (partial + stage_b - 1) / stage_b;
+        const bool half = ck_slots_half != nullptr && ck_slots_half[lg] > ck_slots[lg] &&
+                          fnn::gemm_clusterk_smem_bytes(bn, static_cast<int>(st_need)) <= kCkHalfSmem &&
+                          bn <= 256;
+        const int slots_ck = half ? ck_slots_half[lg] : ck_slots[lg];
+        const double waves = static_cast<double>((units + slots_ck - 1) / slots_ck);
+        const double imbalance = waves * slots_ck / units;
+        const double t_hbm = (in_bytes + out_bytes) / hbm_per_clk * imbalance;
+        const double t_cmp = waves * ceil_div(num_kb, sk) * t_kb;
+        // measured on 512 x 256 x 784: two cluster barriers, the drain to shared memory and the
+        // peer reads cost more the larger the cluster (its CTAs start and finish further apart)
+        double cycles = (t_hbm > t_cmp ? t_hbm : t_cmp) + waves * (800.0 + 1500.0 + 300.0 * sk + 8.0 * bn);
+        cycles *= 1.0 + 1e-4 * (8 - bn / 32) + 1e-3 * (sk - 1);
+        if (cycles < best_cost) {
+          best_cost = cycles;
+          best.block_n = bn;
+          best.split_k = sk;
+          best.pair = false;
+          best.cluster_k = true;
         }
       }
     }
@@ -282,21 +328,39 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   const bool a_mn = (g.layout == FASTNN_B200_TN) && ((g.m % 32) != 0 || no_chunk);
   const bool b_mn = (g.layout != FASTNN_B200_NT) && ((g.n % 32) != 0 || no_chunk);
   const bool dual = g.a2 != nullptr;       // C = A.B + A2.B2: single-CTA kernel, one K range
-  const int pair_mode = dual ? 1 : (pol.policy == 3 ? 1 : (pol.policy == 4 ? 2 : 0));
-  Plan plan = choose_plan(g.m, g.n, g.k + (dual ? g.k2 : 0), g.batch, st->num_sms, st->max_clusters,
-                          a_mn, b_mn, pair_mode);
-  if (pol.block_n > 0) plan.block_n = pol.block_n;
-  if (pol.split_k > 0) plan.split_k = pol.split_k;
+  const int pair_mode = dual ? 1 : ((pol.policy == 3 || pol.policy >= 5) ? 1 : (pol.policy == 4 ? 2 : 0));
   // the backward epilogue is not linear in the partial sums, and the column sums use the workspace
   const bool backward = g.aux != nullptr || g.colsum != nullptr;
+  // cluster split-K writes C itself: not for callers that want the raw partial tiles
+  static const bool ck_env_off = [] {
+    const char* e = std::getenv("FASTNN_B200_CLUSTER_K");
+    return e != nullptr && std::atoi(e) == 0;
+  }();
+  const bool ck_allowed = !backward && g.force_split_k == 0 && pol.policy != 6 && pol.policy != 3 &&
+                          pol.policy != 4 && !ck_env_off;
+  Plan plan = choose_plan(g.m, g.n, g.k + (dual ? g.k2 : 0), g.batch, st->num_sms, st->max_clusters,
+                          a_mn, b_mn, pair_mode, ck_allowed ? st->ck_slots : nullptr, st->ck_slots_half);
+  if (pol.block_n > 0) plan.block_n = pol.block_n;
+  if (pol.split_k > 0) { plan.split_k = pol.split_k; plan.cluster_k = false; }
+  if (pol.policy == 5) plan.cluster_k = ck_allowed;            // forced: split_k is the cluster size
   if (backward) plan.split_k = 1;
   if (g.force_split_k > 0) plan.split_k = g.force_split_k;
   if (plan.pair && (plan.block_n % 64) != 0) plan.block_n = ceil_div(plan.block_n, 64) * 64;
   const int num_kb1 = ceil_div(g.k, fnn::kBlockK);
   const int num_kb = num_kb1 + (dual ? ceil_div(g.k2, fnn::kBlockK) : 0);
   if (plan.split_k > num_kb) plan.split_k = num_kb;
+  if (plan.cluster_k) {
+    // a cluster size the device can place, every slice at least one k-block, and a partial tile
+    // that fits the stage ring it is written over; otherwise the workspace form of the same split
+    const int lg = log2_exact(plan.split_k);
+    const int st_n = stages_for(plan.block_n);
+    const size_t ring = static_cast<size_t>(st_n) * (fnn::kStageABytes + plan.block_n * fnn::kBlockK * 4);
+    if (plan.pair || lg < 1 || st->ck_slots[lg] < plan.split_k || num_kb < plan.split_k ||
+        static_cast<size_t>(fnn::kBlockM) * fnn::cluster_partial_pitch(plan.block_n) > ring)
+      plan.cluster_k = false;
+  }
   const int kbps = ceil_div(num_kb, plan.split_k);
-  plan.split_k = ceil_div(num_kb, kbps);
+  if (!plan.cluster_k) plan.split_k = ceil_div(num_kb, kbps);
   // CTA pairs with wide tiles take two k-blocks per stage: the issuing thread's per-stage
   // cost (wait, commit, loop) is then paid once per eight MMAs instead of once per four
   int kb_per_stage = (plan.pair && plan.block_n == 256 && kbps >= 8) ? 2 : 1;
@@ -309,6 +373,31 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   if (const char* e = std::getenv("FASTNN_B200_STAGES")) {
     const int s = std::atoi(e);
     if (s >= 1 && s < plan.stages) plan.stages = s;
+  }
+  // A cluster split-K CTA lives for one K slice: no more stages than the slice has k-blocks (but
+  // a ring that holds the partial tile), and one accumulator.  The smaller footprint lets CTAs of
+  // consecutive launches, or of two clusters, share an SM.  TMEM allocation blocks until columns
+  // are free, and a CTA waiting there while a cluster peer on the same SM waits for it at the
+  // cluster barrier would never get them: the shared-memory request is kept large enough that the
+  // CTAs that fit one SM never ask for more than the 512 columns together.
+  int ck_tmem_cols = 0;
+  size_t ck_smem = 0;
+  if (plan.cluster_k) {
+    const size_t stage_b = fnn::kStageABytes + static_cast<size_t>(plan.block_n) * fnn::kBlockK * 4;
+    const size_t partial = static_cast<size_t>(fnn::kBlockM) * fnn::cluster_partial_pitch(plan.block_n);
+    const int for_partial = static_cast<int>((partial + stage_b - 1) / stage_b);
+    int want = ceil_div(num_kb, plan.split_k);
+    if (want < 2) want = 2;
+    if (want < for_partial) want = for_partial;
+    if (want < plan.stages) plan.stages = want;
+    if (plan.stages < for_partial) plan.stages = for_partial;
+    ck_tmem_cols = 32;
+    while (ck_tmem_cols < plan.block_n) ck_tmem_cols *= 2;
+    ck_smem = fnn::gemm_clusterk_smem_bytes(plan.block_n, plan.stages);
+    const size_t sm_smem = 228 * 1024;                      // per SM, 1 KiB reserved per CTA
+    const size_t ctas_ok = 512 / ck_tmem_cols;              // CTAs whose accumulators fit together
+    const size_t floor_bytes = sm_smem / (ctas_ok + 1) + 1; // ctas_ok + 1 of these do not fit
+    if (ck_smem < floor_bytes) ck_smem = floor_bytes;
   }
 
   GemmParams p;
@@ -351,7 +440,11 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   float* out = g.c;
   long long out_ld = g.ldc, out_bs = g.sc;
   long long out_z = g.batch;
-  if (plan.split_k > 1) {
+  p.cluster_k = plan.cluster_k ? 1 : 0;
+  p.tmem_cols = ck_tmem_cols;
+  p.cluster_vec = (plan.cluster_k && (g.n & 3) == 0 && aligned16(g.c) && (g.ldc & 3) == 0 &&
+                   (g.batch == 1 || (g.sc & 3) == 0)) ? 1 : 0;
+  if (plan.split_k > 1 && !plan.cluster_k) {
     const size_t need = sizeof(float) * static_cast<size_t>(g.m) * g.n * g.batch * plan.split_k;
     Workspace& ws = st->workspaces[g.stream];
     if (ws.bytes < need) {
@@ -379,7 +472,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     }
     p.colsum = ws.ptr;
   }
-  const bool tma_store = aligned16(out) && (out_ld & 3) == 0 && (out_z == 1 || (out_bs & 3) == 0) &&
+  const bool tma_store = !plan.cluster_k && aligned16(out) && (out_ld & 3) == 0 && (out_z == 1 || (out_bs & 3) == 0) &&
                          (plan.split_k > 1 || g.beta == 0.0f) && out_ld < (1ll << 38) &&
                          out_bs < (1ll << 38);
   p.store_mode = tma_store ? 0 : 1;
@@ -443,6 +536,25 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     grid = 2 * clusters;
     const size_t smem = fnn::gemm_pair_smem_bytes(plan.block_n, plan.stages, kb_per_stage);
     fnn::gemm_tf32_pair_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, p);
+  } else if (plan.cluster_k) {
+    // one CTA per unit, the split_k slices of a tile as one cluster; also a programmatic dependent
+    grid = p.total_units;
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(fnn::kNumThreadsWide, 1, 1);
+    cfg.dynamicSmemBytes = ck_smem;
+    cfg.stream = g.stream;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = static_cast<unsigned>(plan.split_k);
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 2;
+    FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::gemm_tf32_clusterk_kernel, tmA, tmB, tmC, tmA2, tmB2, p));
   } else {
     grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
     const size_t smem = fnn::gemm_smem_bytes(plan.block_n, plan.stages);
@@ -477,7 +589,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   g_launches.fetch_add(1, std::memory_order_relaxed);
   FNN_CUDA_OK(cudaGetLastError());
 
-  if (plan.split_k > 1) {
+  if (plan.split_k > 1 && !plan.cluster_k) {
     const long long total = 1ll * g.m * g.n * g.batch;
     const bool vec = (g.n & 3) == 0 && aligned16(g.c) && (g.ldc & 3) == 0 && (g.sc & 3) == 0 &&
                      (g.bias == nullptr || aligned16(g.bias)) &&
@@ -515,7 +627,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
     FNN_CUDA_OK(cudaGetLastError());
   }
-  t_last = LastCall{plan.pair ? 3 : 2, plan.block_n, plan.split_k, grid};
+  t_last = LastCall{plan.pair ? 3 : (plan.cluster_k ? 6 : 2), plan.block_n, plan.split_k, grid};
   return 0;
 }
 
@@ -589,6 +701,30 @@ extern "C" int fastnn_cuda_init(int device_id) {
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
   st.num_sms = prop.multiProcessorCount;
+  FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_clusterk_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kMaxDynSmem)));
+  for (int pass = 0; pass < 2; ++pass)
+  for (int lg = 1; lg <= 3; ++lg) {
+    // how many CTAs of the cluster split-K kernel fit at once at cluster size 2, 4, 8 (a cluster
+    // inside one GPC), with one CTA per SM and with two
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(((2 * prop.multiProcessorCount) >> lg) << lg, 1, 1);
+    cfg.blockDim = dim3(fnn::kNumThreadsWide, 1, 1);
+    cfg.dynamicSmemBytes = pass == 0 ? kMaxDynSmem : kCkHalfSmem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 1u << lg; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, fnn::gemm_tf32_clusterk_kernel, &cfg) != cudaSuccess) {
+      (void)cudaGetLastError();
+      clusters = 0;
+    }
+    (pass == 0 ? st.ck_slots : st.ck_slots_half)[lg] = clusters << lg;
+  }
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_pair_kernel,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
@@ -1123,7 +1259,7 @@ extern "C" int fastnn_b200_reduce_partials(const float* partials, float* c, int 
 }
 
 extern "C" int fastnn_b200_set_policy(int policy, int block_n, int split_k) {
-  if (policy < 0 || policy > 4) return -1;
+  if (policy < 0 || policy > 6) return -1;
   if (block_n < 0 || block_n > fnn::kMaxBlockN || (block_n % 32) != 0) return -1;
   if (split_k < 0) return -1;
   std::lock_guard<std::mutex> lock(g_mutex);

@@ -64,6 +64,10 @@ struct GemmParams {
   int num_kb1;         // k-blocks read through the first pair of tensor maps (= num_kb normally)
   int split_k;         // >= 1
   int kb_per_split;
+  int cluster_k;       // 1: the split_k CTAs of a tile form a thread-block cluster and add their
+                       // partial tiles through distributed shared memory (gemm_tf32_clusterk_kernel)
+  int cluster_vec;     // that kernel may store float4s: n, ldc, batch stride multiples of 4, C aligned
+  int tmem_cols;       // that kernel's TMEM allocation: one accumulator, a power of two >= block_n
   int kb_per_stage;    // 32-deep k-blocks per pipeline stage (CTA-pair kernel only; else 1)
   int total_units;     // batch * tiles_m * tiles_n * split_k
   int a_mn_major;      // A stored [k, m]
@@ -394,10 +398,22 @@ __device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const C
                          c_first, c_step, nbuf);
 }
 
-__global__ void __launch_bounds__(kNumThreadsWide, 1)
-gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmA2,
-                 const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ GemmParams p) {
+// Pitch in bytes of one row of the partial tile a cluster split-K CTA leaves in shared memory:
+// four floats of padding keep both the row-per-lane writes and the row-wise reads conflict-free.
+__host__ __device__ constexpr uint32_t cluster_partial_pitch(int block_n) {
+  return static_cast<uint32_t>(block_n + 4) * 4u;
+}
+
+// kClusterK = false: the persistent kernel described at the top of this file.
+// kClusterK = true: one work unit per CTA, launched with cluster dimension split_k.  The CTAs
+// of a cluster hold the K slices of one output tile; each leaves its accumulator in its own
+// shared memory, and after a cluster barrier CTA r adds rows [r, r+1) * 128 / split_k of all
+// slices in ascending slice order (deterministic) over distributed shared memory, applies
+// alpha / beta / bias / activation and writes C.  No workspace, no second kernel.
+template <bool kClusterK>
+__device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
+                                               const CUtensorMap& tmC, const CUtensorMap& tmA2,
+                                               const CUtensorMap& tmB2, const GemmParams& p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 B.
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -413,7 +429,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t stage_b_bytes = static_cast<uint32_t>(p.block_n) * kBlockK * 4;
   const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
   const uint32_t staging_base = smem_base + p.num_stages * stage_bytes;
-  const uint32_t bar_base = staging_base + kStagingBytes;
+  const uint32_t bar_base = staging_base + (kClusterK ? 0u : kStagingBytes);   // no staging tiles there
   // barrier layout: full[8] empty[8] tmem_full[2] tmem_empty[2] | tmem address | abort flag
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 64u + 8u * s; };
@@ -458,6 +474,18 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   };
 
+  // k-blocks [kb0, kb1) of unit w.  The cluster form spreads them evenly (every slice non-empty
+  // whenever num_kb >= split_k, which the host guarantees).
+  auto kb_range = [&](const Unit& w, int& kb0, int& kb1) {
+    if constexpr (kClusterK) {
+      kb0 = static_cast<int>(static_cast<long long>(w.s) * p.num_kb / p.split_k);
+      kb1 = static_cast<int>(static_cast<long long>(w.s + 1) * p.num_kb / p.split_k);
+    } else {
+      kb0 = w.s * p.kb_per_split;
+      kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+    }
+  };
+
   int pre_issued = 0;                 // stages of the first unit loaded before the CTA-wide sync
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.num_stages; ++s) {
@@ -487,14 +515,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint64_t pol_a = ptx::make_l2_policy(p.l2_a);
       const uint64_t pol_b = ptx::make_l2_policy(p.l2_b);
       const Unit w = decode_unit(p, blockIdx.x);
-      const int kb0 = w.s * p.kb_per_split;
-      const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+      int kb0, kb1;
+      kb_range(w, kb0, kb1);
       pre_issued = min(p.num_stages, kb1 - kb0);
       for (int i = 0; i < pre_issued; ++i) issue_stage(w, kb0 + i, i, pol_a, pol_b);
     }
   }
   if (warp == 1) {
-    ptx::tmem_alloc_1cta(tmem_slot, kTmemCols);
+    ptx::tmem_alloc_1cta(tmem_slot, kClusterK ? static_cast<uint32_t>(p.tmem_cols) : kTmemCols);
     ptx::tmem_relinquish_1cta();
   }
   ptx::tc_fence_before_sync();
@@ -512,8 +540,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint64_t pol_b = ptx::make_l2_policy(p.l2_b);
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         const Unit w = decode_unit(p, u);
-        const int kb0 = w.s * p.kb_per_split;
-        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        int kb0, kb1;
+        kb_range(w, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (pre_issued > 0) {
             --pre_issued;                         // loaded before the sync, into this same stage
@@ -556,8 +584,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t ready = 0;                          // early probe result for the current stage
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         const Unit w = decode_unit(p, u);
-        const int kb0 = w.s * p.kb_per_split;
-        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        int kb0, kb1;
+        kb_range(w, kb0, kb1);
         ok = wait_barrier(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout);
         if (!ok) break;
         ptx::tc_fence_after_sync();                  // orders the epilogue's TMEM reads before us
@@ -607,6 +635,27 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int buf = 0;
     bool ok = true;
     const bool raw = p.split_k > 1;                 // partial sums: no scale / bias / activation
+    if constexpr (kClusterK) {
+      // One unit.  The accumulator goes, unscaled, to a row-major partial tile at the start of
+      // the stage ring: every stage has been consumed once the accumulator is complete.
+      ok = wait_barrier(tfull_bar(0), 0u, abort_flag, p, kStatusEpilogueTimeout);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        ptx::tc_fence_after_sync();
+        const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        uint8_t* prow = smem_gen + static_cast<size_t>(q * 32 + lane) * cluster_partial_pitch(p.block_n);
+        for (int c = group; c < p.block_n / 32; c += groups) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(taddr0 + c * 32, r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(prow + c * 128 + j * 16) =
+                make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        }
+        ptx::tc_fence_before_sync();
+      }
+    } else
     for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
       const Unit w = decode_unit(p, u);
       const int m0 = w.mt * kBlockM + q * 32;
@@ -635,6 +684,69 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (p.store_mode == 0 && lane == 0) ptx::tma_store_wait_all<0>();
   }
 
+  if constexpr (kClusterK) {
+    // ------------------------------------------- cluster reduction + epilogue ---
+    // Every thread of every CTA of the cluster passes both barriers, aborting or not, so no CTA
+    // waits for one that has left, and none leaves while its shared memory is still being read.
+    __syncwarp();
+    ptx::cluster_arrive_release();
+    ptx::cluster_wait_acquire();
+    if (warp >= kEpilogueWarp0 && !*abort_flag) {
+      const int split = p.split_k;                         // = cluster size: 2, 4, 8 or 16
+      const int rank = static_cast<int>(ptx::cluster_ctarank());
+      const int rows_per = kBlockM / split;
+      const int n4 = p.block_n >> 2;
+      const int nthr = n_epi_warps * 32;
+      const Unit w = decode_unit(p, blockIdx.x);
+      const uint32_t pitch = cluster_partial_pitch(p.block_n);
+      float* cbase = p.c + static_cast<long long>(w.b) * p.c_batch_stride;
+      for (int idx = static_cast<int>(threadIdx.x) - kEpilogueWarp0 * 32; idx < rows_per * n4; idx += nthr) {
+        const int rr = rank * rows_per + idx / n4;
+        const int c4 = idx - (idx / n4) * n4;
+        const int gr = w.mt * kBlockM + rr;
+        const int gc = w.nt * p.block_n + c4 * 4;
+        if (gr >= p.m || gc >= p.n) continue;
+        const uint32_t local = smem_base + static_cast<uint32_t>(rr) * pitch + static_cast<uint32_t>(c4) * 16u;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < split; ++s) {
+          const float4 t = ptx::ld_shared_cluster_f4(ptx::mapa_shared(local, static_cast<uint32_t>(s)));
+          acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+        }
+        float v[4] = {p.alpha * acc.x, p.alpha * acc.y, p.alpha * acc.z, p.alpha * acc.w};
+        float* dst = cbase + static_cast<long long>(gr) * p.ldc + gc;
+        if (p.cluster_vec) {
+          if (p.beta != 0.0f) {
+            const float4 o = *reinterpret_cast<const float4*>(dst);
+            v[0] += p.beta * o.x; v[1] += p.beta * o.y; v[2] += p.beta * o.z; v[3] += p.beta * o.w;
+          }
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] += __ldg(p.bias + gc + j);
+          }
+          if (p.bias2 != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] += __ldg(p.bias2 + gc + j);
+          }
+          *reinterpret_cast<float4*>(dst) = make_float4(apply_act(v[0], p.act), apply_act(v[1], p.act),
+                                                        apply_act(v[2], p.act), apply_act(v[3], p.act));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (gc + j >= p.n) break;
+            float x = v[j];
+            if (p.beta != 0.0f) x += p.beta * dst[j];
+            if (p.bias != nullptr) x += __ldg(p.bias + gc + j);
+            if (p.bias2 != nullptr) x += __ldg(p.bias2 + gc + j);
+            dst[j] = apply_act(x, p.act);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    ptx::cluster_arrive_release();
+    ptx::cluster_wait_acquire();
+  }
+
   // ---------------------------------------------------------------- teardown ---
   __syncwarp();
   if (*abort_flag) {
@@ -646,8 +758,27 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc_1cta(tmem_base, kTmemCols);
+    ptx::tmem_dealloc_1cta(tmem_base, kClusterK ? static_cast<uint32_t>(p.tmem_cols) : kTmemCols);
   }
+}
+
+__global__ void __launch_bounds__(kNumThreadsWide, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmA2,
+                 const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ GemmParams p) {
+  gemm_tf32_body<false>(tmA, tmB, tmC, tmA2, tmB2, p);
+}
+
+__global__ void __launch_bounds__(kNumThreadsWide, 1)
+gemm_tf32_clusterk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                          const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmA2,
+                          const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ GemmParams p) {
+  gemm_tf32_body<true>(tmA, tmB, tmC, tmA2, tmB2, p);
+}
+
+// Bytes of dynamic shared memory the cluster split-K kernel needs (no staging tiles).
+inline size_t gemm_clusterk_smem_bytes(int block_n, int num_stages) {
+  return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + block_n * kBlockK * 4) + kBarrierBytes;
 }
 
 // Bytes of dynamic shared memory a launch with these parameters needs.

@@ -263,13 +263,17 @@ FASTNN_B200_API int fastnn_b200_memcpy_d2h_async(float* dst, const float* src, s
 /* Kernel selection for tests and sweeps.  policy: 0 = automatic (tcgen05 path whenever the
  * operands meet TMA's 16-byte alignment rules, SIMT path otherwise), 1 = SIMT path only,
  * 2 = tcgen05 path only (calls that cannot use it fail with -1), 3 = tcgen05 with single-CTA
- * 128-row tiles only, 4 = tcgen05 with CTA-pair 256-row tiles only.
+ * 128-row tiles only, 4 = tcgen05 with CTA-pair 256-row tiles only, 5 = single-CTA tiles with the
+ * K split done inside thread-block clusters (split_k = cluster size 2, 4 or 8; a call it cannot
+ * serve -- fewer 32-deep k-blocks than split_k, a backward epilogue -- takes the workspace form
+ * of the same split), 6 = automatic, but never the cluster form.  3 and 4 never take it either.
  * block_n in {0 (auto), 32, 64, 96, ..., 256} (rounded up to a multiple of 64 for CTA
  * pairs); split_k >= 0 (0 = auto). */
 FASTNN_B200_API int fastnn_b200_set_policy(int policy, int block_n, int split_k);
 
-/* Which path the most recent GEMM call on this thread took: 1 = SIMT, 2 = tcgen05
- * 1-CTA, 3 = tcgen05 2-CTA; 0 before any call.  Also reports its tile and split choice. */
+/* Which path the most recent call on this thread took: 1 = SIMT, 2 = tcgen05 1-CTA, 3 = tcgen05
+ * 2-CTA, 4 = fused attention, 5 = conv2d, 6 = tcgen05 1-CTA with the K split inside clusters
+ * (one launch, no workspace); 0 before any call.  Also reports its tile and split choice. */
 FASTNN_B200_API int fastnn_b200_last_path(int* block_n, int* split_k, int* num_ctas);
 
 /* Reads and clears the device status word (synchronises the device).  0 = no kernel
