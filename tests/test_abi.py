@@ -79,7 +79,8 @@ def test_argument_validation(built_library):
                                    1.0, 0.0, None, 0, None) == -1
     assert lib.fastnn_cuda_matmul(dummy, dummy, dummy, -1, 4, 4, 4, 4, 4, 1.0, 0.0) == -1
     assert lib.fastnn_cuda_matmul(dummy, dummy, dummy, 4, 4, 4, 2, 4, 4, 1.0, 0.0) == -1
-    assert lib.fastnn_b200_set_policy(5, 0, 0) == -1
+    assert lib.fastnn_b200_set_policy(7, 0, 0) == -1
+    assert lib.fastnn_b200_set_policy(5, 0, 4) == 0 and lib.fastnn_b200_set_policy(0, 0, 0) == 0
     assert lib.fastnn_b200_set_policy(0, 48, 0) == -1
     assert lib.fastnn_b200_set_policy(0, 0, 0) == 0
     # empty outputs succeed without touching the device
