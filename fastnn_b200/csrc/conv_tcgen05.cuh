@@ -354,31 +354,43 @@ flip_weights_kernel(const float* __restrict__ w, float* __restrict__ wp, int ic,
   }
 }
 
-// Explicit im2col for the weight gradient: col[(n * P + p) * ld + k] = the input under tap k of output
-// position p of image n (0 in the padding and for k in [K, ld)).  Same index rule as
-// kernel_im2col of FastNN (cuda/kernels.cu:836-861), but position-major and for all images at once.
+// Explicit im2col for the weight gradient, tap-major: col[(n * K + k) * ldp + p] = the input under
+// tap k = (c, ki, kj) of output position p of image n (0 in the padding and for p in [P, ldp)).
+// FastNN's kernel_im2col uses the same [K, P] layout per image (cuda/kernels.cu:836-861); here one
+// launch covers all images, a block walks whole rows (the tap is decoded once per row), a thread
+// writes four consecutive positions as one float4 and reads along the image row, so both sides
+// are coalesced.  Both operands of the GEMM that follows are then contiguous along its
+// contraction (the positions).
 __global__ void __launch_bounds__(256)
-im2col_rows_kernel(const float* __restrict__ x, float* __restrict__ col, int batch, int ci, int h, int w,
-                   int kh, int kw, int sh, int sw, int ph, int pw, int oh, int ow, int ld) {
+im2col_taps_kernel(const float* __restrict__ x, float* __restrict__ col, int batch, int ci, int h, int w,
+                   int kh, int kw, int sh, int sw, int ph, int pw, int oh, int ow, int ldp) {
   const int khw = kh * kw;
   const int k_all = ci * khw;
-  const long long plane = static_cast<long long>(oh) * ow;
-  const long long total = static_cast<long long>(batch) * plane * ld;
-  for (long long e = blockIdx.x * 256ll + threadIdx.x; e < total; e += 256ll * gridDim.x) {
-    const long long row = e / ld;
-    const int k = static_cast<int>(e - row * ld);
-    float v = 0.0f;
-    if (k < k_all) {
-      const long long n = row / plane;
-      const int rem = static_cast<int>(row - n * plane);
-      const int oy = rem / ow, ox = rem - oy * ow;
-      const int c = k / khw;
-      const int r = k - c * khw;
-      const int ki = r / kw, kj = r - ki * kw;
-      const int iy = oy * sh - ph + ki, ix = ox * sw - pw + kj;
-      if (iy >= 0 && iy < h && ix >= 0 && ix < w) v = x[((n * ci + c) * h + iy) * w + ix];
+  const int plane = oh * ow;
+  const long long rows = static_cast<long long>(batch) * k_all;
+  const int n4 = ldp >> 2;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const long long n = row / k_all;
+    const int k = static_cast<int>(row - n * k_all);
+    const int c = k / khw;
+    const int r = k - c * khw;
+    const int ki = r / kw, kj = r - ki * kw;
+    const float* xc = x + (n * ci + c) * static_cast<long long>(h) * w;
+    float4* dst = reinterpret_cast<float4*>(col + row * ldp);
+    for (int p4 = threadIdx.x; p4 < n4; p4 += 256) {
+      const int p = p4 * 4;
+      int oy = p / ow, ox = p - oy * ow;
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int iy = oy * sh - ph + ki, ix = ox * sw - pw + kj;
+        v[j] = (p + j < plane && static_cast<unsigned>(iy) < static_cast<unsigned>(h) &&
+                static_cast<unsigned>(ix) < static_cast<unsigned>(w))
+                   ? __ldg(xc + static_cast<long long>(iy) * w + ix) : 0.0f;
+        if (++ox == ow) { ox = 0; ++oy; }
+      }
+      dst[p4] = make_float4(v[0], v[1], v[2], v[3]);
     }
-    col[e] = v;
   }
 }
 

@@ -1069,9 +1069,10 @@ extern "C" int fastnn_cuda_conv2d_backward_data(const float* grad_output, const 
                                           kernel_w, stride_h, stride_w, pad_h, pad_w, nullptr);
 }
 
-// grad_weight[co, k] = sum over images n and positions p of grad_output[n, co, p] * col[n, p, k].
-// First version, explicit: one im2col launch for all images (position-major), one batched GEMM
-// grad_output[n] . col[n] into per-image partials, one fixed-order sum over the images.
+// grad_weight[co, k] = sum over images n and positions p of grad_output[n, co, p] * col[n, k, p].
+// Explicit: one im2col launch for all images (tap-major, positions contiguous), one batched NT
+// GEMM grad_output[n] . col[n]^T into per-image partials -- both operands contiguous along the
+// contraction -- and one fixed-order sum over the images.
 extern "C" int fastnn_b200_conv2d_backward_weight(const float* input, const float* grad_output,
                                                   float* grad_weight, int batch_size, int in_channels,
                                                   int out_channels, int input_h, int input_w,
@@ -1096,8 +1097,8 @@ extern "C" int fastnn_b200_conv2d_backward_weight(const float* input, const floa
     return 0;
   }
   if (input == nullptr || grad_output == nullptr) return -1;
-  const int ld = ceil_div(k, 4) * 4;                     // 16-byte rows for TMA
-  const size_t col_floats = static_cast<size_t>(batch_size) * plane * ld;
+  const int ldp = ceil_div(static_cast<int>(plane), 4) * 4;      // 16-byte rows for TMA
+  const size_t col_floats = static_cast<size_t>(batch_size) * k * ldp;
   const size_t part_floats = static_cast<size_t>(batch_size) * out_channels * k;
   float* col = nullptr;
   int num_sms = 0;
@@ -1117,16 +1118,16 @@ extern "C" int fastnn_b200_conv2d_backward_weight(const float* input, const floa
     col = ws.ptr;
   }
   float* partials = col + ((col_floats + 63) / 64) * 64;  // keeps the 16-byte alignment
-  long long blocks = (static_cast<long long>(col_floats) + 255) / 256;
-  if (blocks > 16ll * num_sms) blocks = 16ll * num_sms;
-  fnn::im2col_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+  long long blocks = 1ll * batch_size * k;                         // one row of col per block and turn
+  if (blocks > 32ll * num_sms) blocks = 32ll * num_sms;
+  fnn::im2col_taps_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
       input, col, batch_size, in_channels, input_h, input_w, kernel_h, kernel_w, stride_h, stride_w, pad_h,
-      pad_w, output_h, output_w, ld);
+      pad_w, output_h, output_w, ldp);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   FNN_CUDA_OK(cudaGetLastError());
-  // per image: partial[n][co, k] = grad_output[n][co, P] . col[n][P, k]
-  GemmArgs g{FASTNN_B200_NN, grad_output, col, partials, out_channels, k, static_cast<int>(plane),
-             batch_size, plane, ld, k, 1ll * out_channels * plane, plane * ld, 1ll * out_channels * k,
+  // per image: partial[n][co, k] = grad_output[n][co, P] . col[n][k, P]^T
+  GemmArgs g{FASTNN_B200_NT, grad_output, col, partials, out_channels, k, static_cast<int>(plane),
+             batch_size, plane, ldp, k, 1ll * out_channels * plane, 1ll * k * ldp, 1ll * out_channels * k,
              1.0f, 0.0f, nullptr, 0, s};
   g.force_split_k = 1;
   const int rc = gemm_dispatch(g);

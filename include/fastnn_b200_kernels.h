@@ -168,8 +168,9 @@ FASTNN_B200_API int fastnn_b200_conv2d_forward(const float* input, const float* 
  * image); the _b200_ forms add a stream.
  * backward_data runs the implicit-GEMM forward kernel on grad_output with the kernel reversed and
  * channels swapped; it covers stride 1 with pad <= kernel - 1 and returns -1 otherwise.
- * backward_weight is explicit in this version: one im2col launch for all images, one batched
- * GEMM into per-image partials, one fixed-order sum (deterministic); any stride. */
+ * backward_weight is explicit in this version: one im2col launch for all images (tap-major, as
+ * FastNN's kernel_im2col lays it out), one batched NT GEMM into per-image partials, one
+ * fixed-order sum (deterministic); any stride. */
 FASTNN_B200_API int fastnn_cuda_conv2d_backward_data(const float* grad_output, const float* weight,
                                                      float* grad_input, int batch_size, int in_channels,
                                                      int out_channels, int input_h, int input_w,
