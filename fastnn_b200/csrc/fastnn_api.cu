@@ -134,6 +134,30 @@ inline int log2_exact(int v) {      // 1 -> 0, 2 -> 1, 4 -> 2, 8 -> 3, 16 -> 4, 
   return -1;
 }
 
+int stages_for(int block_n, bool pair, int kb_per_stage);
+
+// Pipeline stages of a cluster split-K CTA: one per k-block of its slice (at least two, at most
+// what fits), and never a ring smaller than the partial tile that is written over it.
+int ck_stages(int block_n, int kb_per_slice) {
+  const size_t stage_b = fnn::kStageABytes + static_cast<size_t>(block_n) * fnn::kBlockK * 4;
+  const size_t partial = static_cast<size_t>(fnn::kBlockM) * fnn::cluster_partial_pitch(block_n);
+  const int for_partial = static_cast<int>((partial + stage_b - 1) / stage_b);
+  int stages = kb_per_slice < 2 ? 2 : kb_per_slice;
+  const int cap = stages_for(block_n, false, 1);
+  if (stages > cap) stages = cap;
+  if (stages < for_partial) stages = for_partial;      // for_partial <= cap for every block_n
+  return stages;
+}
+
+// Co-resident CTAs of that kernel for cluster size 2^lg: CTAs small enough share an SM in pairs.
+int ck_slots_for(const int* full, const int* half, int lg, int block_n, int kb_per_slice) {
+  int slots = full[lg];
+  if (half != nullptr && half[lg] > slots &&
+      fnn::gemm_clusterk_smem_bytes(block_n, ck_stages(block_n, kb_per_slice)) <= kCkHalfSmem)
+    slots = half[lg];
+  return slots;
+}
+
 // Cycle model used to pick the tile shape and the K split.  Per 32-deep k-block (four MMAs) a
 // CTA is bound either by the tensor pipe (block_n / 2 cycles at 4096 dense TF32 flop/clk/SM) or by
 // reading its A and B stage from shared memory at 128 B/clk, or by the producer's TMA issue rate
@@ -212,19 +236,13 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
       // The same K splits with the slices of a tile as one cluster (single CTAs, portable cluster
       // sizes): no partial tiles in global memory and no reduce launch; instead each CTA drains
       // its accumulator to shared memory and reads 512 * bn bytes from its cluster peers.
-      for (int lg = 1; lg <= 3 && pair == 0 && ck_slots != nullptr; ++lg) {
+      for (int lg = 1; lg <= 4 && pair == 0 && ck_slots != nullptr; ++lg) {
         const int sk = 1 << lg;
-        if (ck_slots[lg] < sk || num_kb < 2 * sk) continue;
-        const long long units = 1ll * batch * tiles_m * tiles_n * sk;
+        if (num_kb < 2 * sk) continue;
         // a short slice needs few stages: such CTAs fit two to an SM
-        const size_t stage_b = fnn::kStageABytes + static_cast<size_t>(bn) * fnn::kBlockK * 4;
-        const size_t partial = static_cast<size_t>(fnn::kBlockM) * fnn::cluster_partial_pitch(bn);
-        size_t st_need = static_cast<size_t>(ceil_div(num_kb, sk) < 2 ? 2 : ceil_div(num_kb, sk));
-        if (st_need * stage_b < partial) st_need = (partial + stage_b - 1) / stage_b;
-        const bool half = ck_slots_half != nullptr && ck_slots_half[lg] > ck_slots[lg] &&
-                          fnn::gemm_clusterk_smem_bytes(bn, static_cast<int>(st_need)) <= kCkHalfSmem &&
-                          bn <= 256;
-        const int slots_ck = half ? ck_slots_half[lg] : ck_slots[lg];
+        const int slots_ck = ck_slots_for(ck_slots, ck_slots_half, lg, bn, ceil_div(num_kb, sk));
+        if (slots_ck < sk) continue;
+        const long long units = 1ll * batch * tiles_m * tiles_n * sk;
         const double waves = static_cast<double>((units + slots_ck - 1) / slots_ck);
         const double imbalance = waves * slots_ck / units;
         const double t_hbm = (in_bytes + out_bytes) / hbm_per_clk * imbalance;
@@ -246,7 +264,8 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
   return best;
 }
 
-int stages_for(int block_n, bool pair = false, int kb_per_stage = 1) {
+int stages_for(int block_n, bool pair = false, int kb_per_stage = 1);
+int stages_for(int block_n, bool pair, int kb_per_stage) {
   const size_t stage = kb_per_stage * (fnn::kStageABytes + static_cast<size_t>(pair ? block_n / 2 : block_n) *
                                                                fnn::kBlockK * 4);
   const size_t avail = kMaxDynSmem - 1024 - fnn::kStagingBytes - fnn::kBarrierBytes;
@@ -353,10 +372,9 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     // a cluster size the device can place, every slice at least one k-block, and a partial tile
     // that fits the stage ring it is written over; otherwise the workspace form of the same split
     const int lg = log2_exact(plan.split_k);
-    const int st_n = stages_for(plan.block_n);
-    const size_t ring = static_cast<size_t>(st_n) * (fnn::kStageABytes + plan.block_n * fnn::kBlockK * 4);
-    if (plan.pair || lg < 1 || st->ck_slots[lg] < plan.split_k || num_kb < plan.split_k ||
-        static_cast<size_t>(fnn::kBlockM) * fnn::cluster_partial_pitch(plan.block_n) > ring)
+    if (plan.pair || lg < 1 || num_kb < plan.split_k ||
+        ck_slots_for(st->ck_slots, st->ck_slots_half, lg, plan.block_n,
+                     ceil_div(num_kb, plan.split_k)) < plan.split_k)
       plan.cluster_k = false;
   }
   const int kbps = ceil_div(num_kb, plan.split_k);
@@ -383,14 +401,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   int ck_tmem_cols = 0;
   size_t ck_smem = 0;
   if (plan.cluster_k) {
-    const size_t stage_b = fnn::kStageABytes + static_cast<size_t>(plan.block_n) * fnn::kBlockK * 4;
-    const size_t partial = static_cast<size_t>(fnn::kBlockM) * fnn::cluster_partial_pitch(plan.block_n);
-    const int for_partial = static_cast<int>((partial + stage_b - 1) / stage_b);
-    int want = ceil_div(num_kb, plan.split_k);
-    if (want < 2) want = 2;
-    if (want < for_partial) want = for_partial;
-    if (want < plan.stages) plan.stages = want;
-    if (plan.stages < for_partial) plan.stages = for_partial;
+    plan.stages = ck_stages(plan.block_n, ceil_div(num_kb, plan.split_k));
     ck_tmem_cols = 32;
     while (ck_tmem_cols < plan.block_n) ck_tmem_cols *= 2;
     ck_smem = fnn::gemm_clusterk_smem_bytes(plan.block_n, plan.stages);
@@ -704,10 +715,14 @@ extern "C" int fastnn_cuda_init(int device_id) {
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_clusterk_kernel,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
+  // clusters of 16 are beyond the portable limit of 8; a device that refuses them reports no slots
+  if (cudaFuncSetAttribute(fnn::gemm_tf32_clusterk_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed,
+                           1) != cudaSuccess)
+    (void)cudaGetLastError();
   for (int pass = 0; pass < 2; ++pass)
-  for (int lg = 1; lg <= 3; ++lg) {
-    // how many CTAs of the cluster split-K kernel fit at once at cluster size 2, 4, 8 (a cluster
-    // inside one GPC), with one CTA per SM and with two
+  for (int lg = 1; lg <= 4; ++lg) {
+    // how many CTAs of the cluster split-K kernel fit at once at cluster size 2, 4, 8, 16 (a
+    // cluster inside one GPC), with one CTA per SM and with two
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(((2 * prop.multiProcessorCount) >> lg) << lg, 1, 1);

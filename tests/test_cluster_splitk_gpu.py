@@ -43,7 +43,7 @@ def _gpu_fn(f, layout):
     return [f.matmul, f.matmul_nt, f.matmul_tn][layout]
 
 
-@pytest.mark.parametrize("cluster", [2, 4, 8])
+@pytest.mark.parametrize("cluster", [2, 4, 8, 16])
 @pytest.mark.parametrize("layout", [NN, NT, TN])
 @pytest.mark.parametrize("shape", [(512, 256, 784, 0, 64), (256, 264, 2052, 2, 128), (100, 60, 1028, 0, 32),
                                    (132, 260, 516, 3, 96), (384, 512, 4096, 0, 256)])
@@ -62,6 +62,8 @@ def test_cluster_split_k_matches_oracle_and_is_deterministic(gpu, layout, cluste
         got2 = _host(_gpu_fn(f, layout)(da, db))
     finally:
         f.set_policy(0, 0, 0)
+    if cluster == 16 and lp["path"] == 2:
+        pytest.skip("this device places no clusters of 16 CTAs (beyond the portable size of 8)")
     assert lp["path"] == CLUSTER_PATH and lp["split_k"] == cluster and lp["block_n"] == block_n
     assert lp["num_ctas"] % cluster == 0
     assert np.array_equal(got1, got2), "the cluster reduction adds slices in a fixed order"
