@@ -134,7 +134,7 @@ inline int log2_exact(int v) {      // 1 -> 0, 2 -> 1, 4 -> 2, 8 -> 3, 16 -> 4, 
   return -1;
 }
 
-int stages_for(int block_n, bool pair, int kb_per_stage);
+int stages_for(int block_n, bool pair, int kb_per_stage, int staging_bytes = fnn::kStagingBytes);
 
 // Pipeline stages of a cluster split-K CTA: one per k-block of its slice (at least two, at most
 // what fits), and never a ring smaller than the partial tile that is written over it.
@@ -264,11 +264,11 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
   return best;
 }
 
-int stages_for(int block_n, bool pair = false, int kb_per_stage = 1);
-int stages_for(int block_n, bool pair, int kb_per_stage) {
+int stages_for(int block_n) { return stages_for(block_n, false, 1); }
+int stages_for(int block_n, bool pair, int kb_per_stage, int staging_bytes) {
   const size_t stage = kb_per_stage * (fnn::kStageABytes + static_cast<size_t>(pair ? block_n / 2 : block_n) *
                                                                fnn::kBlockK * 4);
-  const size_t avail = kMaxDynSmem - 1024 - fnn::kStagingBytes - fnn::kBarrierBytes;
+  const size_t avail = kMaxDynSmem - 1024 - staging_bytes - fnn::kBarrierBytes;
   int s = static_cast<int>(avail / stage);
   if (s > fnn::kMaxStages) s = fnn::kMaxStages;
   return s;
@@ -392,6 +392,24 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     const int s = std::atoi(e);
     if (s >= 1 && s < plan.stages) plan.stages = s;
   }
+  // With twice the staging tiles a warp issues four stores (two with eight epilogue warps) before
+  // it has to wait for one of them to be read, at the price of a pipeline stage.
+  // FASTNN_B200_STAGING=2 selects that form for sweeps.
+  int staging_bytes = fnn::kStagingBytes;
+  if (!plan.pair && !plan.cluster_k) {
+    static const int staging_env = [] {
+      const char* e = std::getenv("FASTNN_B200_STAGING");
+      return e ? std::atoi(e) : 0;
+    }();
+    const int deep_stages = stages_for(plan.block_n, false, 1, 2 * fnn::kStagingBytes);
+    // measured on the transformer-block and attention GEMMs: no gain (the stores are not what the
+    // epilogue waits for) and the lost stage costs 256-wide tiles 8 %, so the deep form is opt-in
+    const bool want = staging_env == 2;
+    if (want && deep_stages >= 3) {
+      staging_bytes = 2 * fnn::kStagingBytes;
+      if (plan.stages > deep_stages) plan.stages = deep_stages;
+    }
+  }
   // A cluster split-K CTA lives for one K slice: no more stages than the slice has k-blocks (but
   // a ring that holds the partial tile), and one accumulator.  The smaller footprint lets CTAs of
   // consecutive launches, or of two clusters, share an SM.  TMEM allocation blocks until columns
@@ -452,6 +470,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   long long out_ld = g.ldc, out_bs = g.sc;
   long long out_z = g.batch;
   p.cluster_k = plan.cluster_k ? 1 : 0;
+  p.staging_bytes = staging_bytes;
   p.tmem_cols = ck_tmem_cols;
   p.cluster_vec = (plan.cluster_k && (g.n & 3) == 0 && aligned16(g.c) && (g.ldc & 3) == 0 &&
                    (g.batch == 1 || (g.sc & 3) == 0)) ? 1 : 0;
@@ -568,7 +587,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::gemm_tf32_clusterk_kernel, tmA, tmB, tmC, tmA2, tmB2, p));
   } else {
     grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
-    const size_t smem = fnn::gemm_smem_bytes(plan.block_n, plan.stages);
+    const size_t smem = fnn::gemm_smem_bytes(plan.block_n, plan.stages, staging_bytes);
     // bias, activation, derivative and column sums are a second pass over every output element by
     // the epilogue warps alone: eight of them keep it under a short-K main loop
     const bool epilogue_work = g.act != 0 || g.bias != nullptr || g.colsum != nullptr;
@@ -749,7 +768,7 @@ extern "C" int fastnn_cuda_init(int device_id) {
     std::memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(2 * prop.multiProcessorCount, 1, 1);
     cfg.blockDim = dim3(fnn::kNumThreads, 1, 1);
-    cfg.dynamicSmemBytes = fnn::gemm_pair_smem_bytes(fnn::kMaxBlockN, stages_for(fnn::kMaxBlockN, true), 1);
+    cfg.dynamicSmemBytes = fnn::gemm_pair_smem_bytes(fnn::kMaxBlockN, stages_for(fnn::kMaxBlockN, true, 1), 1);
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;

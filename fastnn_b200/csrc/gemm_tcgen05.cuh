@@ -68,6 +68,9 @@ struct GemmParams {
                        // partial tiles through distributed shared memory (gemm_tf32_clusterk_kernel)
   int cluster_vec;     // that kernel may store float4s: n, ldc, batch stride multiples of 4, C aligned
   int tmem_cols;       // that kernel's TMEM allocation: one accumulator, a power of two >= block_n
+  int staging_bytes;   // single-CTA kernel: shared memory for the epilogue's 4 KiB staging tiles, shared
+                       // evenly by its warps (0 = kStagingBytes; 2 * kStagingBytes lets a warp issue
+                       // four stores, or two with eight warps, before it must wait for one to be read)
   int kb_per_stage;    // 32-deep k-blocks per pipeline stage (CTA-pair kernel only; else 1)
   int total_units;     // batch * tiles_m * tiles_n * split_k
   int a_mn_major;      // A stored [k, m]
@@ -165,6 +168,14 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, vola
   }
 }
 
+// Before a staging tile is overwritten: all but the newest nbuf - 1 stores of this thread have
+// read their source (nbuf = staging tiles the warp cycles through: 1, 2 or 4).
+__device__ __forceinline__ void staging_wait(int nbuf) {
+  if (nbuf == 4) ptx::tma_store_wait_read<3>();
+  else if (nbuf == 2) ptx::tma_store_wait_read<1>();
+  else ptx::tma_store_wait_read<0>();
+}
+
 // Drains one accumulator tile (this warp's 32 TMEM lanes x block_n columns) when nothing but
 // alpha / beta applies: a swizzled staging tile + TMA store, or predicated global stores.
 // m0 is the first output row of this warp, n0 the first column of the tile, cz the outer
@@ -201,9 +212,7 @@ __device__ __forceinline__ void epilogue_drain_plain(const GemmParams& p, const 
     }
     if (p.store_mode == 0) {
       // staging tile: 32 rows x 128 B, 16-byte chunk j of row r at chunk (j ^ (r & 7))
-      if (lane == 0) {                               // the tile about to be overwritten is read
-        if (nbuf == 2) ptx::tma_store_wait_read<1>(); else ptx::tma_store_wait_read<0>();
-      }
+      if (lane == 0) staging_wait(nbuf);             // the tile about to be overwritten is read
       __syncwarp();
       uint8_t* dst_row = staging_gen + buf * 4096 + lane * 128;
 #pragma unroll
@@ -219,7 +228,7 @@ __device__ __forceinline__ void epilogue_drain_plain(const GemmParams& p, const 
         else ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
         ptx::tma_store_commit();
       }
-      if (nbuf == 2) buf ^= 1;
+      buf = (buf + 1) & (nbuf - 1);
     } else if (row < p.m) {
       float* crow = p.c + static_cast<long long>(cz) * p.c_batch_stride +
                     static_cast<long long>(row) * p.ldc;
@@ -295,9 +304,7 @@ __device__ __forceinline__ void epilogue_drain_by_column(const GemmParams& p, co
     }
     if (p.store_mode == 0 || by_column) {
       // staging tile: 32 rows x 128 B, 16-byte chunk j of row r at chunk (j ^ (r & 7))
-      if (lane == 0) {                               // the tile about to be overwritten is read
-        if (nbuf == 2) ptx::tma_store_wait_read<1>(); else ptx::tma_store_wait_read<0>();
-      }
+      if (lane == 0) staging_wait(nbuf);             // the tile about to be overwritten is read
       __syncwarp();
       uint8_t* tile = staging_gen + buf * 4096;
       uint8_t* dst_row = tile + lane * 128;
@@ -373,7 +380,7 @@ __device__ __forceinline__ void epilogue_drain_by_column(const GemmParams& p, co
       }
       // after the store has been issued: a global write ahead of the proxy fence would hold it up
       if (want_colsum && col_ok) p.colsum[static_cast<long long>(m0 >> 5) * p.n + col0 + lane] = colsum;
-      if (nbuf == 2) buf ^= 1;
+      buf = (buf + 1) & (nbuf - 1);
     } else if (row < p.m) {
       float* crow = p.c + static_cast<long long>(cz) * p.c_batch_stride +
                     static_cast<long long>(row) * p.ldc;
@@ -429,7 +436,10 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
   const uint32_t stage_b_bytes = static_cast<uint32_t>(p.block_n) * kBlockK * 4;
   const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
   const uint32_t staging_base = smem_base + p.num_stages * stage_bytes;
-  const uint32_t bar_base = staging_base + (kClusterK ? 0u : kStagingBytes);   // no staging tiles there
+  const uint32_t staging_total = kClusterK ? 0u                            // no staging tiles there
+                                 : (p.staging_bytes > 0 ? static_cast<uint32_t>(p.staging_bytes)
+                                                        : static_cast<uint32_t>(kStagingBytes));
+  const uint32_t bar_base = staging_base + staging_total;
   // barrier layout: full[8] empty[8] tmem_full[2] tmem_empty[2] | tmem address | abort flag
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 64u + 8u * s; };
@@ -627,8 +637,9 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
     const int q = warp & 3;                          // TMEM lane quadrant this warp may read
     const int groups = n_epi_warps >> 2;             // 1 or 2
     const int group = (warp - kEpilogueWarp0) >> 2;
-    const int nbuf = 2 / groups;
-    const uint32_t staging = staging_base + (warp - kEpilogueWarp0) * (kStagingBytesPerWarp / groups);
+    const uint32_t staging_per_warp = staging_total / static_cast<uint32_t>(n_epi_warps);
+    const int nbuf = static_cast<int>(staging_per_warp >> 12);          // 4 KiB tiles: 1, 2 or 4
+    const uint32_t staging = staging_base + (warp - kEpilogueWarp0) * staging_per_warp;
     uint8_t* staging_gen = smem_gen + (staging - smem_base);
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -782,9 +793,9 @@ inline size_t gemm_clusterk_smem_bytes(int block_n, int num_stages) {
 }
 
 // Bytes of dynamic shared memory a launch with these parameters needs.
-inline size_t gemm_smem_bytes(int block_n, int num_stages) {
+inline size_t gemm_smem_bytes(int block_n, int num_stages, int staging_bytes = kStagingBytes) {
   return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + block_n * kBlockK * 4) +
-         kStagingBytes + kBarrierBytes;
+         staging_bytes + kBarrierBytes;
 }
 
 }  // namespace fnn
