@@ -471,6 +471,14 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   long long out_z = g.batch;
   p.cluster_k = plan.cluster_k ? 1 : 0;
   p.staging_bytes = staging_bytes;
+  {
+    static const int epi_sleep_env = [] {
+      const char* e = std::getenv("FASTNN_B200_EPI_SLEEP");
+      return e ? std::atoi(e) : -1;
+    }();
+    // long main loops only: a tile of a short-K GEMM lasts a few microseconds
+    p.epi_sleep_ns = epi_sleep_env >= 0 ? static_cast<unsigned>(epi_sleep_env) : 0u;
+  }
   p.tmem_cols = ck_tmem_cols;
   p.cluster_vec = (plan.cluster_k && (g.n & 3) == 0 && aligned16(g.c) && (g.ldc & 3) == 0 &&
                    (g.batch == 1 || (g.sc & 3) == 0)) ? 1 : 0;

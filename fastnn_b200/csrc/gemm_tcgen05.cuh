@@ -93,6 +93,8 @@ struct GemmParams {
   long long ldc, c_batch_stride;   // elements
   unsigned int* status;
   long long spin_budget;           // clock64 ticks a single wait may last
+  unsigned int epi_sleep_ns;       // > 0: epilogue threads sleep this long between polls of the
+                                   // accumulator-full barrier (they wait there for a whole main loop)
 };
 
 struct Unit {
@@ -150,12 +152,14 @@ __device__ __forceinline__ float apply_act_grad(float x, int act) {
 // Bounded wait.  Returns false when the CTA is aborting (this role's budget ran out, or
 // another role's did).
 __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                             const GemmParams& p, unsigned int code) {
+                                             const GemmParams& p, unsigned int code,
+                                             unsigned int sleep_ns = 0) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int it = 0;
   while (true) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
+    if (sleep_ns != 0) __nanosleep(sleep_ns);
     if ((++it & 63) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > p.spin_budget) {
@@ -677,7 +681,7 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
         for (int c = group; c < p.block_n / 32 && n0 + c * 32 < p.n; c += groups)
           ptx::prefetch_l2(arow + c * 32);
       }
-      ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
+      ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout, p.epi_sleep_ns);
       ok = __all_sync(0xffffffffu, ok);              // keep the warp converged for tcgen05.ld
       if (!ok) break;
       ptx::tc_fence_after_sync();

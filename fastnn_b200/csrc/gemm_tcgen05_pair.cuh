@@ -206,7 +206,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const Unit w = decode_unit_pair(p, u);
       const int m0 = w.mt * kPairBlockM + static_cast<int>(rank) * kBlockM + q * 32;
       const int n0 = w.nt * p.block_n;
-      ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
+      ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout, p.epi_sleep_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
