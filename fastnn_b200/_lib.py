@@ -56,6 +56,7 @@ SIGNATURES = {
     "fastnn_b200_reduce_partials": (_i, [_vp, _vp, _i, _i, _i, _ll, _f, _f, _vp, _i, _vp]),
     "fastnn_b200_set_policy": (_i, [_i, _i, _i]),
     "fastnn_b200_last_path": (_i, [ctypes.POINTER(_i)] * 3),
+    "fastnn_b200_plan_query": (_i, [_i] * 5 + [ctypes.POINTER(_i)] * 4),
     "fastnn_b200_device_status": (_i, [ctypes.POINTER(ctypes.c_uint)]),
     "fastnn_b200_launch_count": (ctypes.c_ulonglong, []),
     "fastnn_b200_version": (ctypes.c_char_p, []),

@@ -789,6 +789,12 @@ extern "C" int fastnn_cuda_init(int device_id) {
     }
     st.max_clusters = clusters;
   }
+  if (std::getenv("FASTNN_B200_VERBOSE") != nullptr)
+    std::fprintf(stderr, "fastnn_b200: device %d: %d SMs, %d CTA pairs; cluster split-K CTAs resident at "
+                 "cluster size 2/4/8/16: %d/%d/%d/%d (full footprint), %d/%d/%d/%d (half)\n",
+                 device_id, prop.multiProcessorCount, st.max_clusters, st.ck_slots[1], st.ck_slots[2],
+                 st.ck_slots[3], st.ck_slots[4], st.ck_slots_half[1], st.ck_slots_half[2],
+                 st.ck_slots_half[3], st.ck_slots_half[4]);
   FNN_CUDA_OK(cudaMalloc(&st.status, sizeof(unsigned int)));
   FNN_CUDA_OK(cudaMemset(st.status, 0, sizeof(unsigned int)));
   // about two seconds at the maximum SM clock (clockRate is in kHz)
@@ -1317,6 +1323,35 @@ extern "C" int fastnn_b200_last_path(int* block_n, int* split_k, int* num_ctas) 
   if (split_k) *split_k = t_last.split_k;
   if (num_ctas) *num_ctas = t_last.num_ctas;
   return t_last.path;
+}
+
+// The planner's choice for a GEMM, without launching anything.  With no initialised device the
+// figures of a B200 stand in (148 SMs, 74 CTA pairs, clusters as measured there), so the host
+// logic can be exercised on a machine without a GPU.
+extern "C" int fastnn_b200_plan_query(int layout, int m, int n, int k, int batch, int* block_n,
+                                      int* split_k, int* cta_pair, int* cluster_k) {
+  if (layout < 0 || layout > 2 || m < 1 || n < 1 || k < 1 || batch < 1) return -1;
+  int num_sms = 148, max_clusters = 74;
+  int slots[5] = {0, 148, 132, 120, 112}, slots_half[5] = {0, 148, 132, 120, 112};   // as a B200 reports
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int dev = -1;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) {
+      num_sms = g_dev[dev].num_sms;
+      max_clusters = g_dev[dev].max_clusters;
+      for (int i = 0; i < 5; ++i) { slots[i] = g_dev[dev].ck_slots[i]; slots_half[i] = g_dev[dev].ck_slots_half[i]; }
+    } else {
+      (void)cudaGetLastError();
+    }
+  }
+  const bool a_mn = layout == FASTNN_B200_TN && (m % 32) != 0;
+  const bool b_mn = layout != FASTNN_B200_NT && (n % 32) != 0;
+  const Plan plan = choose_plan(m, n, k, batch, num_sms, max_clusters, a_mn, b_mn, 0, slots, slots_half);
+  if (block_n) *block_n = plan.block_n;
+  if (split_k) *split_k = plan.split_k;
+  if (cta_pair) *cta_pair = plan.pair ? 1 : 0;
+  if (cluster_k) *cluster_k = plan.cluster_k ? 1 : 0;
+  return 0;
 }
 
 extern "C" int fastnn_b200_device_status(unsigned int* status) {

@@ -365,6 +365,15 @@ def last_path():
     return {"path": path, "block_n": bn.value, "split_k": sk.value, "num_ctas": nc.value}
 
 
+def plan_query(layout, m, n, k, batch=1):
+    """The planner's choice for a GEMM, without a launch (answers without a GPU too)."""
+    out = [ctypes.c_int() for _ in range(4)]
+    if lib().fastnn_b200_plan_query(layout, m, n, k, batch, *[ctypes.byref(o) for o in out]) != 0:
+        raise ValueError("bad GEMM shape")
+    return {"block_n": out[0].value, "split_k": out[1].value, "cta_pair": bool(out[2].value),
+            "cluster_k": bool(out[3].value)}
+
+
 def device_status() -> int:
     v = ctypes.c_uint()
     if lib().fastnn_b200_device_status(ctypes.byref(v)) != 0:

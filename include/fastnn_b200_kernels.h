@@ -277,6 +277,14 @@ FASTNN_B200_API int fastnn_b200_set_policy(int policy, int block_n, int split_k)
  * (one launch, no workspace); 0 before any call.  Also reports its tile and split choice. */
 FASTNN_B200_API int fastnn_b200_last_path(int* block_n, int* split_k, int* num_ctas);
 
+/* The host planner's choice for C[m,n] = op(A).op(B) (x batch), without launching: tile width,
+ * K split, whether CTA pairs (256-row tiles) and whether the split runs inside thread-block
+ * clusters.  Uses the initialised current device's SM and cluster counts, or a B200's when
+ * there is none (so it also answers on a machine without a GPU).  0, or -1 on bad arguments.
+ * No counterpart in the reference: cuBLAS picks its kernels internally (cuda/kernels.cu:431-526). */
+FASTNN_B200_API int fastnn_b200_plan_query(int layout, int m, int n, int k, int batch, int* block_n,
+                                           int* split_k, int* cta_pair, int* cluster_k);
+
 /* Reads and clears the device status word (synchronises the device).  0 = no kernel
  * reported a problem; otherwise the code of the first bounded wait that ran out. */
 FASTNN_B200_API int fastnn_b200_device_status(unsigned int* status);
