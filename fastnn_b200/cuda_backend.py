@@ -300,6 +300,36 @@ def rnn_gates_forward(x_t, h, w_ih, w_hh, b_ih=None, b_hh=None, out=None, stream
     return gates
 
 
+def gru_pack_weights(w_ih, w_hh, b_ih=None, b_hh=None):
+    """One-time repacking of GRU parameters (W_ih [3H,input], W_hh [3H,hidden], biases [3H]; gate
+    order r, z, n as in src/nn/rnn.rs:135-146) so that ONE rnn_gates_forward launch per time step
+    yields everything GRU::forward_seq (src/nn/rnn.rs:164-180) needs:
+        gates[:, 0:2H]  = gi + gh of the r and z gates (biases included)
+        gates[:, 2H:3H] = gi_n = x_t . W_ih[2H:3H]^T + b_ih[2H:3H]
+        gates[:, 3H:4H] = gh_n = h . W_hh[2H:3H]^T + b_hh[2H:3H]   (multiplied by r before the tanh)
+    The n gate's two products must stay apart, so its rows of each matrix face a zero block of the
+    other: W_ih' = [W_ih[0:3H]; 0], W_hh' = [W_hh[0:2H]; 0; W_hh[2H:3H]] (4H rows each)."""
+    _check(w_ih, "w_ih"); _check(w_hh, "w_hh")
+    h3 = int(w_ih.shape[0])
+    if h3 % 3 != 0 or int(w_hh.shape[0]) != h3:
+        raise ValueError("GRU weights have 3 * hidden rows")
+    hs = h3 // 3
+    wi = torch.zeros(4 * hs, w_ih.shape[1], dtype=torch.float32, device=w_ih.device)
+    wh = torch.zeros(4 * hs, w_hh.shape[1], dtype=torch.float32, device=w_hh.device)
+    wi[:3 * hs] = w_ih
+    wh[:2 * hs] = w_hh[:2 * hs]
+    wh[3 * hs:] = w_hh[2 * hs:]
+    bi = bh = None
+    if b_ih is not None:
+        bi = torch.zeros(4 * hs, dtype=torch.float32, device=w_ih.device)
+        bi[:3 * hs] = b_ih
+    if b_hh is not None:
+        bh = torch.zeros(4 * hs, dtype=torch.float32, device=w_hh.device)
+        bh[:2 * hs] = b_hh[:2 * hs]
+        bh[3 * hs:] = b_hh[2 * hs:]
+    return wi, wh, bi, bh
+
+
 def gemm_ex(layout, a_ptr, b_ptr, c_ptr, m, n, k, batch, lda, ldb, ldc, sa, sb, sc,
             alpha=1.0, beta=0.0, bias_ptr=0, act=ACT_NONE, stream=0) -> None:
     """Raw general entry (pointers as integers, strides in elements)."""

@@ -14,7 +14,7 @@ from . import build_oracle as _b
 
 __all__ = [
     "rand_data", "matmul", "matmul_nt", "matmul_tn", "matmul_rows", "transpose",
-    "bias_act", "linear", "linear_backward_input", "rnn_gates", "conv2d", "conv2d_backward", "causal_softmax", "attention", "host_threads", "ACT_NONE", "ACT_RELU",
+    "bias_act", "linear", "linear_backward_input", "rnn_gates", "gru_gates", "gru_step", "conv2d", "conv2d_backward", "causal_softmax", "attention", "host_threads", "ACT_NONE", "ACT_RELU",
     "ACT_GELU", "ref_gpu_library_path",
 ]
 
@@ -244,6 +244,32 @@ def rnn_gates(x_t: np.ndarray, h: np.ndarray, w_ih: np.ndarray, w_hh: np.ndarray
     if b_hh is not None:
         g = g + _f32(b_hh)[None, :]
     return g.astype(np.float32)
+
+
+def gru_gates(x_t: np.ndarray, h: np.ndarray, w_ih: np.ndarray, w_hh: np.ndarray, b_ih, b_hh):
+    """The two biased products of one GRU step as GRU::forward_seq forms them on CPU tensors
+    (src/nn/rnn.rs:164-170): gi = x_t.matmul(W_ih^T) + b_ih and gh = h.matmul(W_hh^T) + b_hh, each
+    [batch, 3H] with gate order r, z, n."""
+    gi = matmul(_f32(x_t), transpose(_f32(w_ih)))
+    gh = matmul(_f32(h), transpose(_f32(w_hh)))
+    if b_ih is not None:
+        gi = gi + _f32(b_ih)[None, :]
+    if b_hh is not None:
+        gh = gh + _f32(b_hh)[None, :]
+    return gi.astype(np.float32), gh.astype(np.float32)
+
+
+def gru_step(gi: np.ndarray, gh: np.ndarray, h: np.ndarray) -> np.ndarray:
+    """h' of one GRU step from the two products (src/nn/rnn.rs:172-180): r = sigmoid(gi_r + gh_r),
+    z = sigmoid(gi_z + gh_z), n = tanh(gi_n + r * gh_n), h' = (1 - z) * n + z * h, all in f32."""
+    gi, gh, h = _f32(gi), _f32(gh), _f32(h)
+    hs = h.shape[1]
+    one = np.float32(1.0)
+    sig = lambda v: (one / (one + np.exp(-v, dtype=np.float32))).astype(np.float32)
+    r = sig(gi[:, :hs] + gh[:, :hs])
+    z = sig(gi[:, hs:2 * hs] + gh[:, hs:2 * hs])
+    n = np.tanh(gi[:, 2 * hs:] + r * gh[:, 2 * hs:], dtype=np.float32)
+    return ((one - z) * n + z * h).astype(np.float32)
 
 
 def causal_softmax(scores: np.ndarray, scale: float) -> np.ndarray:

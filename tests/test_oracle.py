@@ -209,3 +209,26 @@ def test_causal_softmax_rows():
     p = oracle.causal_softmax(s, 1.0 / np.sqrt(32.0))
     assert np.allclose(p.sum(-1), 1.0, atol=1e-6)
     assert np.all(np.triu(p, 1) == 0.0)
+
+
+def test_gru_restatement_matches_a_float64_evaluation():
+    """oracle.gru_gates / gru_step (src/nn/rnn.rs:164-180) against the same formulas in float64."""
+    rng = np.random.default_rng(11)
+    batch, inp, hid = 5, 7, 6
+    x = rng.standard_normal((batch, inp)).astype(np.float32)
+    h = rng.standard_normal((batch, hid)).astype(np.float32)
+    w_ih = rng.standard_normal((3 * hid, inp)).astype(np.float32)
+    w_hh = rng.standard_normal((3 * hid, hid)).astype(np.float32)
+    b_ih = rng.standard_normal(3 * hid).astype(np.float32)
+    b_hh = rng.standard_normal(3 * hid).astype(np.float32)
+    gi, gh = oracle.gru_gates(x, h, w_ih, w_hh, b_ih, b_hh)
+    gi64 = x.astype(np.float64) @ w_ih.astype(np.float64).T + b_ih
+    gh64 = h.astype(np.float64) @ w_hh.astype(np.float64).T + b_hh
+    assert np.allclose(gi, gi64, rtol=1e-5, atol=1e-5) and np.allclose(gh, gh64, rtol=1e-5, atol=1e-5)
+    sig = lambda v: 1.0 / (1.0 + np.exp(-v))
+    r = sig(gi64[:, :hid] + gh64[:, :hid])
+    z = sig(gi64[:, hid:2 * hid] + gh64[:, hid:2 * hid])
+    n = np.tanh(gi64[:, 2 * hid:] + r * gh64[:, 2 * hid:])
+    want = (1 - z) * n + z * h
+    got = oracle.gru_step(gi, gh, h)
+    assert got.dtype == np.float32 and np.allclose(got, want, rtol=1e-4, atol=1e-5)

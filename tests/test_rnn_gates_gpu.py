@@ -108,3 +108,43 @@ def test_gates_argument_errors_and_empty_shapes(gpu):
     assert lib.fastnn_b200_rnn_gates_forward(p, 8, p, p, p, null, null, p, 4, 16, 16, 64, None) == -1   # ld_x
     assert lib.fastnn_b200_rnn_gates_forward(p, 16, null, p, p, null, null, p, 4, 16, 16, 64, None) == -1
     assert lib.fastnn_b200_rnn_gates_forward(p, 16, p, p, p, null, null, p, 0, 16, 16, 64, None) == 0
+
+
+@pytest.mark.parametrize("shape", [(64, 96, 128), (37, 52, 64), (256, 512, 256)])
+def test_gru_step_in_one_launch_with_packed_weights(gpu, shape):
+    """GRU::forward_seq (src/nn/rnn.rs:164-180) needs gi_n and gh_n apart; with the parameters
+    repacked once (zero blocks opposite the n gate's rows) one gates launch per step returns
+    [r and z pre-activations | gi_n | gh_n], and the step computed from it matches the oracle's."""
+    import torch
+    f = gpu
+    batch, inp, hid = shape
+    rng = np.random.default_rng(sum(shape))
+    x = rng.standard_normal((batch, inp), dtype=np.float32)
+    h = rng.standard_normal((batch, hid), dtype=np.float32)
+    bound = 1.0 / np.sqrt(hid)
+    w_ih = rng.uniform(-bound, bound, (3 * hid, inp)).astype(np.float32)
+    w_hh = rng.uniform(-bound, bound, (3 * hid, hid)).astype(np.float32)
+    b_ih = rng.uniform(-bound, bound, 3 * hid).astype(np.float32)
+    b_hh = rng.uniform(-bound, bound, 3 * hid).astype(np.float32)
+    gi, gh = oracle.gru_gates(x, h, w_ih, w_hh, b_ih, b_hh)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    packed = f.gru_pack_weights(dev(w_ih), dev(w_hh), dev(b_ih), dev(b_hh))
+    n0 = f.launch_count()
+    gates = f.rnn_gates_forward(dev(x), dev(h), *packed)
+    lp = f.last_path()
+    assert lp["path"] in (2, 6)
+    assert f.launch_count() - n0 == (2 if lp["split_k"] > 1 and lp["path"] == 2 else 1)
+    got = gates.cpu().numpy()
+    assert got.shape == (batch, 4 * hid)
+    amax = max(np.abs(x).max(), np.abs(h).max())
+    wmax = max(np.abs(w_ih).max(), np.abs(w_hh).max())
+    _check(got[:, :2 * hid], gi[:, :2 * hid] + gh[:, :2 * hid], inp + hid, amax, wmax, "r, z")
+    _check(got[:, 2 * hid:3 * hid], gi[:, 2 * hid:], inp, amax, wmax, "gi_n")
+    _check(got[:, 3 * hid:], gh[:, 2 * hid:], hid, amax, wmax, "gh_n")
+    # the step itself, from the launch's output: 1-Lipschitz gates keep the pre-activation bound
+    gi_dev = np.concatenate([got[:, :2 * hid], got[:, 2 * hid:3 * hid]], axis=1)
+    gh_dev = np.concatenate([np.zeros((batch, 2 * hid), np.float32), got[:, 3 * hid:]], axis=1)
+    h_new = oracle.gru_step(gi_dev, gh_dev, h)
+    want = oracle.gru_step(gi, gh, h)
+    assert np.abs(h_new - want).max() <= 2e-2 * np.sqrt(inp + hid) * amax * wmax
+    assert f.device_status() == 0
