@@ -87,12 +87,61 @@ DeviceState* current_state() {
   return st->ready ? st : nullptr;
 }
 
+// Encoded tensor maps are a pure function of their arguments, and a training loop presents the
+// same buffers with the same shapes over and over: a small direct-mapped cache in front of
+// cuTensorMapEncodeTiled (three to five encodings per GEMM call otherwise).
+struct MapKey {
+  const void* base;
+  uint64_t d[4], s[3];
+  uint32_t box[3], kind;     // kind: 0 = 3-D 16-byte atoms, 1 = 3-D 32-byte atoms, 2 = 4-D 32-byte atoms
+  bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapSlot {
+  bool valid = false;
+  MapKey key;
+  CUtensorMap map;
+};
+constexpr int kMapCacheSlots = 512;
+MapSlot g_map_cache[kMapCacheSlots];
+std::mutex g_map_mutex;
+
+inline size_t map_hash(const MapKey& k) {
+  uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+  for (int i = 0; i < 4; ++i) h = (h ^ k.d[i]) * 0x100000001B3ull;
+  for (int i = 0; i < 3; ++i) h = (h ^ k.s[i]) * 0x100000001B3ull;
+  for (int i = 0; i < 3; ++i) h = (h ^ k.box[i]) * 0x100000001B3ull;
+  h = (h ^ k.kind) * 0x100000001B3ull;
+  return static_cast<size_t>(h >> 20) % kMapCacheSlots;
+}
+inline bool map_cache_get(const MapKey& k, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  const MapSlot& s = g_map_cache[map_hash(k)];
+  if (!s.valid || !(s.key == k)) return false;
+  *out = s.map;
+  return true;
+}
+inline void map_cache_put(const MapKey& k, const CUtensorMap& m) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  MapSlot& s = g_map_cache[map_hash(k)];
+  s.valid = true;
+  s.key = k;
+  s.map = m;
+}
+
 // 3-D FP32 tensor map, 128-byte swizzle span, zero fill outside the tensor.  `atom32` selects
 // the 32-byte swizzle unit that MN-major TF32 operands need; otherwise the unit is 16 bytes.
 bool encode_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                 uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1,
                 bool atom32 = false) {
   if (g_encode == nullptr) return false;
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));          // padding bytes too: the key is compared bytewise
+  key.base = base;
+  key.d[0] = d0; key.d[1] = d1; key.d[2] = d2;
+  key.s[0] = stride1_bytes; key.s[1] = stride2_bytes;
+  key.box[0] = box0; key.box[1] = box1; key.box[2] = 1;
+  key.kind = atom32 ? 1u : 0u;
+  if (map_cache_get(key, map)) return true;
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
   cuuint32_t box[3] = {box0, box1, 1};
@@ -102,6 +151,7 @@ bool encode_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, ui
                         atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) map_cache_put(key, *map);
   return r == CUDA_SUCCESS;
 }
 
@@ -111,6 +161,14 @@ bool encode_map4(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, u
                  uint64_t d3, uint64_t stride1_bytes, uint64_t stride2_bytes,
                  uint64_t stride3_bytes, uint32_t box0, uint32_t box1, uint32_t box2) {
   if (g_encode == nullptr) return false;
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.base = base;
+  key.d[0] = d0; key.d[1] = d1; key.d[2] = d2; key.d[3] = d3;
+  key.s[0] = stride1_bytes; key.s[1] = stride2_bytes; key.s[2] = stride3_bytes;
+  key.box[0] = box0; key.box[1] = box1; key.box[2] = box2;
+  key.kind = 2u;
+  if (map_cache_get(key, map)) return true;
   cuuint64_t dims[4] = {d0, d1, d2, d3};
   cuuint64_t strides[3] = {stride1_bytes, stride2_bytes, stride3_bytes};
   cuuint32_t box[4] = {box0, box1, box2, 1};
@@ -119,6 +177,7 @@ bool encode_map4(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, u
                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) map_cache_put(key, *map);
   return r == CUDA_SUCCESS;
 }
 
@@ -264,6 +323,37 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
   return best;
 }
 
+// choose_plan walks ~250 candidates (2-3 microseconds of host time, as much as the launch itself
+// for a small GEMM), and training loops repeat a handful of shapes: remember the answers.  Called
+// with g_mutex held.  The slot tables are per device and constant after init, so the device's
+// state pointer stands for them in the key.
+Plan choose_plan_cached(const void* device_key, int m, int n, int k, int batch, int num_sms,
+                        int max_clusters, bool a_mn, bool b_mn, int pair_mode, const int* ck_slots,
+                        const int* ck_slots_half) {
+  struct Key {
+    const void* dev;
+    int m, n, k, batch, flags;
+    bool operator<(const Key& o) const {
+      if (dev != o.dev) return dev < o.dev;
+      if (m != o.m) return m < o.m;
+      if (n != o.n) return n < o.n;
+      if (k != o.k) return k < o.k;
+      if (batch != o.batch) return batch < o.batch;
+      return flags < o.flags;
+    }
+  };
+  static std::map<Key, Plan> memo;
+  const Key key{device_key, m, n, k, batch,
+                (a_mn ? 1 : 0) | (b_mn ? 2 : 0) | (pair_mode << 2) | (ck_slots != nullptr ? 16 : 0)};
+  auto it = memo.find(key);
+  if (it != memo.end()) return it->second;
+  const Plan plan = choose_plan(m, n, k, batch, num_sms, max_clusters, a_mn, b_mn, pair_mode, ck_slots,
+                                ck_slots_half);
+  if (memo.size() >= 4096) memo.clear();
+  memo.emplace(key, plan);
+  return plan;
+}
+
 int stages_for(int block_n) { return stages_for(block_n, false, 1); }
 int stages_for(int block_n, bool pair, int kb_per_stage, int staging_bytes) {
   const size_t stage = kb_per_stage * (fnn::kStageABytes + static_cast<size_t>(pair ? block_n / 2 : block_n) *
@@ -357,8 +447,9 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   }();
   const bool ck_allowed = !backward && g.force_split_k == 0 && pol.policy != 6 && pol.policy != 3 &&
                           pol.policy != 4 && !ck_env_off;
-  Plan plan = choose_plan(g.m, g.n, g.k + (dual ? g.k2 : 0), g.batch, st->num_sms, st->max_clusters,
-                          a_mn, b_mn, pair_mode, ck_allowed ? st->ck_slots : nullptr, st->ck_slots_half);
+  Plan plan = choose_plan_cached(st, g.m, g.n, g.k + (dual ? g.k2 : 0), g.batch, st->num_sms,
+                                 st->max_clusters, a_mn, b_mn, pair_mode,
+                                 ck_allowed ? st->ck_slots : nullptr, st->ck_slots_half);
   if (pol.block_n > 0) plan.block_n = pol.block_n;
   if (pol.split_k > 0) { plan.split_k = pol.split_k; plan.cluster_k = false; }
   if (pol.policy == 5) plan.cluster_k = ck_allowed;            // forced: split_k is the cluster size
