@@ -10,8 +10,10 @@
 //              k-block; it reads its 8 inputs (consecutive lanes = consecutive ow, so each load
 //              instruction is one coalesced row segment; padding and the K tail are zeros), one
 //              k-block ahead of the one it writes, into row r of a K-major 128B-swizzled stage,
-//              exactly what TMA would have produced.  Measured: the gather, not the tensor
-//              core, sets the pace (about 1800 cycles per k-block against 256-512 of MMA work);
+//              exactly what TMA would have produced.  What depends on k alone (offset of the tap,
+//              its bit in the tap mask) is read from a table written by conv_ktab_kernel just
+//              before.  Measured: the gather, not the tensor core, sets the pace, and it is bound
+//              by instruction issue;
 //   warp 0     loads the weight tile W[co-tile, k-block] by TMA (weights are [co, k] row-major,
 //              i.e. already K-major; the host pads k to a multiple of 4 when TMA needs it);
 //   warp 1     one lane issues tcgen05.mma kind::tf32 (M = 128 positions, N = block_n channels);
@@ -31,6 +33,8 @@ struct ConvParams {
   int tiles_p, tiles_n, total_units;
   int block_n, num_stages;
   const float* x;
+  const int4* ktab;    // [num_kb * 32] per k: {offset ci*H*W + ki*W + kj, tap bit (low word),
+                       // tap bit (high word), 0}; all zero for k >= ci*kh*kw (conv_ktab_kernel)
   const float* bias;   // [co] or null
   float* out;
   int act;             // 0 none, 1 ReLU
@@ -226,24 +230,20 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------------- gather ---
-    // Eight warps: warp g fills rows (g & 3) * 32 + lane, k sub-range (g >> 2) * 16 .. + 16 of the
+    // Sixteen warps: warp g fills rows (g & 3) * 32 + lane, k sub-range (g >> 2) * 8 .. + 8 of the
     // stage.  The gather is bound by instruction issue, so the per-element work is cut to a
-    // shuffle, a mask test, one add and the load:
+    // broadcast table read, a mask test, one add and the load:
     //  * per unit a thread builds a bit mask over the kernel taps (ki * kw + kj) that fall inside
     //    the image for its position, and the pointer to tap (0, 0) of channel 0;
-    //  * per k-block lane i decodes the warp's i-th k once -- offset ci*H*W + ki*W + kj and tap
-    //    index, stepped from the previous k-block without a division -- and the element loop
-    //    broadcasts it by shuffle.
+    //  * what depends on k alone -- the offset ci*H*W + ki*W + kj and the tap's bit -- comes from a
+    //    table a small kernel wrote before this one (all lanes read the same entry).
     ptx::grid_dep_wait();
     const int g = warp - kConvGatherWarp0;
     const int r = (g & 3) * 32 + lane;                            // row of the A stage = position
     const int part = g >> 2;                                      // which k sub-range of the row
     const long long plane = static_cast<long long>(p.oh) * p.ow;
-    const int khw = p.kh * p.kw;
     const int hw = p.h * p.w;
-    const int step_ci = kBlockK / khw, step_rk = kBlockK % khw;   // k advances by 32 per k-block
-    const int inv_kw = (65536 + p.kw - 1) / p.kw;                 // rk / kw for rk < 64, exactly
-    constexpr int kPastK = 63;                                    // tap index of a k past the end
+    const bool taps_fit_32 = p.kh * p.kw <= 32;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -254,7 +254,7 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int rem = row_ok ? static_cast<int>(pos - img * plane) : 0;
       const int oy = rem / p.ow, ox = rem - oy * p.ow;
       const int iy0 = oy * p.sh - p.ph, ix0 = ox * p.sw - p.pw;
-      unsigned long long tapmask = 0;                             // bit kPastK stays clear
+      unsigned long long tapmask = 0;
       if (row_ok) {
         for (int ki = 0; ki < p.kh; ++ki)
           for (int kj = 0; kj < p.kw; ++kj)
@@ -264,23 +264,25 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       // never dereferenced for a tap outside the image
       const float* xp = p.x + img * p.ci * hw + static_cast<long long>(iy0) * p.w + ix0;
-      // this lane's k of the first k-block
-      int ci = (part * kConvKPerThread + (lane & (kConvKPerThread - 1))) / khw;
-      int rk = (part * kConvKPerThread + (lane & (kConvKPerThread - 1))) - ci * khw;
+      const uint32_t mlo = static_cast<uint32_t>(tapmask), mhi = static_cast<uint32_t>(tapmask >> 32);
       // The loads of k-block kb + 1 are issued before k-block kb is written out, so their latency
       // (L2, mostly) runs under the write, the fence and the wait for the next free stage.
       float nxt[kConvKPerThread];
       auto issue_loads = [&](int kb) {
-        const int kk = kb * kBlockK + part * kConvKPerThread + (lane & (kConvKPerThread - 1));
-        const int ki = (rk * inv_kw) >> 16;
-        const int packed = kk < p.k ? (((ci * hw + ki * p.w + (rk - ki * p.kw)) << 6) | rk) : kPastK;
-        ci += step_ci; rk += step_rk;
-        if (rk >= khw) { rk -= khw; ++ci; }
+        const int4* tab = p.ktab + kb * kBlockK + part * kConvKPerThread;
+        if (taps_fit_32) {                           // warp-uniform: kernels up to 32 taps (1x1 .. 5x5)
 #pragma unroll
-        for (int i = 0; i < kConvKPerThread; ++i) {
-          const int t = __shfl_sync(0xffffffffu, packed, i);
-          const bool in = (tapmask >> (t & 63)) & 1ull;
-          nxt[i] = in ? __ldg(xp + (t >> 6)) : 0.0f;
+          for (int i = 0; i < kConvKPerThread; ++i) {
+            const int4 t = __ldg(tab + i);
+            nxt[i] = (mlo & static_cast<uint32_t>(t.y)) != 0u ? __ldg(xp + t.x) : 0.0f;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < kConvKPerThread; ++i) {
+            const int4 t = __ldg(tab + i);
+            const bool in = ((mlo & static_cast<uint32_t>(t.y)) | (mhi & static_cast<uint32_t>(t.z))) != 0u;
+            nxt[i] = in ? __ldg(xp + t.x) : 0.0f;
+          }
         }
       };
       issue_loads(0);
@@ -317,6 +319,24 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc_1cta(tmem_base, kTmemCols);
+  }
+}
+
+// What the gather needs per k = (ci, ki, kj): the offset of that tap from tap (0, 0) of channel 0
+// and the tap's bit in the 64-bit tap mask; zeros past the end of k (never inside the image).
+__global__ void __launch_bounds__(256)
+conv_ktab_kernel(int4* __restrict__ tab, int entries, int k, int kh, int kw, int h, int w) {
+  const int khw = kh * kw;
+  for (int e = blockIdx.x * 256 + threadIdx.x; e < entries; e += 256 * gridDim.x) {
+    int4 t = make_int4(0, 0, 0, 0);
+    if (e < k) {
+      const int ci = e / khw;
+      const int rk = e - ci * khw;
+      const int ki = rk / kw, kj = rk - ki * kw;
+      t.x = ci * h * w + ki * w + kj;
+      if (rk < 32) t.y = static_cast<int>(1u << rk); else t.z = static_cast<int>(1u << (rk - 32));
+    }
+    tab[e] = t;
   }
 }
 

@@ -1106,27 +1106,37 @@ static int conv_forward_impl(const float* input, const float* weight, const floa
   // rows; otherwise (k = 27 for a 3x3 kernel on RGB) a zero-padded copy goes to the workspace.
   const float* wsrc = weight;
   long long w_ld = k;
-  if (flip_transpose || (k & 3) != 0 || !aligned16(weight)) {
-    const int k_pad = ceil_div(k, fnn::kBlockK) * fnn::kBlockK;
-    const size_t need = sizeof(float) * static_cast<size_t>(out_channels) * k_pad;
-    Workspace& ws = st->workspaces[s];
-    if (ws.bytes < need) {
-      if (ws.ptr) FNN_CUDA_OK(cudaFree(ws.ptr));
-      ws.ptr = nullptr; ws.bytes = 0;
-      FNN_CUDA_OK(cudaMalloc(&ws.ptr, need));
-      ws.bytes = need;
-    }
+  const int num_kb = ceil_div(k, fnn::kBlockK);
+  const bool copy_w = flip_transpose || (k & 3) != 0 || !aligned16(weight);
+  const int k_pad = num_kb * fnn::kBlockK;
+  // workspace of this stream: [the gather's table, one int4 per k] [padded / flipped weights]
+  const size_t tab_bytes = sizeof(int4) * static_cast<size_t>(k_pad);
+  const size_t w_bytes = copy_w ? sizeof(float) * static_cast<size_t>(out_channels) * k_pad : 0;
+  Workspace& ws = st->workspaces[s];
+  if (ws.bytes < tab_bytes + w_bytes) {
+    if (ws.ptr) FNN_CUDA_OK(cudaFree(ws.ptr));
+    ws.ptr = nullptr; ws.bytes = 0;
+    FNN_CUDA_OK(cudaMalloc(&ws.ptr, tab_bytes + w_bytes));
+    ws.bytes = tab_bytes + w_bytes;
+  }
+  int4* ktab = reinterpret_cast<int4*>(ws.ptr);
+  fnn::conv_ktab_kernel<<<ceil_div(k_pad, 256), 256, 0, s>>>(ktab, k_pad, k, kernel_h, kernel_w, input_h,
+                                                            input_w);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (copy_w) {
+    float* wdst = reinterpret_cast<float*>(reinterpret_cast<char*>(ws.ptr) + tab_bytes);
     long long blocks = (1ll * out_channels * k_pad + 255) / 256;
     if (blocks > 1024) blocks = 1024;
     if (flip_transpose)
       fnn::flip_weights_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-          weight, ws.ptr, in_channels, out_channels, kernel_h, kernel_w, k_pad);
+          weight, wdst, in_channels, out_channels, kernel_h, kernel_w, k_pad);
     else
-      fnn::pad_weights_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(weight, ws.ptr, out_channels, k, k_pad);
+      fnn::pad_weights_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(weight, wdst, out_channels, k, k_pad);
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    wsrc = ws.ptr;
+    wsrc = wdst;
     w_ld = k_pad;
   }
+  FNN_CUDA_OK(cudaGetLastError());
   fnn::ConvParams p;
   std::memset(&p, 0, sizeof(p));
   p.batch = batch_size; p.ci = in_channels; p.co = out_channels; p.h = input_h; p.w = input_w;
@@ -1141,7 +1151,7 @@ static int conv_forward_impl(const float* input, const float* weight, const floa
   const size_t stage = fnn::kStageABytes + static_cast<size_t>(p.block_n) * fnn::kBlockK * 4;
   int stages = static_cast<int>((kMaxDynSmem - 1024 - fnn::kBarrierBytes) / stage);
   p.num_stages = stages > fnn::kMaxStages ? fnn::kMaxStages : stages;
-  p.x = input; p.bias = bias; p.out = output; p.act = act;
+  p.x = input; p.ktab = ktab; p.bias = bias; p.out = output; p.act = act;
   p.status = st->status; p.spin_budget = st->spin_budget;
   CUtensorMap tmW;
   if (!encode_map(&tmW, wsrc, static_cast<uint64_t>(w_ld == k ? k : w_ld), out_channels, 1, w_ld * 4ull,
