@@ -266,36 +266,33 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const float* xp = p.x + img * p.ci * hw + static_cast<long long>(iy0) * p.w + ix0;
       const uint32_t mlo = static_cast<uint32_t>(tapmask), mhi = static_cast<uint32_t>(tapmask >> 32);
       // The loads of k-block kb + 1 are issued before k-block kb is written out, so their latency
-      // (L2, mostly) runs under the write, the fence and the wait for the next free stage.
-      float nxt[kConvKPerThread];
-      auto issue_loads = [&](int kb) {
+      // (L2, mostly) runs under the write, the fence and the wait for the next free stage.  Two
+      // register buffers take turns (the loop is unrolled by two so that both are indexed
+      // statically and nothing is copied).
+      float na[kConvKPerThread], nb[kConvKPerThread];
+      auto issue_loads = [&](int kb, float (&dst)[kConvKPerThread]) {
         const int4* tab = p.ktab + kb * kBlockK + part * kConvKPerThread;
         if (taps_fit_32) {                           // warp-uniform: kernels up to 32 taps (1x1 .. 5x5)
 #pragma unroll
           for (int i = 0; i < kConvKPerThread; ++i) {
             const int4 t = __ldg(tab + i);
-            nxt[i] = (mlo & static_cast<uint32_t>(t.y)) != 0u ? __ldg(xp + t.x) : 0.0f;
+            dst[i] = (mlo & static_cast<uint32_t>(t.y)) != 0u ? __ldg(xp + t.x) : 0.0f;
           }
         } else {
 #pragma unroll
           for (int i = 0; i < kConvKPerThread; ++i) {
             const int4 t = __ldg(tab + i);
             const bool in = ((mlo & static_cast<uint32_t>(t.y)) | (mhi & static_cast<uint32_t>(t.z))) != 0u;
-            nxt[i] = in ? __ldg(xp + t.x) : 0.0f;
+            dst[i] = in ? __ldg(xp + t.x) : 0.0f;
           }
         }
       };
-      issue_loads(0);
-      for (int kb = 0; kb < p.num_kb; ++kb) {
-        float e[kConvKPerThread];
-#pragma unroll
-        for (int i = 0; i < kConvKPerThread; ++i) e[i] = nxt[i];
-        if (kb + 1 < p.num_kb) issue_loads(kb + 1);
+      // waits for a free stage, writes this thread's part of the row, hands the stage over
+      auto emit = [&](const float (&e)[kConvKPerThread]) -> bool {
         // one lane per warp polls; the shuffle orders the other lanes' writes after its observation
         int okw = 1;
         if (lane == 0) okw = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
-        if (!ok) break;
+        if (__shfl_sync(0xffffffffu, okw, 0) == 0) return false;
         uint8_t* row = smem_gen + stage * stage_bytes + r * 128;
 #pragma unroll
         for (int j = 0; j < kConvKPerThread / 4; ++j)
@@ -305,6 +302,16 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(full_bar(stage));
         if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+        return true;
+      };
+      issue_loads(0, na);
+      for (int kb = 0; kb < p.num_kb; kb += 2) {
+        if (kb + 1 < p.num_kb) issue_loads(kb + 1, nb);
+        ok = emit(na);
+        if (!ok || kb + 1 >= p.num_kb) break;
+        if (kb + 2 < p.num_kb) issue_loads(kb + 2, na);
+        ok = emit(nb);
+        if (!ok) break;
       }
     }
   }
