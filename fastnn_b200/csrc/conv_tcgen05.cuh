@@ -40,6 +40,8 @@ struct ConvParams {
   int act;             // 0 none, 1 ReLU
   unsigned int* status;
   long long spin_budget;
+  unsigned int poll_sleep_ns;   // sleep between barrier probes of the weight producer and the MMA
+                                // issuer (four times as long for the epilogue warps); 0 = spin
 };
 
 enum : unsigned int { kStatusConvGather = 0x301 };
@@ -48,13 +50,32 @@ constexpr int kConvThreads = 32 * (6 + kConvGatherWarps);   // producer, MMA iss
 constexpr int kConvKPerThread = kBlockK / (kConvGatherWarps / 4);   // k's of a stage row one gather thread fills
 constexpr int kConvGatherWarp0 = 6;
 
+// *ptr when cond != 0, else 0, as ONE predicated load: no branch, and no access when cond is 0
+// (the address may then lie outside the tensor).
+__device__ __forceinline__ float ldg_if(const float* ptr, uint32_t cond) {
+  float v;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.u32 p, %2, 0;\n\t"
+      "mov.f32 %0, 0f00000000;\n\t"
+      "@p ld.global.nc.f32 %0, [%1];\n\t}"
+      : "=f"(v)
+      : "l"(ptr), "r"(cond));
+  return v;
+}
+
+// sleep_ns > 0: the caller is not on the critical path (here everything but the gather) and
+// sleeps between probes, so that its polling does not take issue slots from the gather warps of
+// its scheduler.
 __device__ __forceinline__ bool conv_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          const ConvParams& p, unsigned int code) {
+                                          const ConvParams& p, unsigned int code,
+                                          unsigned int sleep_ns = 0) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int it = 0;
   while (true) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
+    if (sleep_ns != 0) __nanosleep(sleep_ns);
     if ((++it & 63) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > p.spin_budget) {
@@ -126,7 +147,7 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         const int n0 = tile_n(u) * p.block_n;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          ok = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
+          ok = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout, p.poll_sleep_ns);
           if (!ok) break;
           const uint32_t sb = smem_base + stage * stage_bytes + kStageABytes;
           ptx::mbar_expect_tx(full_bar(stage), stage_b_bytes);
@@ -145,13 +166,13 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
-        ok = conv_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout);
+        ok = conv_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout, p.poll_sleep_ns);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBlockN);
         uint32_t first = 0u;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          ok = conv_wait(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout);
+          ok = conv_wait(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout, p.poll_sleep_ns);
           if (!ok) break;
           ptx::tc_fence_after_sync();
           const uint32_t sa = smem_base + stage * stage_bytes;
@@ -186,7 +207,7 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const long long img = row_ok ? pos / plane : 0;
       const long long rem = row_ok ? pos - img * plane : 0;
       float* obase = p.out + (img * p.co) * plane + rem;          // + channel * plane
-      ok = conv_wait(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
+      ok = conv_wait(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout, 4 * p.poll_sleep_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
@@ -276,14 +297,13 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
           for (int i = 0; i < kConvKPerThread; ++i) {
             const int4 t = __ldg(tab + i);
-            dst[i] = (mlo & static_cast<uint32_t>(t.y)) != 0u ? __ldg(xp + t.x) : 0.0f;
+            dst[i] = ldg_if(xp + t.x, mlo & static_cast<uint32_t>(t.y));
           }
         } else {
 #pragma unroll
           for (int i = 0; i < kConvKPerThread; ++i) {
             const int4 t = __ldg(tab + i);
-            const bool in = ((mlo & static_cast<uint32_t>(t.y)) | (mhi & static_cast<uint32_t>(t.z))) != 0u;
-            dst[i] = in ? __ldg(xp + t.x) : 0.0f;
+            dst[i] = ldg_if(xp + t.x, (mlo & static_cast<uint32_t>(t.y)) | (mhi & static_cast<uint32_t>(t.z)));
           }
         }
       };

@@ -1153,6 +1153,13 @@ static int conv_forward_impl(const float* input, const float* weight, const floa
   p.num_stages = stages > fnn::kMaxStages ? fnn::kMaxStages : stages;
   p.x = input; p.ktab = ktab; p.bias = bias; p.out = output; p.act = act;
   p.status = st->status; p.spin_budget = st->spin_budget;
+  {
+    static const int sleep_env = [] {
+      const char* e = std::getenv("FASTNN_B200_CONV_POLL_SLEEP");
+      return e ? std::atoi(e) : -1;
+    }();
+    p.poll_sleep_ns = sleep_env >= 0 ? static_cast<unsigned>(sleep_env) : 0u;
+  }
   CUtensorMap tmW;
   if (!encode_map(&tmW, wsrc, static_cast<uint64_t>(w_ld == k ? k : w_ld), out_channels, 1, w_ld * 4ull,
                   w_ld * 4ull * out_channels, fnn::kBlockK, p.block_n))
