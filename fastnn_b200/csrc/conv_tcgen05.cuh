@@ -416,7 +416,11 @@ im2col_taps_kernel(const float* __restrict__ x, float* __restrict__ col, int bat
   const int plane = oh * ow;
   const long long rows = static_cast<long long>(batch) * k_all;
   const int n4 = ldp >> 2;
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+  // 64 threads walk one row (a row of 56 x 56 positions is 784 float4s: 12.25 turns of 64, where
+  // 256 threads on one row idled through a quarter of their turns); four rows per block and turn
+  const int sub = threadIdx.x >> 6, lane64 = threadIdx.x & 63;
+  const int step_y = 256 / ow, step_x = 256 - step_y * ow;      // 64 float4s = 256 positions on
+  for (long long row = 4ll * blockIdx.x + sub; row < rows; row += 4ll * gridDim.x) {
     const long long n = row / k_all;
     const int k = static_cast<int>(row - n * k_all);
     const int c = k / khw;
@@ -424,9 +428,10 @@ im2col_taps_kernel(const float* __restrict__ x, float* __restrict__ col, int bat
     const int ki = r / kw, kj = r - ki * kw;
     const float* xc = x + (n * ci + c) * static_cast<long long>(h) * w;
     float4* dst = reinterpret_cast<float4*>(col + row * ldp);
-    for (int p4 = threadIdx.x; p4 < n4; p4 += 256) {
+    int oy0 = (lane64 * 4) / ow, ox0 = lane64 * 4 - oy0 * ow;
+    for (int p4 = lane64; p4 < n4; p4 += 64) {
       const int p = p4 * 4;
-      int oy = p / ow, ox = p - oy * ow;
+      int oy = oy0, ox = ox0;
       float v[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -437,6 +442,8 @@ im2col_taps_kernel(const float* __restrict__ x, float* __restrict__ col, int bat
         if (++ox == ow) { ox = 0; ++oy; }
       }
       dst[p4] = make_float4(v[0], v[1], v[2], v[3]);
+      ox0 += step_x; oy0 += step_y;
+      if (ox0 >= ow) { ox0 -= ow; ++oy0; }
     }
   }
 }

@@ -1274,7 +1274,7 @@ extern "C" int fastnn_b200_conv2d_backward_weight(const float* input, const floa
     col = ws.ptr;
   }
   float* partials = col + ((col_floats + 63) / 64) * 64;  // keeps the 16-byte alignment
-  long long blocks = 1ll * batch_size * k;                         // one row of col per block and turn
+  long long blocks = (1ll * batch_size * k + 3) / 4;               // four rows of col per block and turn
   if (blocks > 32ll * num_sms) blocks = 32ll * num_sms;
   fnn::im2col_taps_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
       input, col, batch_size, in_channels, input_h, input_w, kernel_h, kernel_w, stride_h, stride_w, pad_h,
