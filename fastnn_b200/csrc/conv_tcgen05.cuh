@@ -313,11 +313,14 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         int okw = 1;
         if (lane == 0) okw = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather) ? 1 : 0;
         if (__shfl_sync(0xffffffffu, okw, 0) == 0) return false;
-        uint8_t* row = smem_gen + stage * stage_bytes + r * 128;
+        // 32-bit shared-window addresses: row r of the stage, 16-byte chunk c at c ^ (r & 7)
+        const uint32_t row = smem_base + stage * stage_bytes + r * 128;
 #pragma unroll
         for (int j = 0; j < kConvKPerThread / 4; ++j)
-          *reinterpret_cast<float4*>(row + (((part * (kConvKPerThread / 4) + j) ^ (r & 7)) << 4)) =
-              make_float4(e[4 * j], e[4 * j + 1], e[4 * j + 2], e[4 * j + 3]);
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(
+                           row + (((part * (kConvKPerThread / 4) + j) ^ (r & 7)) << 4)),
+                       "f"(e[4 * j]), "f"(e[4 * j + 1]), "f"(e[4 * j + 2]), "f"(e[4 * j + 3])
+                       : "memory");
         ptx::fence_proxy_async_smem();               // generic writes -> visible to the tensor core
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(full_bar(stage));
