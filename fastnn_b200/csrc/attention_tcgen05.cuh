@@ -95,8 +95,6 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // the next kernel of the stream may set itself up on SMs this grid has left
-  ptx::grid_dep_launch_dependents();
 
   const AttnSmem sm = attn_smem_plan(p.d, p.tk_pad, p.nsets);
   const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.nsets) * sm.set_bytes;
@@ -139,6 +137,9 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
+  // the next kernel of the stream may set itself up on SMs this grid has left -- only now that
+  // this CTA holds its tensor-memory columns (a dependent may not take them first)
+  ptx::grid_dep_launch_dependents();
   // score / probability tiles at columns [0, tk_pad) and [tk_pad, 2 tk_pad); O tiles at 256 + b*d
   auto tmem_s = [&](int b) { return tmem_base + static_cast<uint32_t>(b * p.tk_pad); };
   auto tmem_o = [&](int b) { return tmem_base + 256u + static_cast<uint32_t>(b * p.d); };

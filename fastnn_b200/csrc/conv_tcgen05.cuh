@@ -40,8 +40,6 @@ struct ConvParams {
   int act;             // 0 none, 1 ReLU
   unsigned int* status;
   long long spin_budget;
-  unsigned int poll_sleep_ns;   // sleep between barrier probes of the weight producer and the MMA
-                                // issuer (four times as long for the epilogue warps); 0 = spin
 };
 
 enum : unsigned int { kStatusConvGather = 0x301 };
@@ -64,18 +62,14 @@ __device__ __forceinline__ float ldg_if(const float* ptr, uint32_t cond) {
   return v;
 }
 
-// sleep_ns > 0: the caller is not on the critical path (here everything but the gather) and
-// sleeps between probes, so that its polling does not take issue slots from the gather warps of
-// its scheduler.
+// Bounded wait, as in the GEMM kernels.
 __device__ __forceinline__ bool conv_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          const ConvParams& p, unsigned int code,
-                                          unsigned int sleep_ns = 0) {
+                                          const ConvParams& p, unsigned int code) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int it = 0;
   while (true) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
-    if (sleep_ns != 0) __nanosleep(sleep_ns);
     if ((++it & 63) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > p.spin_budget) {
@@ -95,7 +89,6 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  ptx::grid_dep_launch_dependents();
 
   const uint32_t stage_b_bytes = static_cast<uint32_t>(p.block_n) * kBlockK * 4;
   const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
@@ -132,6 +125,8 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
+  // dependents of this grid may be scheduled only now that this CTA holds its TMEM columns
+  ptx::grid_dep_launch_dependents();
   // unit u -> (position tile, channel tile); channel tiles of one position tile are neighbours
   auto tile_p = [&](int u) { return u / p.tiles_n; };
   auto tile_n = [&](int u) { return u % p.tiles_n; };
@@ -147,7 +142,7 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         const int n0 = tile_n(u) * p.block_n;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          ok = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout, p.poll_sleep_ns);
+          ok = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
           if (!ok) break;
           const uint32_t sb = smem_base + stage * stage_bytes + kStageABytes;
           ptx::mbar_expect_tx(full_bar(stage), stage_b_bytes);
@@ -166,13 +161,13 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
-        ok = conv_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout, p.poll_sleep_ns);
+        ok = conv_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBlockN);
         uint32_t first = 0u;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          ok = conv_wait(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout, p.poll_sleep_ns);
+          ok = conv_wait(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout);
           if (!ok) break;
           ptx::tc_fence_after_sync();
           const uint32_t sa = smem_base + stage * stage_bytes;
@@ -207,7 +202,7 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const long long img = row_ok ? pos / plane : 0;
       const long long rem = row_ok ? pos - img * plane : 0;
       float* obase = p.out + (img * p.co) * plane + rem;          // + channel * plane
-      ok = conv_wait(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout, 4 * p.poll_sleep_ns);
+      ok = conv_wait(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
@@ -448,6 +443,82 @@ im2col_taps_kernel(const float* __restrict__ x, float* __restrict__ col, int bat
       ox0 += step_x; oy0 += step_y;
       if (ox0 >= ow) { ox0 -= ow; ++oy0; }
     }
+  }
+}
+
+// Direct convolution, one thread per output element, FP32 FMA: serves the shapes the implicit-GEMM
+// kernel's gather cannot encode (64 kernel taps or more, images of 2^25 elements or more).  With
+// flip != 0 `wt` is [ci, co, kh, kw] and is read with both kernel axes reversed (the stride-1 input
+// gradient written as a convolution of the output gradient; channel roles already swapped by the
+// caller), otherwise [co, ci, kh, kw].  Loop order ci, ki, kj as Conv2d::forward
+// (src/nn/conv.rs:97-123).
+__global__ void __launch_bounds__(256)
+conv2d_direct_kernel(const float* __restrict__ x, const float* __restrict__ wt,
+                     const float* __restrict__ bias, float* __restrict__ out, int batch, int ci, int co,
+                     int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int oh, int ow, int act,
+                     int flip) {
+  const long long total = static_cast<long long>(batch) * co * oh * ow;
+  for (long long e = blockIdx.x * 256ll + threadIdx.x; e < total; e += 256ll * gridDim.x) {
+    const int ox = static_cast<int>(e % ow);
+    const int oy = static_cast<int>((e / ow) % oh);
+    const int c = static_cast<int>((e / (static_cast<long long>(ow) * oh)) % co);
+    const long long n = e / (static_cast<long long>(ow) * oh * co);
+    float acc = 0.0f;
+    for (int i = 0; i < ci; ++i) {
+      const float* xi = x + (n * ci + i) * static_cast<long long>(h) * w;
+      for (int ki = 0; ki < kh; ++ki) {
+        const int iy = oy * sh - ph + ki;
+        if (static_cast<unsigned>(iy) >= static_cast<unsigned>(h)) continue;
+        for (int kj = 0; kj < kw; ++kj) {
+          const int ix = ox * sw - pw + kj;
+          if (static_cast<unsigned>(ix) >= static_cast<unsigned>(w)) continue;
+          const float wv = flip ? __ldg(wt + ((static_cast<long long>(i) * co + c) * kh + (kh - 1 - ki)) * kw +
+                                        (kw - 1 - kj))
+                                : __ldg(wt + ((static_cast<long long>(c) * ci + i) * kh + ki) * kw + kj);
+          acc = fmaf(__ldg(xi + static_cast<long long>(iy) * w + ix), wv, acc);
+        }
+      }
+    }
+    if (bias != nullptr) acc += __ldg(bias + c);
+    if (act == kActRelu) acc = fmaxf(acc, 0.0f);
+    out[e] = acc;
+  }
+}
+
+// Input gradient of a convolution with any stride and padding, gather form: the thread that owns
+// grad_input[n, c, iy, ix] adds grad_output[n, o, oy, ox] * weight[o, c, ki, kj] over all (o, ki, kj)
+// with oy * stride_h = iy + pad_h - ki and ox * stride_w = ix + pad_w - kj inside the output.  The
+// same terms FastNN's GEMM + col2im adds (cuda/kernels.cu:862-893, 949-987); every element is
+// written exactly once, so the output needs no clearing and no atomics.
+__global__ void __launch_bounds__(256)
+conv2d_backward_data_direct_kernel(const float* __restrict__ go, const float* __restrict__ wt,
+                                   float* __restrict__ gi, int batch, int ci, int co, int h, int w, int oh,
+                                   int ow, int kh, int kw, int sh, int sw, int ph, int pw) {
+  const long long total = static_cast<long long>(batch) * ci * h * w;
+  const long long oplane = static_cast<long long>(oh) * ow;
+  for (long long e = blockIdx.x * 256ll + threadIdx.x; e < total; e += 256ll * gridDim.x) {
+    const int ix = static_cast<int>(e % w);
+    const int iy = static_cast<int>((e / w) % h);
+    const int c = static_cast<int>((e / (static_cast<long long>(w) * h)) % ci);
+    const long long n = e / (static_cast<long long>(w) * h * ci);
+    float acc = 0.0f;
+    for (int ki = 0; ki < kh; ++ki) {
+      const int ty = iy + ph - ki;
+      if (ty < 0 || ty % sh != 0) continue;
+      const int oy = ty / sh;
+      if (oy >= oh) continue;
+      for (int kj = 0; kj < kw; ++kj) {
+        const int tx = ix + pw - kj;
+        if (tx < 0 || tx % sw != 0) continue;
+        const int ox = tx / sw;
+        if (ox >= ow) continue;
+        const float* gp = go + n * co * oplane + static_cast<long long>(oy) * ow + ox;
+        const float* wp = wt + (static_cast<long long>(c) * kh + ki) * kw + kj;
+        const long long wstep = static_cast<long long>(ci) * kh * kw;
+        for (int o = 0; o < co; ++o) acc = fmaf(__ldg(gp + o * oplane), __ldg(wp + o * wstep), acc);
+      }
+    }
+    gi[e] = acc;
   }
 }
 

@@ -39,7 +39,8 @@ struct Workspace {
 };
 
 struct DeviceState {
-  bool ready = false;
+  std::atomic<bool> ready{false};   // set last by fastnn_cuda_init; everything but the workspace
+                                    // tables is constant afterwards
   int num_sms = 0;
   int max_clusters = 0;             // co-resident CTA pairs of the pair kernel
   int ck_slots[5] = {0, 0, 0, 0, 0};  // co-resident CTAs of the cluster split-K kernel at cluster
@@ -47,19 +48,51 @@ struct DeviceState {
   int ck_slots_half[5] = {0, 0, 0, 0, 0};   // the same when a CTA asks for at most kCkHalfSmem
   unsigned int* status = nullptr;   // device word written by a kernel whose wait ran out
   long long spin_budget = 0;        // clock ticks one wait may last
+  std::mutex ws_mutex;                            // guards the two tables below
   std::map<cudaStream_t, Workspace> workspaces;   // split-K partials, one per stream
   std::map<cudaStream_t, Workspace> conv_ws;      // im2col matrix + per-image partials of conv dW
 };
 
-std::mutex g_mutex;
+std::mutex g_mutex;                 // device initialisation only; no GEMM call takes it
 DeviceState g_dev[kMaxDevices];
-EncodeTiledFn g_encode = nullptr;
+std::atomic<EncodeTiledFn> g_encode{nullptr};
 std::atomic<unsigned long long> g_launches{0};
 
+// Kernel-selection override of fastnn_b200_set_policy: per calling thread, so a test or sweep
+// that forces a kernel cannot change what another thread's GEMMs run.
 struct Policy {
   int policy = 0, block_n = 0, split_k = 0;
 };
-Policy g_policy;
+thread_local Policy t_policy;
+
+// Environment switches, read once per process (first GEMM call).
+struct Tunables {
+  bool no_chunked = false;      // FASTNN_B200_NO_CHUNKED: per-chunk boxes for MN-major operands
+  bool cluster_k_off = false;   // FASTNN_B200_CLUSTER_K=0
+  bool pdl = true;              // FASTNN_B200_PDL=0: ordinary launches
+  int kb_per_stage = 0;         // FASTNN_B200_KB_PER_STAGE (CTA pairs; 0 = planner)
+  int stages = 0;               // FASTNN_B200_STAGES: upper bound on pipeline stages (0 = none)
+  int group_m = 0;              // FASTNN_B200_GROUP_M: tile rows per rasterisation group
+  int l2 = -1;                  // FASTNN_B200_L2=<C><A><B>: eviction policies of stores and loads
+};
+const Tunables& tunables() {
+  static const Tunables t = [] {
+    Tunables v;
+    auto num = [](const char* name, int fallback) {
+      const char* e = std::getenv(name);
+      return e != nullptr ? std::atoi(e) : fallback;
+    };
+    v.no_chunked = std::getenv("FASTNN_B200_NO_CHUNKED") != nullptr;
+    v.cluster_k_off = num("FASTNN_B200_CLUSTER_K", 1) == 0;
+    v.pdl = num("FASTNN_B200_PDL", 1) != 0;
+    v.kb_per_stage = num("FASTNN_B200_KB_PER_STAGE", 0);
+    v.stages = num("FASTNN_B200_STAGES", 0);
+    v.group_m = num("FASTNN_B200_GROUP_M", 0);
+    v.l2 = num("FASTNN_B200_L2", -1);
+    return v;
+  }();
+  return t;
+}
 
 struct LastCall {
   int path = 0, block_n = 0, split_k = 0, num_ctas = 0;
@@ -84,7 +117,35 @@ DeviceState* current_state() {
     return nullptr;
   }
   DeviceState* st = &g_dev[dev];
-  return st->ready ? st : nullptr;
+  return st->ready.load(std::memory_order_acquire) ? st : nullptr;
+}
+
+// The stream's scratch buffer of one of the two tables, grown when too small.  Growth is
+// stream-ordered (cudaFreeAsync / cudaMallocAsync on the call's stream): kernels already queued on
+// the stream keep their buffer until they have run, and nothing synchronises the device.  A
+// stream under capture cannot grow its buffer (the allocation would belong to the graph): make
+// the same call once before capturing.
+int workspace_reserve(DeviceState* st, std::map<cudaStream_t, Workspace>& table, cudaStream_t s,
+                      size_t need, float** out) {
+  std::lock_guard<std::mutex> lock(st->ws_mutex);
+  Workspace& ws = table[s];
+  if (ws.bytes < need) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+    if (cap != cudaStreamCaptureStatusNone) {
+      std::fprintf(stderr, "fastnn_b200: a scratch buffer of %zu bytes is needed while the stream is "
+                           "being captured; run the call once before the capture\n", need);
+      return -1;
+    }
+    if (ws.ptr != nullptr) FNN_CUDA_OK(cudaFreeAsync(ws.ptr, s));
+    ws.ptr = nullptr; ws.bytes = 0;
+    void* ptr = nullptr;
+    FNN_CUDA_OK(cudaMallocAsync(&ptr, need, s));
+    ws.ptr = static_cast<float*>(ptr);
+    ws.bytes = need;
+  }
+  *out = ws.ptr;
+  return 0;
 }
 
 // Encoded tensor maps are a pure function of their arguments, and a training loop presents the
@@ -133,7 +194,8 @@ inline void map_cache_put(const MapKey& k, const CUtensorMap& m) {
 bool encode_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                 uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1,
                 bool atom32 = false) {
-  if (g_encode == nullptr) return false;
+  const EncodeTiledFn encode = g_encode.load(std::memory_order_acquire);
+  if (encode == nullptr) return false;
   MapKey key;
   std::memset(&key, 0, sizeof(key));          // padding bytes too: the key is compared bytewise
   key.base = base;
@@ -146,7 +208,7 @@ bool encode_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, ui
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
   cuuint32_t box[3] = {box0, box1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims,
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims,
                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -160,7 +222,8 @@ bool encode_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, ui
 bool encode_map4(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                  uint64_t d3, uint64_t stride1_bytes, uint64_t stride2_bytes,
                  uint64_t stride3_bytes, uint32_t box0, uint32_t box1, uint32_t box2) {
-  if (g_encode == nullptr) return false;
+  const EncodeTiledFn encode = g_encode.load(std::memory_order_acquire);
+  if (encode == nullptr) return false;
   MapKey key;
   std::memset(&key, 0, sizeof(key));
   key.base = base;
@@ -173,7 +236,7 @@ bool encode_map4(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, u
   cuuint64_t strides[3] = {stride1_bytes, stride2_bytes, stride3_bytes};
   cuuint32_t box[4] = {box0, box1, box2, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims,
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims,
                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -193,7 +256,7 @@ inline int log2_exact(int v) {      // 1 -> 0, 2 -> 1, 4 -> 2, 8 -> 3, 16 -> 4, 
   return -1;
 }
 
-int stages_for(int block_n, bool pair, int kb_per_stage, int staging_bytes = fnn::kStagingBytes);
+int stages_for(int block_n, bool pair, int kb_per_stage);
 
 // Pipeline stages of a cluster split-K CTA: one per k-block of its slice (at least two, at most
 // what fits), and never a ring smaller than the partial tile that is written over it.
@@ -324,9 +387,9 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
 }
 
 // choose_plan walks ~250 candidates (2-3 microseconds of host time, as much as the launch itself
-// for a small GEMM), and training loops repeat a handful of shapes: remember the answers.  Called
-// with g_mutex held.  The slot tables are per device and constant after init, so the device's
-// state pointer stands for them in the key.
+// for a small GEMM), and training loops repeat a handful of shapes: remember the answers.  The
+// slot tables are per device and constant after init, so the device's state pointer stands for
+// them in the key.
 Plan choose_plan_cached(const void* device_key, int m, int n, int k, int batch, int num_sms,
                         int max_clusters, bool a_mn, bool b_mn, int pair_mode, const int* ck_slots,
                         const int* ck_slots_half) {
@@ -343,6 +406,8 @@ Plan choose_plan_cached(const void* device_key, int m, int n, int k, int batch, 
     }
   };
   static std::map<Key, Plan> memo;
+  static std::mutex memo_mutex;
+  std::lock_guard<std::mutex> lock(memo_mutex);
   const Key key{device_key, m, n, k, batch,
                 (a_mn ? 1 : 0) | (b_mn ? 2 : 0) | (pair_mode << 2) | (ck_slots != nullptr ? 16 : 0)};
   auto it = memo.find(key);
@@ -355,10 +420,10 @@ Plan choose_plan_cached(const void* device_key, int m, int n, int k, int batch, 
 }
 
 int stages_for(int block_n) { return stages_for(block_n, false, 1); }
-int stages_for(int block_n, bool pair, int kb_per_stage, int staging_bytes) {
+int stages_for(int block_n, bool pair, int kb_per_stage) {
   const size_t stage = kb_per_stage * (fnn::kStageABytes + static_cast<size_t>(pair ? block_n / 2 : block_n) *
                                                                fnn::kBlockK * 4);
-  const size_t avail = kMaxDynSmem - 1024 - staging_bytes - fnn::kBarrierBytes;
+  const size_t avail = kMaxDynSmem - 1024 - fnn::kStagingBytes - fnn::kBarrierBytes;
   int s = static_cast<int>(avail / stage);
   if (s > fnn::kMaxStages) s = fnn::kMaxStages;
   return s;
@@ -384,6 +449,10 @@ struct GemmArgs {
   long long lda2 = 0, ldb2 = 0;
   const float* bias2 = nullptr;
   int force_split_k = 0;     // > 0: overrides the planner's K split (callers that own the workspace)
+  // gather: the location of C's rows in up to kMaxPeers other GPUs' memory (peer-mapped pointers);
+  // every finished tile is stored there as well as to c
+  float* const* peer_c = nullptr;
+  int n_peers = 0;
 };
 
 bool tma_operands_ok(const GemmArgs& g) {
@@ -433,27 +502,25 @@ int launch_simt(const GemmArgs& g) {
 }
 
 int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
-  const bool no_chunk = std::getenv("FASTNN_B200_NO_CHUNKED") != nullptr;
+  const Tunables& tune = tunables();
+  const bool no_chunk = tune.no_chunked;
   const bool a_mn = (g.layout == FASTNN_B200_TN) && ((g.m % 32) != 0 || no_chunk);
   const bool b_mn = (g.layout != FASTNN_B200_NT) && ((g.n % 32) != 0 || no_chunk);
   const bool dual = g.a2 != nullptr;       // C = A.B + A2.B2: single-CTA kernel, one K range
+  const bool gather = g.n_peers > 0;       // tiles also go to other GPUs: whole K per tile, TMA stores
   const int pair_mode = dual ? 1 : ((pol.policy == 3 || pol.policy >= 5) ? 1 : (pol.policy == 4 ? 2 : 0));
   // the backward epilogue is not linear in the partial sums, and the column sums use the workspace
   const bool backward = g.aux != nullptr || g.colsum != nullptr;
   // cluster split-K writes C itself: not for callers that want the raw partial tiles
-  static const bool ck_env_off = [] {
-    const char* e = std::getenv("FASTNN_B200_CLUSTER_K");
-    return e != nullptr && std::atoi(e) == 0;
-  }();
-  const bool ck_allowed = !backward && g.force_split_k == 0 && pol.policy != 6 && pol.policy != 3 &&
-                          pol.policy != 4 && !ck_env_off;
+  const bool ck_allowed = !backward && !gather && g.force_split_k == 0 && pol.policy != 6 &&
+                          pol.policy != 3 && pol.policy != 4 && !tune.cluster_k_off;
   Plan plan = choose_plan_cached(st, g.m, g.n, g.k + (dual ? g.k2 : 0), g.batch, st->num_sms,
                                  st->max_clusters, a_mn, b_mn, pair_mode,
                                  ck_allowed ? st->ck_slots : nullptr, st->ck_slots_half);
   if (pol.block_n > 0) plan.block_n = pol.block_n;
   if (pol.split_k > 0) { plan.split_k = pol.split_k; plan.cluster_k = false; }
   if (pol.policy == 5) plan.cluster_k = ck_allowed;            // forced: split_k is the cluster size
-  if (backward) plan.split_k = 1;
+  if (backward || gather) { plan.split_k = 1; plan.cluster_k = false; }
   if (g.force_split_k > 0) plan.split_k = g.force_split_k;
   if (plan.pair && (plan.block_n % 64) != 0) plan.block_n = ceil_div(plan.block_n, 64) * 64;
   const int num_kb1 = ceil_div(g.k, fnn::kBlockK);
@@ -473,34 +540,10 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   // CTA pairs with wide tiles take two k-blocks per stage: the issuing thread's per-stage
   // cost (wait, commit, loop) is then paid once per eight MMAs instead of once per four
   int kb_per_stage = (plan.pair && plan.block_n == 256 && kbps >= 8) ? 2 : 1;
-  if (const char* e = std::getenv("FASTNN_B200_KB_PER_STAGE")) {
-    const int r = std::atoi(e);
-    if (plan.pair && r >= 1 && r <= 4) kb_per_stage = r;
-  }
+  if (plan.pair && tune.kb_per_stage >= 1 && tune.kb_per_stage <= 4) kb_per_stage = tune.kb_per_stage;
   plan.stages = stages_for(plan.block_n, plan.pair, kb_per_stage);
   if (plan.stages < 2) { kb_per_stage = 1; plan.stages = stages_for(plan.block_n, plan.pair, 1); }
-  if (const char* e = std::getenv("FASTNN_B200_STAGES")) {
-    const int s = std::atoi(e);
-    if (s >= 1 && s < plan.stages) plan.stages = s;
-  }
-  // With twice the staging tiles a warp issues four stores (two with eight epilogue warps) before
-  // it has to wait for one of them to be read, at the price of a pipeline stage.
-  // FASTNN_B200_STAGING=2 selects that form for sweeps.
-  int staging_bytes = fnn::kStagingBytes;
-  if (!plan.pair && !plan.cluster_k) {
-    static const int staging_env = [] {
-      const char* e = std::getenv("FASTNN_B200_STAGING");
-      return e ? std::atoi(e) : 0;
-    }();
-    const int deep_stages = stages_for(plan.block_n, false, 1, 2 * fnn::kStagingBytes);
-    // measured on the transformer-block and attention GEMMs: no gain (the stores are not what the
-    // epilogue waits for) and the lost stage costs 256-wide tiles 8 %, so the deep form is opt-in
-    const bool want = staging_env == 2;
-    if (want && deep_stages >= 3) {
-      staging_bytes = 2 * fnn::kStagingBytes;
-      if (plan.stages > deep_stages) plan.stages = deep_stages;
-    }
-  }
+  if (tune.stages >= 1 && tune.stages < plan.stages) plan.stages = tune.stages;
   // A cluster split-K CTA lives for one K slice: no more stages than the slice has k-blocks (but
   // a ring that holds the partial tile), and one accumulator.  The smaller footprint lets CTAs of
   // consecutive launches, or of two clusters, share an SM.  TMEM allocation blocks until columns
@@ -547,12 +590,9 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   // 61 % -> 34 %, cross-partition requests 15.3 M -> 4.5 M, DRAM bytes unchanged).  Measured at
   // 8192^3 on single CTAs: +10 % in a burst, +19 % sustained under the power cap.
   p.l2_a = 3; p.l2_b = 3; p.l2_c = 0;
-  if (const char* e = std::getenv("FASTNN_B200_GROUP_M")) {
-    const int v = std::atoi(e);
-    if (v >= 1 && v <= 1024) p.group_m = v;
-  }
-  if (const char* e = std::getenv("FASTNN_B200_L2")) {          // digits: C, A, B policy
-    const int v = std::atoi(e);
+  if (tune.group_m >= 1 && tune.group_m <= 1024) p.group_m = tune.group_m;
+  if (tune.l2 >= 0) {                                           // digits: C, A, B policy
+    const int v = tune.l2;
     p.l2_c = (v / 100) % 10 % 5; p.l2_a = (v / 10) % 10 % 5; p.l2_b = v % 10 % 5;
   }
 
@@ -561,28 +601,13 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   long long out_ld = g.ldc, out_bs = g.sc;
   long long out_z = g.batch;
   p.cluster_k = plan.cluster_k ? 1 : 0;
-  p.staging_bytes = staging_bytes;
-  {
-    static const int epi_sleep_env = [] {
-      const char* e = std::getenv("FASTNN_B200_EPI_SLEEP");
-      return e ? std::atoi(e) : -1;
-    }();
-    // long main loops only: a tile of a short-K GEMM lasts a few microseconds
-    p.epi_sleep_ns = epi_sleep_env >= 0 ? static_cast<unsigned>(epi_sleep_env) : 0u;
-  }
+  p.n_peers = g.n_peers;
   p.tmem_cols = ck_tmem_cols;
   p.cluster_vec = (plan.cluster_k && (g.n & 3) == 0 && aligned16(g.c) && (g.ldc & 3) == 0 &&
                    (g.batch == 1 || (g.sc & 3) == 0)) ? 1 : 0;
   if (plan.split_k > 1 && !plan.cluster_k) {
     const size_t need = sizeof(float) * static_cast<size_t>(g.m) * g.n * g.batch * plan.split_k;
-    Workspace& ws = st->workspaces[g.stream];
-    if (ws.bytes < need) {
-      if (ws.ptr) FNN_CUDA_OK(cudaFree(ws.ptr));
-      ws.ptr = nullptr; ws.bytes = 0;
-      FNN_CUDA_OK(cudaMalloc(&ws.ptr, need));
-      ws.bytes = need;
-    }
-    out = ws.ptr;
+    if (workspace_reserve(st, st->workspaces, g.stream, need, &out) != 0) return -1;
     out_ld = g.n;
     out_bs = static_cast<long long>(g.m) * g.n;
     out_z = static_cast<long long>(g.batch) * plan.split_k;
@@ -592,20 +617,14 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   const int slabs = ceil_div(g.m, 32);              // 32-row slabs of C, one partial row each
   if (g.colsum != nullptr) {
     const size_t need = sizeof(float) * static_cast<size_t>(slabs) * g.n;
-    Workspace& ws = st->workspaces[g.stream];
-    if (ws.bytes < need) {
-      if (ws.ptr) FNN_CUDA_OK(cudaFree(ws.ptr));
-      ws.ptr = nullptr; ws.bytes = 0;
-      FNN_CUDA_OK(cudaMalloc(&ws.ptr, need));
-      ws.bytes = need;
-    }
-    p.colsum = ws.ptr;
+    if (workspace_reserve(st, st->workspaces, g.stream, need, &p.colsum) != 0) return -1;
   }
   const bool tma_store = !plan.cluster_k && aligned16(out) && (out_ld & 3) == 0 && (out_z == 1 || (out_bs & 3) == 0) &&
                          (plan.split_k > 1 || g.beta == 0.0f) && out_ld < (1ll << 38) &&
                          out_bs < (1ll << 38);
   p.store_mode = tma_store ? 0 : 1;
   p.c = out; p.ldc = out_ld; p.c_batch_stride = out_bs;
+  if (gather && !tma_store) return -1;        // peer tiles leave by TMA store only
 
   CUtensorMap tmA, tmB, tmC;
   const uint64_t B = static_cast<uint64_t>(g.batch);
@@ -657,6 +676,16 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     ok = ok && encode_map(&tmB2, g.b2, g.k2, g.n, 1, g.ldb2 * 4ull, g.ldb2 * 4ull * g.n,
                           fnn::kBlockK, b_cols);
   }
+  fnn::PeerMaps peers;
+  if (gather) {
+    // the same rows of C on the other GPUs: identical shape and strides, another base address
+    std::memset(&peers, 0, sizeof(peers));
+    const uint64_t sc_bytes = (out_z > 1 ? out_bs : out_ld * g.m) * 4ull;
+    for (int i = 0; i < g.n_peers && ok; ++i)
+      ok = g.peer_c[i] != nullptr && aligned16(g.peer_c[i]) &&
+           encode_map(&peers.m[i], g.peer_c[i], g.n, g.m, static_cast<uint64_t>(out_z), out_ld * 4ull,
+                      sc_bytes, 32, 32);
+  }
   if (!ok) return -1;
 
   int grid;
@@ -664,7 +693,16 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     const int clusters = p.total_units < st->max_clusters ? p.total_units : st->max_clusters;
     grid = 2 * clusters;
     const size_t smem = fnn::gemm_pair_smem_bytes(plan.block_n, plan.stages, kb_per_stage);
-    fnn::gemm_tf32_pair_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, p);
+    if (gather)
+      fnn::gemm_tf32_pair_gather_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, peers, p);
+    else
+      fnn::gemm_tf32_pair_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, p);
+  } else if (gather) {
+    grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
+    const size_t smem = fnn::gemm_smem_bytes(plan.block_n, plan.stages);
+    const bool epilogue_work = g.act != 0 || g.bias != nullptr;
+    fnn::gemm_tf32_gather_kernel<<<grid, epilogue_work ? fnn::kNumThreadsWide : fnn::kNumThreads, smem,
+                                   g.stream>>>(tmA, tmB, tmC, peers, p);
   } else if (plan.cluster_k) {
     // one CTA per unit, the split_k slices of a tile as one cluster; also a programmatic dependent
     grid = p.total_units;
@@ -686,16 +724,12 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::gemm_tf32_clusterk_kernel, tmA, tmB, tmC, tmA2, tmB2, p));
   } else {
     grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
-    const size_t smem = fnn::gemm_smem_bytes(plan.block_n, plan.stages, staging_bytes);
+    const size_t smem = fnn::gemm_smem_bytes(plan.block_n, plan.stages);
     // bias, activation, derivative and column sums are a second pass over every output element by
     // the epilogue warps alone: eight of them keep it under a short-K main loop
     const bool epilogue_work = g.act != 0 || g.bias != nullptr || g.colsum != nullptr;
     const int threads = (epilogue_work && plan.split_k == 1) ? fnn::kNumThreadsWide : fnn::kNumThreads;
-    static const bool pdl = [] {
-      const char* e = std::getenv("FASTNN_B200_PDL");
-      return e == nullptr || std::atoi(e) != 0;
-    }();
-    if (pdl) {
+    if (tune.pdl) {
       // programmatic dependent launch: this grid's CTAs may start on SMs the previous kernel of
       // the stream has left; the kernel waits for that kernel's completion before it touches
       // global memory (griddepcontrol.wait), so only its set-up overlaps
@@ -771,12 +805,12 @@ int gemm_dispatch(const GemmArgs& g) {
   const long long b_row = (g.layout == FASTNN_B200_NT) ? g.k : g.n;
   if (g.lda < a_row || g.ldb < b_row || g.ldc < g.n) return -1;
 
-  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g.n_peers < 0 || g.n_peers > fnn::kMaxPeers || (g.n_peers > 0 && g.peer_c == nullptr)) return -1;
   DeviceState* st = current_state();
   if (st == nullptr) return -1;                                   // fastnn_cuda_init not called
-  const Policy pol = g_policy;
+  const Policy pol = t_policy;
   const bool can_tma = tma_operands_ok(g);
-  if (pol.policy >= 2 && !can_tma) return -1;
+  if ((pol.policy >= 2 || g.n_peers > 0) && !can_tma) return -1;
   if (pol.policy == 1 || !can_tma) return launch_simt(g);
   return launch_tcgen05(st, g, pol);
 }
@@ -786,11 +820,7 @@ int gemm_dispatch(const GemmArgs& g) {
 int dual_dispatch(GemmArgs g) {
   const bool pair2_ok = g.k2 >= 1 && aligned16(g.a2) && aligned16(g.b2) && (g.lda2 & 3) == 0 &&
                         (g.ldb2 & 3) == 0;
-  bool fused = false;
-  {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    fused = g_policy.policy != 1 && tma_operands_ok(g) && pair2_ok;
-  }
+  const bool fused = t_policy.policy != 1 && tma_operands_ok(g) && pair2_ok;
   if (fused) return gemm_dispatch(g);
   GemmArgs first = g;
   first.a2 = first.b2 = nullptr; first.k2 = 0; first.bias2 = nullptr;
@@ -802,6 +832,17 @@ int dual_dispatch(GemmArgs g) {
   return gemm_dispatch(second);
 }
 
+// The driver's tensor-map encoder, looked up once per process.
+int resolve_encoder() {
+  if (g_encode.load(std::memory_order_acquire) != nullptr) return 0;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  FNN_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+  if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return -1;
+  g_encode.store(reinterpret_cast<EncodeTiledFn>(fn), std::memory_order_release);
+  return 0;
+}
+
 }  // namespace
 
 // ============================================================ drop-in symbols ===
@@ -811,7 +852,7 @@ extern "C" int fastnn_cuda_init(int device_id) {
   FNN_CUDA_OK(cudaSetDevice(device_id));
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState& st = g_dev[device_id];
-  if (st.ready) return 0;
+  if (st.ready.load(std::memory_order_acquire)) return 0;
   cudaDeviceProp prop;
   FNN_CUDA_OK(cudaGetDeviceProperties(&prop, device_id));
   if (prop.major != 10) {
@@ -819,15 +860,19 @@ extern "C" int fastnn_cuda_init(int device_id) {
                  device_id, prop.major, prop.minor);
     return -1;
   }
-  if (g_encode == nullptr) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    FNN_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
-    if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return -1;
-    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-  }
+  if (resolve_encoder() != 0) return -1;
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_kernel,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kMaxDynSmem)));
+  FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_gather_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kMaxDynSmem)));
+  FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_pair_gather_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kMaxDynSmem)));
+  FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kMaxDynSmem)));
+  FNN_CUDA_OK(cudaFuncSetAttribute(fnn::attention_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
   st.num_sms = prop.multiProcessorCount;
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_clusterk_kernel,
@@ -899,7 +944,7 @@ extern "C" int fastnn_cuda_init(int device_id) {
     const long long ms = std::atoll(e);
     if (ms > 0) st.spin_budget = ms * khz;
   }
-  st.ready = true;
+  st.ready.store(true, std::memory_order_release);
   return 0;
 }
 
@@ -1079,8 +1124,6 @@ static int conv_forward_impl(const float* input, const float* weight, const floa
       act < 0 || act > 1)
     return -1;
   if (input_h + 2 * pad_h < kernel_h || input_w + 2 * pad_w < kernel_w) return -1;
-  // the gather packs (offset inside the image, tap index) into 32 bits and keeps a 64-bit tap mask
-  if (1ll * kernel_h * kernel_w > 63 || 1ll * in_channels * input_h * input_w >= (1ll << 25)) return -1;
   if (batch_size == 0) return 0;
   if (input == nullptr || weight == nullptr || output == nullptr) return -1;
   const int oh = (input_h + 2 * pad_h - kernel_h) / stride_h + 1;      // cuda/kernels.cu:903-904
@@ -1091,16 +1134,22 @@ static int conv_forward_impl(const float* input, const float* weight, const floa
   const int k = static_cast<int>(k_ll);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState* st = current_state();
   if (st == nullptr) return -1;
-  static bool attr_set[kMaxDevices] = {};
-  int dev = 0;
-  FNN_CUDA_OK(cudaGetDevice(&dev));
-  if (!attr_set[dev]) {
-    FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kMaxDynSmem)));
-    attr_set[dev] = true;
+  // The gather packs (offset inside the image, tap index) into 32 bits and keeps a 64-bit tap
+  // mask.  Kernels of 64 taps or more and images of 2^25 elements or more go to the direct kernel
+  // (FP32 FMA, one thread per output element): rare shapes, served rather than refused.
+  if (1ll * kernel_h * kernel_w > 63 || 1ll * in_channels * input_h * input_w >= (1ll << 25)) {
+    const long long total = positions * out_channels;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 64ll * st->num_sms) blocks = 64ll * st->num_sms;
+    fnn::conv2d_direct_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        input, weight, bias, output, batch_size, in_channels, out_channels, input_h, input_w, kernel_h,
+        kernel_w, stride_h, stride_w, pad_h, pad_w, oh, ow, act, flip_transpose ? 1 : 0);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    FNN_CUDA_OK(cudaGetLastError());
+    t_last = LastCall{7, 0, 1, static_cast<int>(blocks)};
+    return 0;
   }
   // weights are [co, k] row-major: K-major for the tensor core as they stand.  TMA needs 16-byte
   // rows; otherwise (k = 27 for a 3x3 kernel on RGB) a zero-padded copy goes to the workspace.
@@ -1112,19 +1161,14 @@ static int conv_forward_impl(const float* input, const float* weight, const floa
   // workspace of this stream: [the gather's table, one int4 per k] [padded / flipped weights]
   const size_t tab_bytes = sizeof(int4) * static_cast<size_t>(k_pad);
   const size_t w_bytes = copy_w ? sizeof(float) * static_cast<size_t>(out_channels) * k_pad : 0;
-  Workspace& ws = st->workspaces[s];
-  if (ws.bytes < tab_bytes + w_bytes) {
-    if (ws.ptr) FNN_CUDA_OK(cudaFree(ws.ptr));
-    ws.ptr = nullptr; ws.bytes = 0;
-    FNN_CUDA_OK(cudaMalloc(&ws.ptr, tab_bytes + w_bytes));
-    ws.bytes = tab_bytes + w_bytes;
-  }
-  int4* ktab = reinterpret_cast<int4*>(ws.ptr);
+  float* ws_ptr = nullptr;
+  if (workspace_reserve(st, st->workspaces, s, tab_bytes + w_bytes, &ws_ptr) != 0) return -1;
+  int4* ktab = reinterpret_cast<int4*>(ws_ptr);
   fnn::conv_ktab_kernel<<<ceil_div(k_pad, 256), 256, 0, s>>>(ktab, k_pad, k, kernel_h, kernel_w, input_h,
                                                             input_w);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   if (copy_w) {
-    float* wdst = reinterpret_cast<float*>(reinterpret_cast<char*>(ws.ptr) + tab_bytes);
+    float* wdst = reinterpret_cast<float*>(reinterpret_cast<char*>(ws_ptr) + tab_bytes);
     long long blocks = (1ll * out_channels * k_pad + 255) / 256;
     if (blocks > 1024) blocks = 1024;
     if (flip_transpose)
@@ -1153,13 +1197,6 @@ static int conv_forward_impl(const float* input, const float* weight, const floa
   p.num_stages = stages > fnn::kMaxStages ? fnn::kMaxStages : stages;
   p.x = input; p.ktab = ktab; p.bias = bias; p.out = output; p.act = act;
   p.status = st->status; p.spin_budget = st->spin_budget;
-  {
-    static const int sleep_env = [] {
-      const char* e = std::getenv("FASTNN_B200_CONV_POLL_SLEEP");
-      return e ? std::atoi(e) : -1;
-    }();
-    p.poll_sleep_ns = sleep_env >= 0 ? static_cast<unsigned>(sleep_env) : 0u;
-  }
   CUtensorMap tmW;
   if (!encode_map(&tmW, wsrc, static_cast<uint64_t>(w_ld == k ? k : w_ld), out_channels, 1, w_ld * 4ull,
                   w_ld * 4ull * out_channels, fnn::kBlockK, p.block_n))
@@ -1195,22 +1232,42 @@ extern "C" int fastnn_b200_conv2d_forward(const float* input, const float* weigh
 // grad_input[n, ci, iy, ix] = sum over (co, ki, kj) of grad_output[n, co, iy + ph - ki, ix + pw - kj]
 // * weight[co, ci, ki, kj] for a stride-1 convolution: with ki' = kh-1-ki this is the forward
 // kernel run on grad_output (co channels in, ci out) with the kernel reversed and padding
-// kh-1-ph.  Strides other than 1 are not covered (-1).
+// kh-1-ph.  Any other stride, and padding beyond kernel - 1, take the gather-form kernel: every
+// grad_input element adds up the (co, ki, kj) terms whose output position (iy + ph - ki) / stride
+// exists -- what FastNN's GEMM + col2im computes (cuda/kernels.cu:862-893, 949-987), without the
+// column matrix and without atomics.
 extern "C" int fastnn_b200_conv2d_backward_data(const float* grad_output, const float* weight,
                                                 float* grad_input, int batch_size, int in_channels,
                                                 int out_channels, int input_h, int input_w,
                                                 int output_h, int output_w, int kernel_h,
                                                 int kernel_w, int stride_h, int stride_w, int pad_h,
                                                 int pad_w, void* stream) {
-  if (stride_h != 1 || stride_w != 1) return -1;
-  if (kernel_h < 1 || kernel_w < 1 || pad_h < 0 || pad_w < 0 || pad_h > kernel_h - 1 ||
-      pad_w > kernel_w - 1)
+  if (batch_size < 0 || in_channels < 1 || out_channels < 1 || input_h < 1 || input_w < 1 ||
+      kernel_h < 1 || kernel_w < 1 || stride_h < 1 || stride_w < 1 || pad_h < 0 || pad_w < 0)
     return -1;
-  if (output_h != input_h + 2 * pad_h - kernel_h + 1 || output_w != input_w + 2 * pad_w - kernel_w + 1)
+  if (input_h + 2 * pad_h < kernel_h || input_w + 2 * pad_w < kernel_w) return -1;
+  if (output_h != (input_h + 2 * pad_h - kernel_h) / stride_h + 1 ||
+      output_w != (input_w + 2 * pad_w - kernel_w) / stride_w + 1)
     return -1;
-  return conv_forward_impl(grad_output, weight, nullptr, grad_input, batch_size, out_channels,
-                           in_channels, output_h, output_w, kernel_h, kernel_w, 1, 1,
-                           kernel_h - 1 - pad_h, kernel_w - 1 - pad_w, 0, stream, true);
+  if (stride_h == 1 && stride_w == 1 && pad_h <= kernel_h - 1 && pad_w <= kernel_w - 1)
+    return conv_forward_impl(grad_output, weight, nullptr, grad_input, batch_size, out_channels,
+                             in_channels, output_h, output_w, kernel_h, kernel_w, 1, 1,
+                             kernel_h - 1 - pad_h, kernel_w - 1 - pad_w, 0, stream, true);
+  if (batch_size == 0) return 0;
+  if (grad_output == nullptr || weight == nullptr || grad_input == nullptr) return -1;
+  DeviceState* st = current_state();
+  if (st == nullptr) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long total = 1ll * batch_size * in_channels * input_h * input_w;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 64ll * st->num_sms) blocks = 64ll * st->num_sms;
+  fnn::conv2d_backward_data_direct_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+      grad_output, weight, grad_input, batch_size, in_channels, out_channels, input_h, input_w, output_h,
+      output_w, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  FNN_CUDA_OK(cudaGetLastError());
+  t_last = LastCall{7, 0, 1, static_cast<int>(blocks)};
+  return 0;
 }
 
 // FastNN's own entry (cuda/kernels.cu:949-987): same arguments, default stream.
@@ -1257,22 +1314,11 @@ extern "C" int fastnn_b200_conv2d_backward_weight(const float* input, const floa
   const size_t col_floats = static_cast<size_t>(batch_size) * k * ldp;
   const size_t part_floats = static_cast<size_t>(batch_size) * out_channels * k;
   float* col = nullptr;
-  int num_sms = 0;
-  {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    DeviceState* st = current_state();
-    if (st == nullptr) return -1;
-    num_sms = st->num_sms;
-    Workspace& ws = st->conv_ws[s];
-    const size_t need = sizeof(float) * (col_floats + part_floats + 64);
-    if (ws.bytes < need) {
-      if (ws.ptr) FNN_CUDA_OK(cudaFree(ws.ptr));
-      ws.ptr = nullptr; ws.bytes = 0;
-      FNN_CUDA_OK(cudaMalloc(&ws.ptr, need));
-      ws.bytes = need;
-    }
-    col = ws.ptr;
-  }
+  DeviceState* st = current_state();
+  if (st == nullptr) return -1;
+  const int num_sms = st->num_sms;
+  if (workspace_reserve(st, st->conv_ws, s, sizeof(float) * (col_floats + part_floats + 64), &col) != 0)
+    return -1;
   float* partials = col + ((col_floats + 63) / 64) * 64;  // keeps the 16-byte alignment
   long long blocks = (1ll * batch_size * k + 3) / 4;               // four rows of col per block and turn
   if (blocks > 32ll * num_sms) blocks = 32ll * num_sms;
@@ -1337,18 +1383,8 @@ extern "C" int fastnn_b200_attention_forward(const float* q, const float* k, con
   fnn::AttnSmem plan = fnn::attn_smem_plan(head_dim, tk_pad, nsets);
   while (plan.total > kMaxDynSmem && nsets > 1) plan = fnn::attn_smem_plan(head_dim, tk_pad, --nsets);
   if (plan.total > kMaxDynSmem) return -1;
-  std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState* st = current_state();
   if (st == nullptr) return -1;
-  static bool attr_set[kMaxDevices] = {};
-  int dev = 0;
-  FNN_CUDA_OK(cudaGetDevice(&dev));
-  if (!attr_set[dev]) {
-    FNN_CUDA_OK(cudaFuncSetAttribute(fnn::attention_tf32_kernel,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kMaxDynSmem)));
-    attr_set[dev] = true;
-  }
   fnn::AttnParams p;
   std::memset(&p, 0, sizeof(p));
   p.heads = batch_heads; p.tq = t_q; p.tk = t_k; p.d = head_dim; p.tk_pad = tk_pad;
@@ -1394,7 +1430,6 @@ extern "C" int fastnn_b200_reduce_partials(const float* partials, float* c, int 
   if (m < 0 || n < 0 || count < 1 || act < 0 || act > 2 || ldc < n) return -1;
   if (m == 0 || n == 0) return 0;
   if (partials == nullptr || c == nullptr) return -1;
-  std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState* st = current_state();
   if (st == nullptr) return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1419,10 +1454,9 @@ extern "C" int fastnn_b200_set_policy(int policy, int block_n, int split_k) {
   if (policy < 0 || policy > 6) return -1;
   if (block_n < 0 || block_n > fnn::kMaxBlockN || (block_n % 32) != 0) return -1;
   if (split_k < 0) return -1;
-  std::lock_guard<std::mutex> lock(g_mutex);
-  g_policy.policy = policy;
-  g_policy.block_n = block_n;
-  g_policy.split_k = split_k;
+  t_policy.policy = policy;
+  t_policy.block_n = block_n;
+  t_policy.split_k = split_k;
   return 0;
 }
 
@@ -1442,9 +1476,9 @@ extern "C" int fastnn_b200_plan_query(int layout, int m, int n, int k, int batch
   int num_sms = 148, max_clusters = 74;
   int slots[5] = {0, 148, 132, 120, 112}, slots_half[5] = {0, 148, 132, 120, 112};   // as a B200 reports
   {
-    std::lock_guard<std::mutex> lock(g_mutex);
     int dev = -1;
-    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) {
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices &&
+        g_dev[dev].ready.load(std::memory_order_acquire)) {
       num_sms = g_dev[dev].num_sms;
       max_clusters = g_dev[dev].max_clusters;
       for (int i = 0; i < 5; ++i) { slots[i] = g_dev[dev].ck_slots[i]; slots_half[i] = g_dev[dev].ck_slots_half[i]; }
@@ -1462,16 +1496,72 @@ extern "C" int fastnn_b200_plan_query(int layout, int m, int n, int k, int batch
   return 0;
 }
 
+// Defined with the allocation-free entry below: that entry's own status word, 0 when the entry
+// has not been used on the device.
+static int static_status_read_clear(int dev, unsigned int* value);
+
 extern "C" int fastnn_b200_device_status(unsigned int* status) {
-  std::lock_guard<std::mutex> lock(g_mutex);
-  DeviceState* st = current_state();
-  if (st == nullptr) return -1;
+  int dev = -1;
+  FNN_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return -1;
   FNN_CUDA_OK(cudaDeviceSynchronize());
   unsigned int v = 0;
-  FNN_CUDA_OK(cudaMemcpy(&v, st->status, sizeof(v), cudaMemcpyDeviceToHost));
-  if (v != 0) FNN_CUDA_OK(cudaMemset(st->status, 0, sizeof(v)));
-  if (status) *status = v;
+  DeviceState* st = current_state();
+  if (st != nullptr) {
+    FNN_CUDA_OK(cudaMemcpy(&v, st->status, sizeof(v), cudaMemcpyDeviceToHost));
+    if (v != 0) FNN_CUDA_OK(cudaMemset(st->status, 0, sizeof(v)));
+  }
+  // kernels of fastnn_b200_gemm_splitk_static report into a word of their own (that entry works
+  // without fastnn_cuda_init): the first non-zero code of the two is returned, both are cleared
+  unsigned int vs = 0;
+  if (static_status_read_clear(dev, &vs) != 0) return -1;
+  if (status) *status = v != 0 ? v : vs;
   return 0;
+}
+
+extern "C" int fastnn_b200_selftest_bounded_wait(unsigned int budget_us, unsigned int* waited_us) {
+  DeviceState* st = current_state();
+  if (st == nullptr) return -1;
+  if (budget_us < 1 || budget_us > 100000) return -1;            // 1 us .. 0.1 s
+  int dev = 0, khz = 0;
+  FNN_CUDA_OK(cudaGetDevice(&dev));
+  if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev) != cudaSuccess || khz <= 0) {
+    (void)cudaGetLastError();
+    khz = 2000000;
+  }
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.status = st->status;
+  p.spin_budget = static_cast<long long>(budget_us) * khz / 1000;   // ticks at the maximum clock
+  unsigned int* out = nullptr;
+  FNN_CUDA_OK(cudaMalloc(&out, 2 * sizeof(unsigned int)));
+  int rc = -1;
+  unsigned int host[2] = {0u, 0u};
+  if (cudaMemset(out, 0, 2 * sizeof(unsigned int)) == cudaSuccess) {
+    fnn::bounded_wait_selftest_kernel<<<1, 32>>>(p, fnn::kStatusSelfTest, out);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (cudaGetLastError() == cudaSuccess && cudaDeviceSynchronize() == cudaSuccess &&
+        cudaMemcpy(host, out, sizeof(host), cudaMemcpyDeviceToHost) == cudaSuccess)
+      rc = host[0] == 1u ? 0 : -1;        // the wait must have given up
+  }
+  (void)cudaGetLastError();
+  (void)cudaFree(out);
+  if (waited_us) *waited_us = static_cast<unsigned int>(1000ull * host[1] / static_cast<unsigned>(khz));
+  return rc;
+}
+
+extern "C" int fastnn_b200_gemm_gather_ex(int layout, const float* a, const float* b, float* c, int m,
+                                          int n, int k, int batch, long long lda, long long ldb,
+                                          long long ldc, long long stride_a, long long stride_b,
+                                          long long stride_c, float alpha, const float* bias, int act,
+                                          float* const* peer_c, int n_peers, void* stream) {
+  if (n_peers < 0 || n_peers > fnn::kMaxPeers) return -1;
+  if (n_peers > 0 && peer_c == nullptr) return -1;
+  GemmArgs g{layout, a, b, c, m, n, k, batch, lda, ldb, ldc, stride_a, stride_b, stride_c,
+             alpha, 0.0f, bias, act, static_cast<cudaStream_t>(stream)};
+  g.peer_c = peer_c;
+  g.n_peers = n_peers;
+  return gemm_dispatch(g);
 }
 
 extern "C" unsigned long long fastnn_b200_launch_count(void) {
@@ -1524,13 +1614,7 @@ int static_setup(int dev, StaticState** out) {
     FNN_CUDA_OK(cudaGetSymbolAddress(&p, g_static_status));
     st.status = static_cast<unsigned int*>(p);
     if (st.scratch == nullptr || st.status == nullptr) return -1;
-    if (g_encode == nullptr) {
-      void* fn = nullptr;
-      cudaDriverEntryPointQueryResult qres;
-      FNN_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
-      if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return -1;
-      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-    }
+    if (resolve_encoder() != 0) return -1;
     FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_kernel,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(kMaxDynSmem)));
@@ -1543,6 +1627,20 @@ int static_setup(int dev, StaticState** out) {
 }
 
 }  // namespace
+
+// Reads and clears the status word of the allocation-free entry on device `dev` (current).  A
+// plain copy from the symbol's address: nothing is allocated.  0 when the entry was never used.
+static int static_status_read_clear(int dev, unsigned int* value) {
+  *value = 0;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  const StaticState& st = g_static[dev];
+  if (!st.ready) return 0;
+  unsigned int v = 0;
+  FNN_CUDA_OK(cudaMemcpy(&v, st.status, sizeof(v), cudaMemcpyDeviceToHost));
+  if (v != 0) FNN_CUDA_OK(cudaMemset(st.status, 0, sizeof(v)));
+  *value = v;
+  return 0;
+}
 
 extern "C" int fastnn_b200_gemm_splitk_static(int layout, const float* a, const float* b, float* c,
                                               int m, int n, int k, int split_k, void* stream) {

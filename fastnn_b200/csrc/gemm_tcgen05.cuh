@@ -48,6 +48,7 @@ enum : unsigned int {
   kStatusMmaTimeout = 0x102,
   kStatusEpilogueTimeout = 0x103,
   kStatusMmaTmemTimeout = 0x104,
+  kStatusSelfTest = 0x1F0,          // bounded_wait_selftest_kernel: the wait gave up, as it must
 };
 
 // 1, 2: forward activations.  3, 4: the output is multiplied by the activation's derivative at
@@ -68,9 +69,8 @@ struct GemmParams {
                        // partial tiles through distributed shared memory (gemm_tf32_clusterk_kernel)
   int cluster_vec;     // that kernel may store float4s: n, ldc, batch stride multiples of 4, C aligned
   int tmem_cols;       // that kernel's TMEM allocation: one accumulator, a power of two >= block_n
-  int staging_bytes;   // single-CTA kernel: shared memory for the epilogue's 4 KiB staging tiles, shared
-                       // evenly by its warps (0 = kStagingBytes; 2 * kStagingBytes lets a warp issue
-                       // four stores, or two with eight warps, before it must wait for one to be read)
+  int n_peers;         // gather kernels: every finished tile is also stored through this many extra
+                       // tensor maps (the same rows of C in other GPUs' memory); 0 elsewhere
   int kb_per_stage;    // 32-deep k-blocks per pipeline stage (CTA-pair kernel only; else 1)
   int total_units;     // batch * tiles_m * tiles_n * split_k
   int a_mn_major;      // A stored [k, m]
@@ -93,8 +93,14 @@ struct GemmParams {
   long long ldc, c_batch_stride;   // elements
   unsigned int* status;
   long long spin_budget;           // clock64 ticks a single wait may last
-  unsigned int epi_sleep_ns;       // > 0: epilogue threads sleep this long between polls of the
-                                   // accumulator-full barrier (they wait there for a whole main loop)
+};
+
+// Extra destinations of a gather launch: tensor maps over the rows this GPU computes, as they lie
+// in the full C of up to seven other GPUs (peer-mapped memory).  Stores only -- nothing is ever
+// loaded through these maps.
+constexpr int kMaxPeers = 7;
+struct PeerMaps {
+  CUtensorMap m[kMaxPeers];
 };
 
 struct Unit {
@@ -118,48 +124,37 @@ __device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u) {
   return w;
 }
 
+// 0.5 x (1 + erf(x / sqrt 2)) with the library erff, the form FastNN's CPU path (libm erff,
+// src/tensor/ops.rs:220-230) and its CUDA kernel (cuda/kernels.cu:236-242) both evaluate; every
+// epilogue of this library -- by-column, split-K reduce, cluster reduce -- goes through here.
+__device__ __forceinline__ float gelu_erf(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.7071067811865475f));
+}
+
 __device__ __forceinline__ float apply_act(float x, int act) {
   if (act == kActRelu) return fmaxf(x, 0.0f);
-  if (act == kActGelu) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+  if (act == kActGelu) return gelu_erf(x);
   return x;
 }
 
-// The epilogue warps are few, so the tensor-core kernels evaluate the Gaussian CDF branch-free
-// and short: erf(z) = 1 - P(t) exp(-z^2) with t = 1/(1 + 0.3275911 z), z = |x|/sqrt 2
-// (Abramowitz & Stegun 7.1.26, |error| <= 1.5e-7: two orders below the TF32 rounding of the
-// product it multiplies).  e returns exp(-x^2/2), which the derivative needs as the density.
-__device__ __forceinline__ float gelu_cdf_fast(float x, float* e_out = nullptr) {
-  const float z = fabsf(x) * 0.70710678118654752440f;
-  const float e = __expf(-z * z);
-  const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
-  float poly = fmaf(1.061405429f, t, -1.453152027f);
-  poly = fmaf(poly, t, 1.421413741f);
-  poly = fmaf(poly, t, -0.284496736f);
-  poly = fmaf(poly, t, 0.254829592f);
-  const float erf_abs = fmaf(-poly * t, e, 1.0f);
-  if (e_out != nullptr) *e_out = e;
-  return fmaf(0.5f, copysignf(erf_abs, x), 0.5f);
-}
-
-// d act / dx at the saved pre-activation x: 1 or 0 for ReLU; Phi(x) + x phi(x) for erf-GELU.
+// d act / dx at the saved pre-activation x: 1 or 0 for ReLU; Phi(x) + x phi(x) for erf-GELU, term
+// by term as FastNN's kernel_gelu_backward (cuda/kernels.cu:244-252).
 __device__ __forceinline__ float apply_act_grad(float x, int act) {
   if (act == kActReluGrad) return x > 0.0f ? 1.0f : 0.0f;
-  float e;
-  const float cdf = gelu_cdf_fast(x, &e);
-  return fmaf(x * 0.3989422804014327f, e, cdf);
+  const float cdf = 0.5f * (1.0f + erff(x * 0.7071067811865475f));
+  const float pdf = __expf(-0.5f * x * x) * 0.3989422804014327f;
+  return cdf + x * pdf;
 }
 
 // Bounded wait.  Returns false when the CTA is aborting (this role's budget ran out, or
 // another role's did).
 __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                             const GemmParams& p, unsigned int code,
-                                             unsigned int sleep_ns = 0) {
+                                             const GemmParams& p, unsigned int code) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int it = 0;
   while (true) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
-    if (sleep_ns != 0) __nanosleep(sleep_ns);
     if ((++it & 63) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > p.spin_budget) {
@@ -173,10 +168,9 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, vola
 }
 
 // Before a staging tile is overwritten: all but the newest nbuf - 1 stores of this thread have
-// read their source (nbuf = staging tiles the warp cycles through: 1, 2 or 4).
+// read their source (nbuf = staging tiles the warp cycles through: 1 or 2).
 __device__ __forceinline__ void staging_wait(int nbuf) {
-  if (nbuf == 4) ptx::tma_store_wait_read<3>();
-  else if (nbuf == 2) ptx::tma_store_wait_read<1>();
+  if (nbuf == 2) ptx::tma_store_wait_read<1>();
   else ptx::tma_store_wait_read<0>();
 }
 
@@ -190,7 +184,8 @@ __device__ __forceinline__ void epilogue_drain_plain(const GemmParams& p, const 
                                                      uint32_t taddr0, uint32_t staging,
                                                      uint8_t* staging_gen, int& buf, int m0, int n0,
                                                      int cz, int cb, bool raw, int lane, int c_first,
-                                                     int c_step, int nbuf) {
+                                                     int c_step, int nbuf,
+                                                     const CUtensorMap* peers, int n_peers) {
   const int row = m0 + lane;
   for (int c = c_first; c < p.block_n / 32; c += c_step) {
     const int col0 = n0 + c * 32;
@@ -230,6 +225,9 @@ __device__ __forceinline__ void epilogue_drain_plain(const GemmParams& p, const 
         if (p.l2_c != 0) ptx::tma_store_3d_hint(tmC, staging + buf * 4096, col0, m0, cz,
                                                  ptx::make_l2_policy(p.l2_c));
         else ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
+        // gather launches: the same tile into the same rows of C on every other GPU, one bulk
+        // group with the local store, so the staging tile is free once all of them have read it
+        for (int i = 0; i < n_peers; ++i) ptx::tma_store_3d(peers + i, staging + buf * 4096, col0, m0, cz);
         ptx::tma_store_commit();
       }
       buf = (buf + 1) & (nbuf - 1);
@@ -253,7 +251,8 @@ __device__ __forceinline__ void epilogue_drain_by_column(const GemmParams& p, co
                                                       uint32_t taddr0, uint32_t staging,
                                                       uint8_t* staging_gen, int& buf, int m0, int n0,
                                                       int cz, int cb, bool raw, int lane,
-                                                      int c_first, int c_step, int nbuf) {
+                                                      int c_first, int c_step, int nbuf,
+                                                      const CUtensorMap* peers, int n_peers) {
   const int row = m0 + lane;
   const bool grad = !raw && (p.act == kActReluGrad || p.act == kActGeluGrad);
   const bool want_colsum = p.colsum != nullptr && !raw;
@@ -341,7 +340,7 @@ __device__ __forceinline__ void epilogue_drain_by_column(const GemmParams& p, co
           for (int rr = 0; rr < 32; ++rr) t[rr] = fmaxf(t[rr], 0.0f);
         } else if (p.act == kActGelu) {
 #pragma unroll
-          for (int rr = 0; rr < 32; ++rr) t[rr] *= gelu_cdf_fast(t[rr]);
+          for (int rr = 0; rr < 32; ++rr) t[rr] = gelu_erf(t[rr]);
         } else if (p.act == kActReluGrad) {
 #pragma unroll
           for (int rr = 0; rr < 32; ++rr) t[rr] = x[rr] > 0.0f ? t[rr] : 0.0f;
@@ -379,6 +378,7 @@ __device__ __forceinline__ void epilogue_drain_by_column(const GemmParams& p, co
           if (p.l2_c != 0) ptx::tma_store_3d_hint(tmC, staging + buf * 4096, col0, m0, cz,
                                                    ptx::make_l2_policy(p.l2_c));
           else ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
+          for (int i = 0; i < n_peers; ++i) ptx::tma_store_3d(peers + i, staging + buf * 4096, col0, m0, cz);
           ptx::tma_store_commit();
         }
       }
@@ -399,14 +399,16 @@ __device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const C
                                                     uint32_t taddr0, uint32_t staging,
                                                     uint8_t* staging_gen, int& buf, int m0, int n0,
                                                     int cz, int cb, bool raw, int lane,
-                                                    int c_first = 0, int c_step = 1, int nbuf = 2) {
+                                                    int c_first = 0, int c_step = 1, int nbuf = 2,
+                                                    const CUtensorMap* peers = nullptr,
+                                                    int n_peers = 0) {
   const bool by_column = !raw && (p.bias != nullptr || p.act != kActNone || p.colsum != nullptr);
   if (by_column)
     epilogue_drain_by_column(p, tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, cb, raw, lane,
-                             c_first, c_step, nbuf);
+                             c_first, c_step, nbuf, peers, n_peers);
   else
     epilogue_drain_plain(p, tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, cb, raw, lane,
-                         c_first, c_step, nbuf);
+                         c_first, c_step, nbuf, peers, n_peers);
 }
 
 // Pitch in bytes of one row of the partial tile a cluster split-K CTA leaves in shared memory:
@@ -421,10 +423,13 @@ __host__ __device__ constexpr uint32_t cluster_partial_pitch(int block_n) {
 // shared memory, and after a cluster barrier CTA r adds rows [r, r+1) * 128 / split_k of all
 // slices in ascending slice order (deterministic) over distributed shared memory, applies
 // alpha / beta / bias / activation and writes C.  No workspace, no second kernel.
-template <bool kClusterK>
+// kGather = true (persistent form only): every finished tile is also stored through the
+// p.n_peers tensor maps of `peers`, i.e. into the same rows of C on the other GPUs.
+template <bool kClusterK, bool kGather = false>
 __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
                                                const CUtensorMap& tmC, const CUtensorMap& tmA2,
-                                               const CUtensorMap& tmB2, const GemmParams& p) {
+                                               const CUtensorMap& tmB2, const GemmParams& p,
+                                               const CUtensorMap* peers = nullptr) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 B.
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -433,16 +438,10 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_epi_warps = static_cast<int>(blockDim.x >> 5) - kEpilogueWarp0;     // 4 or 8
-  // The next kernel of the stream may take over SMs as this grid's CTAs finish: its set-up
-  // (barriers, TMEM, tensor-map prefetch) then overlaps this grid's last tiles.
-  ptx::grid_dep_launch_dependents();
-
   const uint32_t stage_b_bytes = static_cast<uint32_t>(p.block_n) * kBlockK * 4;
   const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
   const uint32_t staging_base = smem_base + p.num_stages * stage_bytes;
-  const uint32_t staging_total = kClusterK ? 0u                            // no staging tiles there
-                                 : (p.staging_bytes > 0 ? static_cast<uint32_t>(p.staging_bytes)
-                                                        : static_cast<uint32_t>(kStagingBytes));
+  const uint32_t staging_total = kClusterK ? 0u : static_cast<uint32_t>(kStagingBytes);   // none there
   const uint32_t bar_base = staging_base + staging_total;
   // barrier layout: full[8] empty[8] tmem_full[2] tmem_empty[2] | tmem address | abort flag
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -520,6 +519,9 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
       ptx::prefetch_tensormap(&tmA2);
       ptx::prefetch_tensormap(&tmB2);
     }
+    if constexpr (kGather) {
+      for (int i = 0; i < p.n_peers; ++i) ptx::prefetch_tensormap(peers + i);
+    }
     // Everything above touched no global data; from here on the kernels before this one in
     // the stream must be complete (a no-op unless launched as a programmatic dependent).
     ptx::grid_dep_wait();
@@ -543,6 +545,13 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
+  // From here the next kernel of the stream (if launched as a programmatic dependent) may place
+  // its CTAs on SMs this grid has left, so its set-up overlaps this grid's last tiles.  Issued
+  // only now, after this CTA holds its tensor-memory columns: a dependent CTA that became
+  // resident beside a CTA still waiting in tcgen05.alloc could take the columns that CTA needs
+  // and then sit in griddepcontrol.wait for it -- with the trigger here, every CTA of this grid
+  // has its allocation before any dependent can be scheduled.
+  ptx::grid_dep_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer ---
@@ -642,7 +651,7 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
     const int groups = n_epi_warps >> 2;             // 1 or 2
     const int group = (warp - kEpilogueWarp0) >> 2;
     const uint32_t staging_per_warp = staging_total / static_cast<uint32_t>(n_epi_warps);
-    const int nbuf = static_cast<int>(staging_per_warp >> 12);          // 4 KiB tiles: 1, 2 or 4
+    const int nbuf = static_cast<int>(staging_per_warp >> 12);          // 4 KiB tiles: 2, or 1 with eight warps
     const uint32_t staging = staging_base + (warp - kEpilogueWarp0) * staging_per_warp;
     uint8_t* staging_gen = smem_gen + (staging - smem_base);
     int acc = 0;
@@ -681,7 +690,7 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
         for (int c = group; c < p.block_n / 32 && n0 + c * 32 < p.n; c += groups)
           ptx::prefetch_l2(arow + c * 32);
       }
-      ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout, p.epi_sleep_ns);
+      ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
       ok = __all_sync(0xffffffffu, ok);              // keep the warp converged for tcgen05.ld
       if (!ok) break;
       ptx::tc_fence_after_sync();
@@ -689,7 +698,7 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
                               static_cast<uint32_t>(acc * kMaxBlockN);
       const int cz = raw ? (w.b * p.split_k + w.s) : w.b;   // outer coordinate of the store
       epilogue_drain_tile(p, &tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, w.b, raw, lane,
-                          group, groups, nbuf);
+                          group, groups, nbuf, kGather ? peers : nullptr, kGather ? p.n_peers : 0);
       // accumulator drained: hand it back to the MMA warp
       ptx::tc_fence_before_sync();
       __syncwarp();
@@ -791,15 +800,51 @@ gemm_tf32_clusterk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   gemm_tf32_body<true>(tmA, tmB, tmC, tmA2, tmB2, p);
 }
 
+// The persistent kernel whose epilogue also stores every tile into other GPUs' copies of C (an
+// all-gather of C fused into the GEMM: no collective afterwards, only a barrier between ranks).
+__global__ void __launch_bounds__(kNumThreadsWide, 1)
+gemm_tf32_gather_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmC, const __grid_constant__ PeerMaps peers,
+                        const __grid_constant__ GemmParams p) {
+  gemm_tf32_body<false, true>(tmA, tmB, tmC, tmA, tmB, p, peers.m);
+}
+
+// One warp, one mbarrier that nothing ever arrives on, and the GEMM kernels' own bounded wait:
+// the wait must give up after p.spin_budget clock ticks, leave `code` in the status word and
+// return false.  No TMA, no tensor memory, nothing in flight -- the kernel cannot fault or hang.
+// out[0] = 1 when the wait returned false (as it must), out[1] = ticks it lasted (low 32 bits).
+__global__ void __launch_bounds__(32, 1)
+bounded_wait_selftest_kernel(const __grid_constant__ GemmParams p, unsigned int code,
+                             unsigned int* out) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  __shared__ volatile int abort_storage;
+  const uint32_t bar = ptx::smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(bar, 1);
+    abort_storage = 0;
+    ptx::fence_mbar_init();
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    const long long t0 = clock64();
+    const bool got = wait_barrier(bar, 0u, &abort_storage, p, code);
+    const long long dt = clock64() - t0;
+    if (out != nullptr) {
+      out[0] = got ? 0u : 1u;
+      out[1] = static_cast<unsigned int>(dt);
+    }
+  }
+}
+
 // Bytes of dynamic shared memory the cluster split-K kernel needs (no staging tiles).
 inline size_t gemm_clusterk_smem_bytes(int block_n, int num_stages) {
   return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + block_n * kBlockK * 4) + kBarrierBytes;
 }
 
 // Bytes of dynamic shared memory a launch with these parameters needs.
-inline size_t gemm_smem_bytes(int block_n, int num_stages, int staging_bytes = kStagingBytes) {
+inline size_t gemm_smem_bytes(int block_n, int num_stages) {
   return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + block_n * kBlockK * 4) +
-         staging_bytes + kBarrierBytes;
+         kStagingBytes + kBarrierBytes;
 }
 
 }  // namespace fnn

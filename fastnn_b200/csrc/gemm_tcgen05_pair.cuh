@@ -28,10 +28,11 @@ __device__ __forceinline__ Unit decode_unit_pair(const GemmParams& p, int u) {
   return decode_unit(p, u);
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
-gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const __grid_constant__ CUtensorMap tmC,
-                 const __grid_constant__ GemmParams p) {
+// kGather: every finished tile is also stored through p.n_peers extra tensor maps (see PeerMaps).
+template <bool kGather>
+__device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
+                                                    const CUtensorMap& tmC, const GemmParams& p,
+                                                    const CUtensorMap* peers) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -74,6 +75,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     ptx::prefetch_tensormap(&tmA);
     ptx::prefetch_tensormap(&tmB);
     if (p.store_mode == 0) ptx::prefetch_tensormap(&tmC);
+    if constexpr (kGather) {
+      for (int i = 0; i < p.n_peers; ++i) ptx::prefetch_tensormap(peers + i);
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc_2cta(tmem_slot, kTmemCols);
@@ -206,14 +210,15 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const Unit w = decode_unit_pair(p, u);
       const int m0 = w.mt * kPairBlockM + static_cast<int>(rank) * kBlockM + q * 32;
       const int n0 = w.nt * p.block_n;
-      ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout, p.epi_sleep_ns);
+      ok = wait_barrier(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                               static_cast<uint32_t>(acc * kMaxBlockN);
       const int cz = raw ? (w.b * p.split_k + w.s) : w.b;
-      epilogue_drain_tile(p, &tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, w.b, raw, lane);
+      epilogue_drain_tile(p, &tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, w.b, raw, lane, 0, 1, 2,
+                          kGather ? peers : nullptr, kGather ? p.n_peers : 0);
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(acc), 0));
@@ -236,6 +241,19 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc_2cta(tmem_base, kTmemCols);
   }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmC, const __grid_constant__ GemmParams p) {
+  gemm_tf32_pair_body<false>(tmA, tmB, tmC, p, nullptr);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+gemm_tf32_pair_gather_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ PeerMaps peers,
+                             const __grid_constant__ GemmParams p) {
+  gemm_tf32_pair_body<true>(tmA, tmB, tmC, p, peers.m);
 }
 
 // Dynamic shared memory per CTA of the pair kernel.

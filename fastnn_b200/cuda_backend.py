@@ -255,8 +255,7 @@ def conv2d_forward(x, weight, bias=None, stride=(1, 1), padding=(0, 0), act=ACT_
 
 def conv2d_backward(x, weight, grad_output, stride=(1, 1), padding=(0, 0), stream=0):
     """Conv2dBackward (src/autograd/backward_ops.rs:753-770): returns (grad_input, grad_weight) for
-    x [N,Cin,H,W], weight [Cout,Cin,KH,KW], grad_output [N,Cout,OH,OW].  grad_input needs stride 1
-    (CudaError otherwise); grad_weight takes any stride."""
+    x [N,Cin,H,W], weight [Cout,Cin,KH,KW], grad_output [N,Cout,OH,OW]; any stride and padding."""
     _check(x, "x"); _check(weight, "weight"); _check(grad_output, "grad_output")
     _ensure_ctx(x)
     n, ci, h, w = (int(v) for v in x.shape)
@@ -341,17 +340,62 @@ def gemm_ex(layout, a_ptr, b_ptr, c_ptr, m, n, k, batch, lda, ldb, ldc, sa, sb, 
         raise CudaError("fastnn_b200_gemm_ex failed")
 
 
+def _same_device(*tensors) -> None:
+    """All tensors on the current CUDA device; does not initialise the library's context."""
+    cur = torch.cuda.current_device()
+    for t in tensors:
+        if t is not None and t.device.index != cur:
+            raise ValueError("tensor is not on the current CUDA device")
+
+
 def gemm_splitk_static(layout, a, b, m, n, k, split_k, out=None, stream=0):
     """C = op(A).op(B) through the entry point that allocates nothing: split-K partial sums go
     to the 16 MiB array built into the library.  Returns the output tensor; raises CudaError
-    with ``too_large=True`` in its args when m*n*split_k floats exceed that array."""
+    with ``too_large=True`` in its args when m*n*split_k floats exceed that array.  Needs no
+    ``cuda_init`` (and does not call it); pass ``out`` to keep torch's allocator out of it too."""
     _check(a, "a"); _check(b, "b")
+    if layout not in (NN, NT, TN):
+        raise ValueError("bad layout")
+    want_a = (k, m) if layout == TN else (m, k)
+    want_b = (n, k) if layout == NT else (k, n)
+    if tuple(a.shape) != want_a or tuple(b.shape) != want_b:
+        raise ValueError(f"operand shapes {tuple(a.shape)}, {tuple(b.shape)} do not match "
+                         f"layout {layout} with m={m}, n={n}, k={k}")
     c = _out((m, n), a, out)
+    _same_device(a, b, c)
     rc = lib().fastnn_b200_gemm_splitk_static(layout, _ptr(a), _ptr(b), _ptr(c), m, n, k, split_k,
                                               ctypes.c_void_p(stream))
     if rc != 0:
         raise CudaError("fastnn_b200_gemm_splitk_static failed", rc == -2)
     return c
+
+
+def gemm_gather_ex(layout, a_ptr, b_ptr, c_ptr, m, n, k, batch, lda, ldb, ldc, sa, sb, sc, peer_ptrs,
+                   alpha=1.0, bias_ptr=0, act=ACT_NONE, stream=0) -> None:
+    """fastnn_b200_gemm_ex with the all-gather of C fused into the epilogue: every finished tile is
+    also stored to ``peer_ptrs`` (the same rows of C in the other GPUs' buffers, peer-mapped)."""
+    arr = (ctypes.c_void_p * max(1, len(peer_ptrs)))(*[ctypes.c_void_p(int(p)) for p in peer_ptrs])
+    rc = lib().fastnn_b200_gemm_gather_ex(layout, ctypes.c_void_p(a_ptr), ctypes.c_void_p(b_ptr),
+                                          ctypes.c_void_p(c_ptr), m, n, k, batch, lda, ldb, ldc, sa, sb, sc,
+                                          alpha, ctypes.c_void_p(bias_ptr), act, arr, len(peer_ptrs),
+                                          ctypes.c_void_p(stream))
+    if rc != 0:
+        raise CudaError("fastnn_b200_gemm_gather_ex failed")
+
+
+def selftest_bounded_wait(budget_us: int = 1000) -> int:
+    """Runs the one-warp kernel whose bounded wait must run out; returns how long it waited (us).
+    Afterwards ``device_status()`` returns 0x1F0 once and then 0 again."""
+    waited = ctypes.c_uint()
+    if lib().fastnn_b200_selftest_bounded_wait(int(budget_us), ctypes.byref(waited)) != 0:
+        raise CudaError("bounded-wait self-test failed: the wait did not give up")
+    return waited.value
+
+
+def current_stream_ptr() -> int:
+    """torch's current stream as an integer for the ``stream`` arguments of this module.  The
+    entries without a stream argument use the legacy default stream, as FastNN's do."""
+    return int(torch.cuda.current_stream().cuda_stream)
 
 
 def attention_forward(q, k, v, scale=None, causal=False, out=None, stream=0):

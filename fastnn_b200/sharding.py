@@ -58,9 +58,95 @@ def _cuda_local(layout: int, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         c = torch.empty((m, n), dtype=torch.float32, device=a.device)
         cb._ensure_ctx(b)
         cb.gemm_ex(TN, a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, 1,
-                   a.stride(0), b.stride(0), n, 0, 0, 0)
+                   a.stride(0), b.stride(0), n, 0, 0, 0, stream=cb.current_stream_ptr())
         return c
     return [cb.matmul, cb.matmul_nt, cb.matmul_tn][layout](a, b)
+
+
+# ------------------------------------------------------------------------------------------
+# All of C on every rank, with the all-gather fused into the GEMM: rank r computes its rows (or
+# batches) of C and its GEMM's epilogue stores every finished tile into the same rows of EVERY
+# rank's full-size C (TMA stores to peer-mapped symmetric memory over NVLink), while the tensor
+# core works on the next tile.  No collective follows; the ranks meet at one barrier before any
+# of them reads rows it did not compute.  Nothing is ever loaded from a peer.
+# ------------------------------------------------------------------------------------------
+
+def gather_plan(layout: int, a_shape, a_row_stride: int, b_shape, total: int, world: int, rank: int):
+    """Arguments of the fused-gather GEMM of rank ``rank``, as plain integers (no device needed):
+    the GEMM's m, n, k, batch, leading dimensions and batch strides in elements, and ``offset``,
+    the element offset of this rank's part inside the full C (``total`` rows, or batches).
+    ``a_shape`` is the shape of this rank's shard of the left operand, ``a_row_stride`` its row
+    stride in elements (a TN shard is a column slice: the stride is the full row)."""
+    r0, r1 = row_partition(total, world, rank)
+    if len(a_shape) == 3:
+        batch = int(a_shape[0])
+        if batch != r1 - r0:
+            raise ValueError("a_shard does not hold this rank's batches")
+        m = int(a_shape[2] if layout == TN else a_shape[1])
+        k = int(a_shape[1] if layout == TN else a_shape[2])
+        n = int(b_shape[1] if layout == NT else b_shape[2])
+        if int(b_shape[0]) != batch or int(b_shape[2] if layout == NT else b_shape[1]) != k:
+            raise ValueError("operand shapes do not match")
+        return dict(m=m, n=n, k=k, batch=batch, lda=int(a_shape[2]), ldb=int(b_shape[2]), ldc=n,
+                    sa=int(a_shape[1] * a_shape[2]), sb=int(b_shape[1] * b_shape[2]), sc=m * n,
+                    offset=r0 * m * n)
+    m = int(a_shape[1] if layout == TN else a_shape[0])
+    k = int(a_shape[0] if layout == TN else a_shape[1])
+    if m != r1 - r0:
+        raise ValueError("a_shard does not hold this rank's rows")
+    n = int(b_shape[0] if layout == NT else b_shape[1])
+    if int(b_shape[1] if layout == NT else b_shape[0]) != k:
+        raise ValueError("operand shapes do not match")
+    return dict(m=m, n=n, k=k, batch=1, lda=int(a_row_stride), ldb=int(b_shape[1]), ldc=n,
+                sa=0, sb=0, sc=0, offset=r0 * n)
+
+
+class GatheredOutput:
+    """The full C of a sharded product in symmetric memory: the same ``shape`` on every rank, each
+    rank's buffer mapped into every other rank's address space."""
+
+    def __init__(self, shape, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world - 1 > 7:
+            raise ValueError("the fused gather stores to at most seven peers")
+        self.tensor = symm_mem.empty(tuple(shape), dtype=torch.float32,
+                                     device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+
+    def barrier(self, channel: int = 0) -> None:
+        """Every rank's GEMMs enqueued before this point are complete on every rank afterwards
+        (runs on torch's current stream; no host synchronisation)."""
+        self.handle.barrier(channel=channel)
+
+
+def sharded_matmul_gathered(layout: int, a_shard: torch.Tensor, b: torch.Tensor, out: GatheredOutput,
+                            bias: Optional[torch.Tensor] = None, act: int = cb.ACT_NONE,
+                            stream: Optional[int] = None) -> torch.Tensor:
+    """This rank's rows (or batches) of C = act(op(A).op(B) + bias), written by the GEMM itself
+    into ``out`` on EVERY rank.  Returns this rank's full-size buffer; rows computed by other ranks
+    are valid after ``out.barrier()``."""
+    cb._ensure_ctx(b)
+    total = int(out.tensor.shape[0])
+    if a_shard.dim() == 3:
+        a_shard = a_shard.contiguous()
+    elif a_shard.stride(1) != 1:
+        raise ValueError("a_shard must have contiguous rows")
+    plan = gather_plan(layout, tuple(a_shard.shape), a_shard.stride(-2), tuple(b.shape), total,
+                       out.world, out.rank)
+    if plan["m"] == 0 or plan["batch"] == 0:
+        return out.tensor
+    off = 4 * plan["offset"]
+    peers = [out.base_ptrs[r] + off for r in range(out.world) if r != out.rank]
+    cb.gemm_gather_ex(layout, a_shard.data_ptr(), b.data_ptr(), out.base_ptrs[out.rank] + off,
+                      plan["m"], plan["n"], plan["k"], plan["batch"], plan["lda"], plan["ldb"], plan["ldc"],
+                      plan["sa"], plan["sb"], plan["sc"], peers,
+                      bias_ptr=bias.data_ptr() if bias is not None else 0, act=act,
+                      stream=cb.current_stream_ptr() if stream is None else stream)
+    return out.tensor
 
 
 def sharded_matmul(layout: int, a_shard: torch.Tensor, b: torch.Tensor,
@@ -153,6 +239,8 @@ def k_sharded_matmul_tn(x_local: torch.Tensor, dy_local: torch.Tensor, group=Non
         raise ValueError("workspace was built for another problem")
     cb._check(x_local, "x_local"); cb._check(dy_local, "dy_local")
     cb._ensure_ctx(x_local)
+    # everything on torch's current stream: the symmetric-memory barriers run there too
+    stream = cb.current_stream_ptr()
     ws.handle.barrier(channel=0)                             # previous use of the slots is over
     for step in range(world):                                # start at the neighbour: spread traffic
         owner = (rank + 1 + step) % world
@@ -160,15 +248,15 @@ def k_sharded_matmul_tn(x_local: torch.Tensor, dy_local: torch.Tensor, group=Non
         if o1 == o0:
             continue
         cb.gemm_ex(TN, x_local.data_ptr() + 4 * o0, dy_local.data_ptr(), ws.slot_ptr(owner, rank),
-                   o1 - o0, n, k_r, 1, m, n, n, 0, 0, 0)
+                   o1 - o0, n, k_r, 1, m, n, n, 0, 0, 0, stream=stream)
     ws.handle.barrier(channel=1)                             # every partial has landed
     out = torch.empty((r1 - r0, n), dtype=torch.float32, device=x_local.device)
     if r1 > r0:
         # slots are [world][rows_max][n]; a partial occupies the first r1-r0 rows of its slot, so
         # the reduce walks slots with a stride of rows_max*n by treating them as rows_max-row blocks
         if r1 - r0 == ws.rows_max:
-            cb.reduce_partials(ws.slots.data_ptr(), out.data_ptr(), r1 - r0, n, world)
+            cb.reduce_partials(ws.slots.data_ptr(), out.data_ptr(), r1 - r0, n, world, stream=stream)
         else:
             packed = ws.slots[:, : r1 - r0].contiguous()
-            cb.reduce_partials(packed.data_ptr(), out.data_ptr(), r1 - r0, n, world)
+            cb.reduce_partials(packed.data_ptr(), out.data_ptr(), r1 - r0, n, world, stream=stream)
     return out

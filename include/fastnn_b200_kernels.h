@@ -166,8 +166,10 @@ FASTNN_B200_API int fastnn_b200_conv2d_forward(const float* input, const float* 
  * (likewise iw); both outputs are overwritten, not accumulated into.  The fastnn_cuda_ names keep
  * FastNN's argument lists (cuda/kernels.cu:949-987 and 989-1026: col2im / im2col + cuBLAS per
  * image); the _b200_ forms add a stream.
- * backward_data runs the implicit-GEMM forward kernel on grad_output with the kernel reversed and
- * channels swapped; it covers stride 1 with pad <= kernel - 1 and returns -1 otherwise.
+ * backward_data: for stride 1 with pad <= kernel - 1, the implicit-GEMM forward kernel run on
+ * grad_output with the kernel reversed and channels swapped; for every other stride and padding a
+ * gather-form kernel in which each grad_input element adds its (co, ki, kj) terms (the sums
+ * FastNN's GEMM + col2im forms, cuda/kernels.cu:862-893) -- no column matrix, no atomics.
  * backward_weight is explicit in this version: one im2col launch for all images (tap-major, as
  * FastNN's kernel_im2col lays it out), one batched NT GEMM into per-image partials, one
  * fixed-order sum (deterministic); any stride. */
@@ -210,6 +212,28 @@ FASTNN_B200_API int fastnn_b200_attention_forward(const float* q, const float* k
                                                   int head_dim, float scale, int causal,
                                                   void* stream);
 
+/* The general GEMM with an all-gather of C fused into its epilogue, for the multi-GPU form of the
+ * path in which the rows of C (or the batches) are split over GPUs and a caller wants all of C on
+ * every device.  No counterpart in FastNN (it has no multi-GPU path); replaces "GEMM, then an
+ * all-gather of the C shards" by one launch per rank:
+ *   C[b] = act( alpha * op(A[b]) . op(B[b]) + bias )  as fastnn_b200_gemm_ex with beta = 0,
+ * and every finished 32 x 32 tile is stored not only to c but also to peer_c[0..n_peers-1]: the
+ * address of the SAME rows of C inside each other GPU's full-size buffer, as mapped into this
+ * process (CUDA peer access / symmetric memory).  n_peers <= 7.  All destinations share ldc and
+ * stride_c.  The stores are plain TMA stores over NVLink issued by the epilogue warps while the
+ * tensor core works on the next tile; nothing is ever LOADED from a peer.  c and every peer_c[i]
+ * must be 16-byte aligned and ldc a multiple of 4 (-1 otherwise: peer tiles leave by TMA only).
+ * Completion: when the kernel has finished on this GPU its tiles are in every destination; the
+ * ranks still need one barrier among themselves before any of them reads rows it did not
+ * compute.  n_peers = 0 is fastnn_b200_gemm_ex. */
+FASTNN_B200_API int fastnn_b200_gemm_gather_ex(int layout, const float* a, const float* b, float* c,
+                                               int m, int n, int k, int batch,
+                                               long long lda, long long ldb, long long ldc,
+                                               long long stride_a, long long stride_b,
+                                               long long stride_c, float alpha, const float* bias,
+                                               int act, float* const* peer_c, int n_peers,
+                                               void* stream);
+
 /* c[m,n] = act( alpha * (partials[0] + partials[1] + ... + partials[count-1]) + beta * c + bias ),
  * partials stored back to back as count dense [m,n] matrices, added in ascending order.
  * The reduce step of split-K, exposed for the multi-GPU weight-gradient path where the K
@@ -244,6 +268,8 @@ FASTNN_B200_API int fastnn_b200_reduce_partials(const float* partials, float* c,
  *   - It does not need fastnn_cuda_init.  The first call on each device looks up the device
  *     address of the array and of the tensor-map encoder; make that first call before any
  *     stream capture begins.
+ *   - A bounded wait that runs out inside its kernels is reported through
+ *     fastnn_b200_device_status, like every other kernel's.
  *   - All calls on one device share the array and it keeps the previous call's contents.
  *     Every element that is read was written earlier in the same call, so nothing has to be
  *     cleared, but two calls that overlap on the GPU (different streams without an ordering
@@ -261,7 +287,8 @@ FASTNN_B200_API int fastnn_b200_gemm_splitk_static(int layout, const float* a, c
 FASTNN_B200_API int fastnn_b200_memcpy_h2d_async(float* dst, const float* src, size_t size, void* stream);
 FASTNN_B200_API int fastnn_b200_memcpy_d2h_async(float* dst, const float* src, size_t size, void* stream);
 
-/* Kernel selection for tests and sweeps.  policy: 0 = automatic (tcgen05 path whenever the
+/* Kernel selection for tests and sweeps; applies to calls made by the CALLING THREAD only (other
+ * threads keep the automatic choice).  policy: 0 = automatic (tcgen05 path whenever the
  * operands meet TMA's 16-byte alignment rules, SIMT path otherwise), 1 = SIMT path only,
  * 2 = tcgen05 path only (calls that cannot use it fail with -1), 3 = tcgen05 with single-CTA
  * 128-row tiles only, 4 = tcgen05 with CTA-pair 256-row tiles only, 5 = single-CTA tiles with the
@@ -274,7 +301,8 @@ FASTNN_B200_API int fastnn_b200_set_policy(int policy, int block_n, int split_k)
 
 /* Which path the most recent call on this thread took: 1 = SIMT, 2 = tcgen05 1-CTA, 3 = tcgen05
  * 2-CTA, 4 = fused attention, 5 = conv2d, 6 = tcgen05 1-CTA with the K split inside clusters
- * (one launch, no workspace); 0 before any call.  Also reports its tile and split choice. */
+ * (one launch, no workspace), 7 = a direct (FP32 FMA) convolution kernel; 0 before any call.
+ * Also reports its tile and split choice. */
 FASTNN_B200_API int fastnn_b200_last_path(int* block_n, int* split_k, int* num_ctas);
 
 /* The host planner's choice for C[m,n] = op(A).op(B) (x batch), without launching: tile width,
@@ -285,9 +313,20 @@ FASTNN_B200_API int fastnn_b200_last_path(int* block_n, int* split_k, int* num_c
 FASTNN_B200_API int fastnn_b200_plan_query(int layout, int m, int n, int k, int batch, int* block_n,
                                            int* split_k, int* cta_pair, int* cluster_k);
 
-/* Reads and clears the device status word (synchronises the device).  0 = no kernel
- * reported a problem; otherwise the code of the first bounded wait that ran out. */
+/* Reads and clears the status words of the current device (synchronises the device).  0 = no
+ * kernel reported a problem; otherwise the code of the first bounded wait that ran out.  Covers
+ * both the kernels launched after fastnn_cuda_init and those of fastnn_b200_gemm_splitk_static
+ * (which keeps a word of its own inside the library image); works whether or not
+ * fastnn_cuda_init has been called, and allocates nothing. */
 FASTNN_B200_API int fastnn_b200_device_status(unsigned int* status);
+
+/* Exercises the bounded wait every kernel of this library uses on its mbarriers: one warp waits,
+ * with a budget of budget_us microseconds (1 .. 100000, counted in SM clock ticks at the maximum
+ * clock), on a barrier nothing arrives on.  Nothing else is in flight, so the launch cannot fault
+ * or hang.  Returns 0 when the wait gave up as designed; the device status word then holds code
+ * 0x1F0 until fastnn_b200_device_status reads and clears it.  waited_us (may be NULL) receives how
+ * long the wait lasted.  Needs fastnn_cuda_init.  No counterpart in FastNN. */
+FASTNN_B200_API int fastnn_b200_selftest_bounded_wait(unsigned int budget_us, unsigned int* waited_us);
 
 /* Number of kernels this library has launched since load (all threads). */
 FASTNN_B200_API unsigned long long fastnn_b200_launch_count(void);

@@ -68,10 +68,13 @@ def test_grad_weight_with_stride_and_through_the_reference_symbols(gpu):
                                                   2, 2, 1, 1) == 0
     torch.cuda.synchronize()
     _check(gw.cpu().numpy(), want_gw, 3 * oh * ow, go, x, "strided grad_weight")
-    # grad_input: stride 2 is not covered; stride 1 through FastNN's own symbol is
-    gi = torch.empty_like(xd)
+    # grad_input with stride 2 through FastNN's own symbol (the gather-form kernel)
+    want_gi2, _ = oracle.conv2d_backward(x, wt, go, (2, 2), (1, 1))
+    gi = torch.full(x.shape, float("nan"), device="cuda")
     assert lib.fastnn_cuda_conv2d_backward_data(vp(gd), vp(wd), vp(gi), 3, 6, 10, 15, 17, oh, ow, 3, 3,
-                                                2, 2, 1, 1) == -1
+                                                2, 2, 1, 1) == 0
+    torch.cuda.synchronize()
+    _check(gi.cpu().numpy(), want_gi2, 10 * 9, go, wt, "strided grad_input via the reference symbol")
     x1, w1, g1 = _case(2, 6, 10, 12, 12, 3, 3, (1, 1), (1, 1), 78)
     want_gi, _ = oracle.conv2d_backward(x1, w1, g1, (1, 1), (1, 1))
     g1d, w1d = torch.from_numpy(g1).cuda(), torch.from_numpy(w1).cuda()
@@ -95,5 +98,47 @@ def test_conv2d_gradients_are_deterministic_and_check_their_arguments(gpu):
     # output size that does not follow from the other arguments
     assert lib.fastnn_b200_conv2d_backward_weight(p, p, p, 1, 8, 16, 12, 12, 11, 12, 3, 3, 1, 1, 1, 1, None) == -1
     assert lib.fastnn_b200_conv2d_backward_data(p, p, p, 1, 8, 16, 12, 12, 11, 12, 3, 3, 1, 1, 1, 1, None) == -1
-    # padding beyond kernel - 1 is outside what grad_input covers
-    assert lib.fastnn_b200_conv2d_backward_data(p, p, p, 1, 8, 16, 12, 12, 16, 16, 3, 3, 1, 1, 3, 3, None) == -1
+
+
+@pytest.mark.parametrize("cfg", [
+    # n, ci, co, h, w, kh, kw, stride, padding: what the stride-1 implicit-GEMM form does not cover
+    (2, 8, 16, 16, 16, 3, 3, (2, 2), (1, 1)),
+    (3, 5, 7, 19, 23, 7, 7, (2, 2), (3, 3)),        # 7 x 7, stride 2 (a network's first layer)
+    (2, 4, 6, 17, 15, 3, 5, (3, 2), (0, 2)),        # uneven strides, rows the kernel never reaches
+    (1, 3, 4, 10, 10, 2, 2, (1, 1), (3, 3)),        # stride 1 with padding beyond kernel - 1
+    (2, 6, 5, 12, 12, 1, 1, (2, 2), (0, 0)),        # strided pointwise: three quarters of grad_input are 0
+])
+def test_conv2d_gradients_for_any_stride_and_padding(gpu, cfg):
+    """FastNN's own entries accept every stride and padding (col2im, cuda/kernels.cu:862-893):
+    so do these, against the CPU loops."""
+    import torch
+    f = gpu
+    n, ci, co, h, w, kh, kw, stride, padding = cfg
+    x, wt, go = _case(n, ci, co, h, w, kh, kw, stride, padding, 1000 + sum(cfg[:7]))
+    want_gi, want_gw = oracle.conv2d_backward(x, wt, go, stride, padding)
+    gi, gw = f.conv2d_backward(torch.from_numpy(x).cuda(), torch.from_numpy(wt).cuda(),
+                               torch.from_numpy(go).cuda(), stride=stride, padding=padding)
+    torch.cuda.synchronize()
+    _check(gi.cpu().numpy(), want_gi, co * kh * kw, go, wt, f"grad_input {cfg}")
+    _check(gw.cpu().numpy(), want_gw, n * go.shape[2] * go.shape[3], go, x, f"grad_weight {cfg}")
+    # FP32 FMA throughout: far inside the TF32 bound
+    assert np.abs(gi.cpu().numpy() - want_gi).max() <= 1e-4 * co * kh * kw
+    assert f.device_status() == 0
+
+
+def test_conv2d_forward_with_more_taps_than_the_gather_encodes(gpu):
+    """An 8 x 8 kernel has 64 taps, one more than the implicit-GEMM gather's mask holds: served by
+    the direct kernel (path 7), forward and input gradient."""
+    import torch
+    f = gpu
+    x, wt, go = _case(2, 3, 5, 20, 20, 8, 8, (1, 1), (2, 2), 31)
+    b = np.arange(5, dtype=np.float32)
+    y = f.conv2d_forward(torch.from_numpy(x).cuda(), torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda(),
+                         padding=(2, 2), act=f.ACT_RELU)
+    assert f.last_path()["path"] == 7
+    want = np.maximum(oracle.conv2d(x, wt, b, (1, 1), (2, 2)), 0.0)
+    assert np.abs(y.cpu().numpy() - want).max() <= 1e-4 * 3 * 64
+    want_gi, _ = oracle.conv2d_backward(x, wt, go, (1, 1), (2, 2))
+    gi, _ = f.conv2d_backward(torch.from_numpy(x).cuda(), torch.from_numpy(wt).cuda(),
+                              torch.from_numpy(go).cuda(), padding=(2, 2))
+    assert np.abs(gi.cpu().numpy() - want_gi).max() <= 1e-4 * 5 * 64

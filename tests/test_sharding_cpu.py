@@ -104,3 +104,75 @@ def test_two_rank_sharded_matmul_and_gather_gloo():
         p.join(100)
         assert p.exitcode == 0
     assert results.get(timeout=5) == 1
+
+
+def test_gather_plan_places_every_shard_once():
+    """The fused-gather arguments of all ranks tile the full C without gaps or overlap, and a TN
+    shard (a column slice of the stored [k, m]) keeps the full row stride."""
+    for world in (1, 2, 3, 8):
+        for layout, (m, n, k) in ((NN, (8192, 512, 64)), (NT, (1001, 36, 20)), (TN, (250, 72, 64))):
+            covered = np.zeros(m * n, dtype=np.int32)
+            for rank in range(world):
+                r0, r1 = sharding.row_partition(m, world, rank)
+                a_shape = (k, r1 - r0) if layout == TN else (r1 - r0, k)
+                b_shape = (n, k) if layout == NT else (k, n)
+                plan = sharding.gather_plan(layout, a_shape, m if layout == TN else k, b_shape, m, world, rank)
+                assert (plan["m"], plan["n"], plan["k"], plan["batch"]) == (r1 - r0, n, k, 1)
+                assert plan["lda"] == (m if layout == TN else k) and plan["ldc"] == n
+                covered[plan["offset"]: plan["offset"] + plan["m"] * n] += 1
+            assert (covered == 1).all()
+    # batched: batches are partitioned, strides are dense
+    plan = sharding.gather_plan(NT, (3, 128, 32), 32, (3, 128, 32), 6, 2, 1)
+    assert plan == dict(m=128, n=128, k=32, batch=3, lda=32, ldb=32, ldc=128, sa=4096, sb=4096,
+                        sc=128 * 128, offset=3 * 128 * 128)
+    with pytest.raises(ValueError):
+        sharding.gather_plan(NN, (5, 4), 4, (4, 3), 8, 2, 0)          # 5 rows is not this rank's share
+    with pytest.raises(ValueError):
+        sharding.gather_plan(NN, (4, 4), 4, (5, 3), 8, 2, 0)          # inner dimensions differ
+
+
+def _gather_worker(rank, world, port, results):
+    """Two gloo ranks play the fused gather with host memory standing in for peer-mapped C: each
+    rank computes its shard with the oracle and 'stores' it at gather_plan's offset into every
+    rank's buffer (an all_gather of (offset, values) pairs); all buffers must equal the product."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(321)
+        ok = True
+        for layout, (m, n, k) in ((NN, (11, 6, 5)), (NT, (9, 4, 7)), (TN, (10, 5, 3))):
+            sa = (k, m) if layout == TN else (m, k)
+            sb = (n, k) if layout == NT else (k, n)
+            a = torch.from_numpy(rng.standard_normal(sa, dtype=np.float32))
+            b = torch.from_numpy(rng.standard_normal(sb, dtype=np.float32))
+            shard = sharding.shard_left_operand(layout, a, world, rank)
+            plan = sharding.gather_plan(layout, tuple(shard.shape), shard.stride(0), tuple(b.shape), m,
+                                        world, rank)
+            mine = _oracle_local(layout, shard, b).reshape(-1)
+            pieces = [None] * world
+            dist.all_gather_object(pieces, (plan["offset"], mine.numpy()))
+            full = np.full(m * n, np.nan, dtype=np.float32)
+            for off, vals in pieces:
+                full[off: off + vals.size] = vals
+            want = [oracle.matmul, oracle.matmul_nt, oracle.matmul_tn][layout](a.numpy(), b.numpy())
+            ok = ok and np.array_equal(full.reshape(m, n), want)
+        results.put((rank, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_fused_gather_layout():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    procs = [ctx.Process(target=_gather_worker, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(results.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert got == [(0, True), (1, True)]

@@ -22,6 +22,7 @@ def _worker(rank, world, port, queue):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")      # plain peer mappings only
     torch.cuda.set_device(rank)
     f.cuda_init(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -60,7 +61,32 @@ def _worker(rank, world, port, queue):
             full = sharding.all_gather_rows(mine, m).cpu().numpy()
             full_plain = sharding.all_gather_rows(plain, m).cpu().numpy()
             grads[(m, n, k)] = (full, full_plain, x, dy)
+        # all of C on every rank with the all-gather fused into the GEMM epilogue (peer stores
+        # into symmetric memory), twice per shape (the buffer is reused), incl. a batched product
+        gathered = {}
+        for layout, (m, n, k) in ((NN, (520, 264, 132)), (NT, (512, 256, 128)), (TN, (768, 136, 260)),
+                                  (TN, (251, 72, 64))):
+            sa = (k, m) if layout == TN else (m, k)
+            sb = (n, k) if layout == NT else (k, n)
+            a = rng.standard_normal(sa, dtype=np.float32)
+            b = rng.standard_normal(sb, dtype=np.float32)
+            da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+            shard = sharding.shard_left_operand(layout, da, world, rank)
+            full = sharding.GatheredOutput((m, n))
+            for _ in range(2):
+                full.tensor.fill_(float("nan"))
+                full.barrier()
+                sharding.sharded_matmul_gathered(layout, shard, db, full)
+                full.barrier()
+            gathered[(layout, m, n, k)] = (full.tensor.cpu().numpy(), a, b)
+        gb = sharding.GatheredOutput((6, 128, 128))
+        gb.tensor.fill_(float("nan"))
+        gb.barrier()
+        sharding.sharded_matmul_gathered(NT, torch.from_numpy(q[r0:r1]).cuda(), torch.from_numpy(kk[r0:r1]).cuda(), gb)
+        gb.barrier()
+        gathered_batched = gb.tensor.cpu().numpy()
         status = f.device_status()
+        queue.put((rank, gathered, gathered_batched))
         if rank == 0:
             queue.put((out, s_full, q, kk, status, grads))
         dist.barrier()
@@ -81,11 +107,21 @@ def test_two_gpu_sharded_matmul_nccl(built_library):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, queue)) for r in range(2)]
     for p in procs:
         p.start()
-    out, s_full, q, kk, status, grads = queue.get(timeout=240)
+    items = [queue.get(timeout=300) for _ in range(3)]
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
+    out, s_full, q, kk, status, grads = [it for it in items if len(it) == 6][0]
     assert status == 0
+    per_rank = sorted((it for it in items if len(it) == 3), key=lambda it: it[0])
+    assert [it[0] for it in per_rank] == [0, 1]
+    for rank, gathered, gathered_batched in per_rank:          # EVERY rank holds all of C
+        for (layout, m, n, k), (got, a, b) in gathered.items():
+            want = [oracle.matmul, oracle.matmul_nt, oracle.matmul_tn][layout](a, b)
+            check_tf32_parity(got, want, k, a, b, what=f"fused gather rank {rank} L{layout} {m}x{n}x{k}")
+        check_tf32_parity(gathered_batched, oracle.matmul_nt(q, kk), 32, q, kk,
+                          what=f"fused gather batched rank {rank}")
+    assert np.array_equal(per_rank[0][2], per_rank[1][2])
     for (layout, m, n, k), (got, a, b) in out.items():
         want = [oracle.matmul, oracle.matmul_nt, oracle.matmul_tn][layout](a, b)
         check_tf32_parity(got, want, k, a, b, what=f"2-GPU L{layout} {m}x{n}x{k}")

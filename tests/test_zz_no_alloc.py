@@ -78,3 +78,63 @@ def test_static_scratch_entry_refuses_what_does_not_fit(gpu):
     assert bool((c == 0.0).all())
     # misaligned row length
     assert lib.fastnn_b200_gemm_splitk_static(NN, p(a), p(b), p(c), 8, 6, 8, 1, None) == -1
+
+
+_FRESH_PROCESS = r"""
+import ctypes, sys
+import torch
+sys.path.insert(0, {root!r})
+from fastnn_b200 import _lib
+lib = _lib.lib()                      # loads the library; fastnn_cuda_init is never called here
+torch.cuda.set_device(0)
+vp = lambda t: ctypes.c_void_p(t.data_ptr())
+free = lambda: torch.cuda.mem_get_info()[0]
+status = ctypes.c_uint(99)
+
+# every buffer the calls use exists before the first measurement (torch's allocator is the
+# caller's business, not the library's)
+shapes = [(256, 256, 512, 2), (384, 512, 2048, 8), (1024, 1024, 1024, 4)]
+bufs = []
+for m, n, k, s in shapes:
+    a = torch.randn(m, k, device="cuda"); b = torch.randn(k, n, device="cuda")
+    bufs.append((a, b, torch.empty(m, n, device="cuda"), torch.matmul(a.double(), b.double())))
+torch.cuda.synchronize()
+
+# first call: the CUDA runtime loads the library's kernels and its 16 MiB array on first use
+m, n, k, s = shapes[0]; a, b, c, want = bufs[0]
+assert lib.fastnn_b200_gemm_splitk_static(0, vp(a), vp(b), vp(c), m, n, k, s, None) == 0
+torch.cuda.synchronize()
+assert lib.fastnn_b200_device_status(ctypes.byref(status)) == 0 and status.value == 0
+before = free()
+# later calls, with partial-sum footprints 4x and 32x the first one's: an entry that kept its
+# partial sums in an allocated workspace would have to grow it here
+for (m, n, k, s), (a, b, c, want) in zip(shapes, bufs):
+    for _ in range(2):
+        assert lib.fastnn_b200_gemm_splitk_static(0, vp(a), vp(b), vp(c), m, n, k, s, None) == 0
+    torch.cuda.synchronize()
+    assert free() == before, "device free memory changed across a call"
+status.value = 99
+assert lib.fastnn_b200_device_status(ctypes.byref(status)) == 0 and status.value == 0
+assert free() == before
+# results, checked only now: torch's own temporaries may grow its pool
+for a, b, c, want in bufs:
+    err = (c.double() - want).norm() / want.norm()
+    assert float(err) < 5e-3, float(err)
+# the entries that need fastnn_cuda_init still refuse to run without it
+assert lib.fastnn_cuda_matmul_nt(vp(bufs[0][0]), vp(bufs[0][0]), vp(bufs[0][2]), 256, 256, 512) == -1
+print("ok")
+"""
+
+
+def test_static_entry_in_a_fresh_process_without_init_allocates_nothing(built_library):
+    """The two properties the entry exists for, in a process that never calls fastnn_cuda_init:
+    it works, and device free memory (cudaMemGetInfo) is identical before and after its calls.
+    Its status word is readable through fastnn_b200_device_status without initialisation too."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.run([sys.executable, "-c", _FRESH_PROCESS.format(root=root)], capture_output=True,
+                          text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout + proc.stderr
+    assert proc.stdout.strip().endswith("ok")
