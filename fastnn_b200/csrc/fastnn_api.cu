@@ -794,6 +794,35 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   return 0;
 }
 
+int gemm_dispatch(const GemmArgs& g);
+
+// The gather for operands or outputs TMA cannot address (row lengths that are not multiples of
+// four floats, unaligned bases): the ordinary GEMM into this GPU's C, then one strided copy per
+// destination on the same stream.  Not overlapped with the product -- a correctness path for odd
+// shapes; aligned shapes take the kernels whose epilogue stores to the peers tile by tile.
+int gather_by_copies(const GemmArgs& g) {
+  GemmArgs local = g;
+  local.peer_c = nullptr;
+  local.n_peers = 0;
+  const int rc = gemm_dispatch(local);
+  if (rc != 0) return rc;
+  const bool dense_batches = g.batch == 1 || g.sc == 1ll * g.m * g.ldc;
+  for (int i = 0; i < g.n_peers; ++i) {
+    if (g.peer_c[i] == nullptr) return -1;
+    if (dense_batches) {
+      FNN_CUDA_OK(cudaMemcpy2DAsync(g.peer_c[i], sizeof(float) * g.ldc, g.c, sizeof(float) * g.ldc,
+                                    sizeof(float) * g.n, static_cast<size_t>(g.m) * g.batch,
+                                    cudaMemcpyDeviceToDevice, g.stream));
+    } else {
+      for (int b = 0; b < g.batch; ++b)
+        FNN_CUDA_OK(cudaMemcpy2DAsync(g.peer_c[i] + b * g.sc, sizeof(float) * g.ldc, g.c + b * g.sc,
+                                      sizeof(float) * g.ldc, sizeof(float) * g.n, g.m,
+                                      cudaMemcpyDeviceToDevice, g.stream));
+    }
+  }
+  return 0;
+}
+
 int gemm_dispatch(const GemmArgs& g) {
   if (g.layout < 0 || g.layout > 2) return -1;
   if (g.m < 0 || g.n < 0 || g.k < 0 || g.batch < 0) return -1;
@@ -810,7 +839,13 @@ int gemm_dispatch(const GemmArgs& g) {
   if (st == nullptr) return -1;                                   // fastnn_cuda_init not called
   const Policy pol = t_policy;
   const bool can_tma = tma_operands_ok(g);
-  if ((pol.policy >= 2 || g.n_peers > 0) && !can_tma) return -1;
+  if (g.n_peers > 0) {
+    bool stores_ok = can_tma && pol.policy != 1 && g.beta == 0.0f && aligned16(g.c) && (g.ldc & 3) == 0 &&
+                     (g.batch == 1 || (g.sc & 3) == 0) && g.ldc < (1ll << 38) && g.sc < (1ll << 38);
+    for (int i = 0; i < g.n_peers && stores_ok; ++i) stores_ok = g.peer_c[i] != nullptr && aligned16(g.peer_c[i]);
+    if (!stores_ok) return gather_by_copies(g);
+  }
+  if (pol.policy >= 2 && !can_tma) return -1;
   if (pol.policy == 1 || !can_tma) return launch_simt(g);
   return launch_tcgen05(st, g, pol);
 }

@@ -140,7 +140,8 @@ def sharded_matmul_gathered(layout: int, a_shard: torch.Tensor, b: torch.Tensor,
     if plan["m"] == 0 or plan["batch"] == 0:
         return out.tensor
     off = 4 * plan["offset"]
-    peers = [out.base_ptrs[r] + off for r in range(out.world) if r != out.rank]
+    # destinations start at the next rank, so that the ranks do not all write one GPU at a time
+    peers = [out.base_ptrs[(out.rank + 1 + i) % out.world] + off for i in range(out.world - 1)]
     cb.gemm_gather_ex(layout, a_shard.data_ptr(), b.data_ptr(), out.base_ptrs[out.rank] + off,
                       plan["m"], plan["n"], plan["k"], plan["batch"], plan["lda"], plan["ldb"], plan["ldc"],
                       plan["sa"], plan["sb"], plan["sc"], peers,

@@ -221,8 +221,10 @@ FASTNN_B200_API int fastnn_b200_attention_forward(const float* q, const float* k
  * address of the SAME rows of C inside each other GPU's full-size buffer, as mapped into this
  * process (CUDA peer access / symmetric memory).  n_peers <= 7.  All destinations share ldc and
  * stride_c.  The stores are plain TMA stores over NVLink issued by the epilogue warps while the
- * tensor core works on the next tile; nothing is ever LOADED from a peer.  c and every peer_c[i]
- * must be 16-byte aligned and ldc a multiple of 4 (-1 otherwise: peer tiles leave by TMA only).
+ * tensor core works on the next tile; nothing is ever LOADED from a peer.  That form needs TMA-
+ * addressable operands, c and every peer_c[i] 16-byte aligned and ldc a multiple of 4; any other
+ * call is served by the ordinary GEMM into c followed by one strided device-to-device copy per
+ * destination on the same stream (correct, not overlapped).
  * Completion: when the kernel has finished on this GPU its tiles are in every destination; the
  * ranks still need one barrier among themselves before any of them reads rows it did not
  * compute.  n_peers = 0 is fastnn_b200_gemm_ex. */

@@ -44,8 +44,10 @@ def build_oracle(force: bool = False) -> str:
 
 
 def build_reference(reference_root: str | None = None, force: bool = False) -> str | None:
-    """Compile the reference's own GPU library when its checkout is available."""
-    root = reference_root or os.environ.get("FASTNN_REFERENCE_ROOT", "/root/reference")
+    """Compile the reference's own GPU library when its checkout is available: the directory
+    given, else $FASTNN_REFERENCE_ROOT, else a `reference` directory beside this repository."""
+    root = reference_root or os.environ.get("FASTNN_REFERENCE_ROOT") or \
+        os.path.join(os.path.dirname(HERE), os.pardir, "reference")
     src = os.path.join(root, "cuda", "kernels.cu")
     if not os.path.exists(src):
         return REF_SO if os.path.exists(REF_SO) else None

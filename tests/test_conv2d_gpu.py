@@ -88,8 +88,8 @@ def test_conv2d_is_deterministic_and_rejects_bad_arguments(gpu):
     assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 4, 4, 8, 8, 3, 3, 0, 1, 0, 0, 0, None) == -1   # stride
     assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 4, 4, 8, 8, 3, 3, 1, 1, 0, 0, 2, None) == -1   # act
     assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 0, 4, 4, 8, 8, 3, 3, 1, 1, 0, 0, 0, None) == 0    # empty batch
-    assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 4, 4, 16, 16, 8, 8, 1, 1, 0, 0, 0, None) == -1  # 64 taps
-    assert lib.fastnn_b200_conv2d_forward(p, p, null, p, 1, 2048, 4, 128, 128, 3, 3, 1, 1, 0, 0, 0, None) == -1  # image >= 2^25
+    # (64 taps or more and images of 2^25 elements or more are served by the direct kernel:
+    # tests/test_conv2d_backward_gpu.py::test_conv2d_forward_with_more_taps_than_the_gather_encodes)
 
 
 def test_conv2d_with_a_seven_by_seven_kernel_and_stride_two(gpu):

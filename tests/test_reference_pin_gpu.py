@@ -111,3 +111,135 @@ def test_this_library_agrees_with_reference_gpu(gpu, ref, op):
     e_ours = np.linalg.norm(ours - want) / np.linalg.norm(want)
     e_theirs = np.linalg.norm(theirs - want) / np.linalg.norm(want)
     assert e_ours <= 5e-3 and e_theirs <= 5e-3, (e_ours, e_theirs)
+
+
+# ----------------------------------------------------------------------------------------
+# The restatements beside the matmul family -- Conv2d forward and both gradients, the ReLU / GELU
+# derivatives, the row softmax -- pinned the same way: FastNN's own CUDA entries for them
+# (cuda/kernels.cu:896-1026, 244-282, 289-337, 407) run here on identical inputs, the oracle takes
+# the CPU role of tests/cuda_parity.rs with its element rule (rtol 2e-2 / atol 2e-3 where a TF32
+# GEMM is involved; 1e-5 for the elementwise kernels, which are FP32 on both sides).
+# ----------------------------------------------------------------------------------------
+
+def _dev(x):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).cuda()
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+CONV_CASES = [
+    # n, ci, co, h, w, kh, kw, stride, padding
+    (2, 3, 8, 12, 12, 3, 3, (1, 1), (1, 1)),
+    (3, 4, 6, 15, 17, 3, 3, (2, 2), (1, 1)),         # stride 2
+    (2, 5, 7, 19, 23, 7, 7, (2, 2), (3, 3)),         # 7 x 7, stride 2
+    (1, 6, 4, 9, 11, 1, 1, (1, 1), (0, 0)),          # pointwise
+    (2, 2, 3, 10, 8, 5, 3, (1, 2), (2, 0)),          # rectangular kernel, uneven stride and padding
+]
+
+
+@pytest.mark.parametrize("cfg", CONV_CASES)
+def test_conv_oracle_agrees_with_reference_gpu(ref, cfg):
+    import torch
+    n, ci, co, h, w, kh, kw, (sh, sw), (ph, pw) = cfg
+    rng = np.random.default_rng(sum(cfg[:7]))
+    x = rng.uniform(-1, 1, (n, ci, h, w)).astype(np.float32)
+    wt = rng.uniform(-1, 1, (co, ci, kh, kw)).astype(np.float32)
+    bias = rng.uniform(-1, 1, co).astype(np.float32)
+    oh, ow = (h + 2 * ph - kh) // sh + 1, (w + 2 * pw - kw) // sw + 1
+    go = rng.uniform(-1, 1, (n, co, oh, ow)).astype(np.float32)
+    dx, dw, db, dgo = _dev(x), _dev(wt), _dev(bias), _dev(go)
+    dims = [_i(v) for v in (n, ci, co, h, w)]
+    tail = [_i(v) for v in (kh, kw, sh, sw, ph, pw)]
+    out = torch.full((n, co, oh, ow), float("nan"), device="cuda")
+    assert ref.fastnn_cuda_conv2d_forward(_p(dx), _p(dw), _p(db), _p(out), *dims, *tail) == 0
+    gi = torch.full(x.shape, float("nan"), device="cuda")
+    gw = torch.full(wt.shape, float("nan"), device="cuda")
+    assert ref.fastnn_cuda_conv2d_backward_data(_p(dgo), _p(dw), _p(gi), *dims, _i(oh), _i(ow), *tail) == 0
+    assert ref.fastnn_cuda_conv2d_backward_weight(_p(dx), _p(dgo), _p(gw), *dims, _i(oh), _i(ow), *tail) == 0
+    torch.cuda.synchronize()
+    want = oracle.conv2d(x, wt, bias, (sh, sw), (ph, pw))
+    want_gi, want_gw = oracle.conv2d_backward(x, wt, go, (sh, sw), (ph, pw))
+    reference_assert_close(want, out.cpu().numpy(), what=f"conv forward {cfg}")
+    reference_assert_close(want_gi, gi.cpu().numpy(), what=f"conv grad_input {cfg}")
+    reference_assert_close(want_gw, gw.cpu().numpy(), what=f"conv grad_weight {cfg}")
+
+
+@pytest.mark.parametrize("cfg", CONV_CASES)
+def test_this_library_conv_agrees_with_reference_gpu(gpu, ref, cfg):
+    """The drop-in symbols against the entries they replace, same arguments."""
+    import torch
+    f = gpu
+    n, ci, co, h, w, kh, kw, (sh, sw), (ph, pw) = cfg
+    rng = np.random.default_rng(100 + sum(cfg[:7]))
+    x = rng.standard_normal((n, ci, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((co, ci, kh, kw)) * 0.2).astype(np.float32)
+    oh, ow = (h + 2 * ph - kh) // sh + 1, (w + 2 * pw - kw) // sw + 1
+    go = rng.standard_normal((n, co, oh, ow)).astype(np.float32)
+    dx, dw, dgo = _dev(x), _dev(wt), _dev(go)
+    dims = (n, ci, co, h, w)
+    tail = (kh, kw, sh, sw, ph, pw)
+    outs = {}
+    for name, lib in (("theirs", ref), ("ours", f.lib())):
+        y = torch.full((n, co, oh, ow), float("nan"), device="cuda")
+        gi = torch.full(x.shape, float("nan"), device="cuda")
+        gw = torch.full(wt.shape, float("nan"), device="cuda")
+        i = _i if name == "theirs" else int
+        assert lib.fastnn_cuda_conv2d_forward(_p(dx), _p(dw), ctypes.c_void_p(0), _p(y), *map(i, dims), *map(i, tail)) == 0
+        assert lib.fastnn_cuda_conv2d_backward_data(_p(dgo), _p(dw), _p(gi), *map(i, dims), i(oh), i(ow), *map(i, tail)) == 0
+        assert lib.fastnn_cuda_conv2d_backward_weight(_p(dx), _p(dgo), _p(gw), *map(i, dims), i(oh), i(ow), *map(i, tail)) == 0
+        torch.cuda.synchronize()
+        outs[name] = [t.cpu().numpy() for t in (y, gi, gw)]
+    for what, a, b in zip(("forward", "grad_input", "grad_weight"), outs["theirs"], outs["ours"]):
+        reference_assert_close(a, b, what=f"{what} {cfg}: ours vs FastNN's entry")
+
+
+def test_activation_derivative_oracle_agrees_with_reference_gpu(ref):
+    """ReluBackward / GeluBackward (src/autograd/backward_ops.rs:136-160, 194-218) as restated in the
+    oracle's backward epilogue against fastnn_cuda_relu_backward / fastnn_cuda_gelu_backward."""
+    import torch
+    rng = np.random.default_rng(8)
+    rows, n = 37, 53
+    pre = (rng.standard_normal((rows, n)) * 2.5).astype(np.float32)
+    pre[0, :5] = [0.0, -0.0, 1e-30, -1e-30, 8.0]                       # the ReLU kink and the tails
+    go = rng.uniform(-1, 1, (rows, n)).astype(np.float32)
+    ident = np.eye(n, dtype=np.float32)                                # dy . I = dy exactly
+    for act, name in ((oracle.ACT_RELU, "fastnn_cuda_relu_backward"), (oracle.ACT_GELU, "fastnn_cuda_gelu_backward")):
+        want, colsum = oracle.linear_backward_input(go, ident, pre, act)
+        gi = torch.full((rows, n), float("nan"), device="cuda")
+        fn = getattr(ref, name)
+        fn.argtypes = [_vp, _vp, _vp, ctypes.c_size_t]
+        assert fn(_p(_dev(go)), _p(_dev(pre)), _p(gi), rows * n) == 0
+        torch.cuda.synchronize()
+        got = gi.cpu().numpy()
+        assert np.abs(got - want).max() <= 1e-5, name
+        assert np.abs(colsum - got.astype(np.float64).sum(axis=0)).max() <= 1e-4
+
+
+@pytest.mark.parametrize("t", [64, 128, 320])
+def test_softmax_oracle_agrees_with_reference_gpu(ref, t):
+    """Tensor::softmax over the last axis (src/tensor/ops.rs:273-284), as the oracle's attention
+    restatement applies it to scaled, causally masked scores, against fastnn_cuda_softmax on the
+    same masked input (-1e9 above the diagonal, src/nn/transformer.rs:22-27).
+
+    Row lengths are powers of two or at least 256: FastNN's kernel_softmax launches
+    min(row length, 256) threads and halves that count in its shared-memory reduction
+    (cuda/kernels.cu:304-308, 408), which drops partial sums for any other thread count (48 keys
+    gave probabilities off by 1.5).  Its CPU path, which the oracle restates, has no such limit."""
+    import torch
+    rng = np.random.default_rng(9)
+    heads = 5
+    scale = np.float32(1.0 / np.sqrt(32.0))
+    scores = (rng.standard_normal((heads, t, t)) * 6.0).astype(np.float32)
+    want = oracle.causal_softmax(scores, float(scale))
+    masked = scores * scale + np.triu(np.full((t, t), -1e9, dtype=np.float32), k=1)[None]
+    out = torch.full((heads * t, t), float("nan"), device="cuda")
+    ref.fastnn_cuda_softmax.argtypes = [_vp, _vp, _i, _i]
+    assert ref.fastnn_cuda_softmax(_p(_dev(masked.reshape(heads * t, t))), _p(out), heads * t, t) == 0
+    torch.cuda.synchronize()
+    got = out.cpu().numpy().reshape(heads, t, t)
+    assert np.abs(got - want).max() <= 1e-5
+    assert np.abs(got.sum(axis=-1) - 1.0).max() <= 1e-5
+    assert (got[:, np.triu_indices(t, 1)[0], np.triu_indices(t, 1)[1]] == 0.0).all()

@@ -27,6 +27,17 @@ def _worker(rank, world, port, queue):
     f.cuda_init(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
+        _work(rank, world, queue, torch, dist, f, sharding)
+    except BaseException as exc:                 # the parent must not wait for results that never come
+        import traceback
+        queue.put(("error", rank, "".join(traceback.format_exception(exc))))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def _work(rank, world, queue, torch, dist, f, sharding):
+    if True:
         rng = np.random.default_rng(7)                      # same operands on every rank
         out = {}
         for layout, (m, n, k) in ((NN, (520, 264, 132)), (NT, (512, 256, 128)), (TN, (768, 136, 260)),
@@ -90,8 +101,6 @@ def _worker(rank, world, port, queue):
         if rank == 0:
             queue.put((out, s_full, q, kk, status, grads))
         dist.barrier()
-    finally:
-        dist.destroy_process_group()
 
 
 def test_two_gpu_sharded_matmul_nccl(built_library):
@@ -107,7 +116,16 @@ def test_two_gpu_sharded_matmul_nccl(built_library):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, queue)) for r in range(2)]
     for p in procs:
         p.start()
-    items = [queue.get(timeout=300) for _ in range(3)]
+    items = []
+    while len(items) < 3:
+        item = queue.get(timeout=300)
+        if item[0] == "error":
+            for p in procs:
+                p.join(30)
+                if p.is_alive():
+                    p.kill()
+            pytest.fail(f"rank {item[1]} failed:\n{item[2]}")
+        items.append(item)
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
