@@ -53,6 +53,8 @@ SIGNATURES = {
     "fastnn_b200_conv2d_backward_weight": (_i, [_vp, _vp, _vp] + [_i] * 13 + [_vp]),
     "fastnn_b200_gemm_splitk_static": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "fastnn_b200_attention_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
+    "fastnn_b200_attention_forward_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
+    "fastnn_cuda_scaled_dot_product_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i]),
     "fastnn_b200_gemm_gather_ex": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll,
                                         _f, _vp, _i, ctypes.POINTER(_vp), _i, _vp]),
     "fastnn_b200_selftest_bounded_wait": (_i, [ctypes.c_uint, ctypes.POINTER(ctypes.c_uint)]),

@@ -30,6 +30,8 @@ struct AttnParams {
   float scale;
   int causal;
   int nsets;                     // Q/K/V buffer sets in shared memory, 1..4 as fit and are useful
+  const float* mask;             // null, or an additive [tq, tk] mask shared by all heads (added to
+                                 // scale * q.k before the softmax, src/nn/transformer.rs:99-105)
   unsigned int* status;
   long long spin_budget;
 };
@@ -267,29 +269,65 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (!ok) return 0.0f;
       ptx::tc_fence_after_sync();
       // pass 1 finds the row maximum, pass 2 re-reads the scores for the exponentials
-      float mx = -INFINITY;
-      for (int c = 0; c < nchunks; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(ts + c * 32, r);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (c * 32 + j < jmax) mx = fmaxf(mx, __uint_as_float(r[j]));
-      }
-      const float mx2 = (jmax > 0) ? mx * sl2 : 0.0f;
       float sum = 0.0f;
-      for (int c = 0; c < nchunks; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(ts + c * 32, r);
-        ptx::tmem_ld_wait();
+      // The branch below must be warp-uniform (tcgen05.ld / .st are .sync.aligned: every lane of the
+      // warp has to execute the same one), so it depends on the launch alone; lanes whose row lies
+      // past the last query read the last query's mask row and their results are never stored.
+      const float* mrow = p.mask != nullptr
+                              ? p.mask + static_cast<long long>(min(qi, p.tq - 1)) * p.tk : nullptr;
+      if (p.mask == nullptr) {
+        float mx = -INFINITY;
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(ts + c * 32, r);
+          ptx::tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float x = ptx::ex2_approx(fmaf(__uint_as_float(r[j]), sl2, -mx2));
-          const float e = (c * 32 + j < jmax) ? x : 0.0f;
-          sum += e;
-          r[j] = __float_as_uint(e);
+          for (int j = 0; j < 32; ++j)
+            if (c * 32 + j < jmax) mx = fmaxf(mx, __uint_as_float(r[j]));
         }
-        ptx::tmem_st_32x32(ts + c * 32, r);
+        const float mx2 = (jmax > 0) ? mx * sl2 : 0.0f;
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(ts + c * 32, r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float x = ptx::ex2_approx(fmaf(__uint_as_float(r[j]), sl2, -mx2));
+            const float e = (c * 32 + j < jmax) ? x : 0.0f;
+            sum += e;
+            r[j] = __float_as_uint(e);
+          }
+          ptx::tmem_st_32x32(ts + c * 32, r);
+        }
+      } else {
+        // additive mask: logits are scale * s + mask, here in the base-2 domain.  The mask row is
+        // read twice (it is small and stays in L1/L2; lanes hold different rows).
+        constexpr float kLog2e = 1.4426950408889634f;
+        float mx = -INFINITY;
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(ts + c * 32, r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c * 32 + j < jmax)
+              mx = fmaxf(mx, fmaf(__uint_as_float(r[j]), sl2, __ldg(mrow + c * 32 + j) * kLog2e));
+        }
+        const float mx2 = (jmax > 0) ? mx : 0.0f;
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(ts + c * 32, r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float e = 0.0f;
+            if (c * 32 + j < jmax)
+              e = ptx::ex2_approx(fmaf(__uint_as_float(r[j]), sl2, __ldg(mrow + c * 32 + j) * kLog2e) - mx2);
+            sum += e;
+            r[j] = __float_as_uint(e);
+          }
+          ptx::tmem_st_32x32(ts + c * 32, r);
+        }
       }
       ptx::tmem_st_wait();                            // P is in TMEM before the tensor core is told
       ptx::tc_fence_before_sync();
@@ -355,6 +393,42 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc_1cta(tmem_base, kTmemCols);
+  }
+}
+
+// Row softmax of scale-d, masked scores in place, one warp per row of a [rows_total, tk] matrix
+// whose rows cycle through tq query positions: x_j = s_j + mask[qi, j] (mask null = none), keys
+// j > qi hidden when causal; p_j = exp(x_j - max) / sum, the order of Tensor::softmax
+// (src/tensor/ops.rs:273-284).  For the attention shapes the fused kernel does not take.
+__global__ void __launch_bounds__(256)
+masked_softmax_rows_kernel(float* __restrict__ s, const float* __restrict__ mask, long long rows_total,
+                           int tq, int tk, int causal) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long row = warp0; row < rows_total; row += nwarps) {
+    const int qi = static_cast<int>(row % tq);
+    float* x = s + row * tk;
+    const float* m = mask != nullptr ? mask + static_cast<long long>(qi) * tk : nullptr;
+    const int jmax = causal ? min(tk, qi + 1) : tk;
+    float mx = -INFINITY;
+    for (int j = lane; j < jmax; j += 32) {
+      const float v = x[j] + (m != nullptr ? __ldg(m + j) : 0.0f);
+      x[j] = v;
+      mx = fmaxf(mx, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.0f;
+    for (int j = lane; j < jmax; j += 32) {
+      const float e = expf(x[j] - mx);
+      x[j] = e;
+      sum += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+    for (int j = lane; j < tk; j += 32) x[j] = j < jmax ? x[j] * inv : 0.0f;
   }
 }
 

@@ -51,6 +51,7 @@ struct DeviceState {
   std::mutex ws_mutex;                            // guards the two tables below
   std::map<cudaStream_t, Workspace> workspaces;   // split-K partials, one per stream
   std::map<cudaStream_t, Workspace> conv_ws;      // im2col matrix + per-image partials of conv dW
+  std::map<cudaStream_t, Workspace> attn_ws;      // scores of the composed attention path
 };
 
 std::mutex g_mutex;                 // device initialisation only; no GEMM call takes it
@@ -74,6 +75,7 @@ struct Tunables {
   int stages = 0;               // FASTNN_B200_STAGES: upper bound on pipeline stages (0 = none)
   int group_m = 0;              // FASTNN_B200_GROUP_M: tile rows per rasterisation group
   int l2 = -1;                  // FASTNN_B200_L2=<C><A><B>: eviction policies of stores and loads
+  bool no_wide = false;         // FASTNN_B200_WIDE=0: CTA pairs keep 256-wide tiles
 };
 const Tunables& tunables() {
   static const Tunables t = [] {
@@ -89,6 +91,7 @@ const Tunables& tunables() {
     v.stages = num("FASTNN_B200_STAGES", 0);
     v.group_m = num("FASTNN_B200_GROUP_M", 0);
     v.l2 = num("FASTNN_B200_L2", -1);
+    v.no_wide = num("FASTNN_B200_WIDE", 1) == 0;
     return v;
   }();
   return t;
@@ -386,6 +389,30 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
   return best;
 }
 
+// Wide pair tiles (256 x 512, two MMA groups per A stage): where the planner takes CTA pairs with
+// 256-wide tiles and the whole K range per tile, a K deep enough that the no longer overlapped
+// epilogue is a per cent or two of a tile, and a tile count that fills the machine about as well
+// as the 256-wide tiling does.  A 256 x 256 tile needs 64 B/clk of L2 -> SM traffic per CTA at
+// full tensor rate, all an SM can take in; the wide tile needs 48.
+// Measured (8192^3 and 32768 x 16384 x 4096 with its two gradient products, interleaved runs on one
+// box): plain products +7 % at K = 8192, +10-18 % at K = 16384-32768; the fused bias + erf-GELU
+// forward at K = 4096 -10 % (its epilogue is a fifth of a tile's time once it no longer overlaps),
+// so a call with epilogue work keeps 256-wide tiles unless K is very deep.
+void widen_pair_tile(Plan* plan, int m, int n, int k, int batch, int max_clusters, bool epilogue_work) {
+  if (!plan->pair || plan->block_n != fnn::kMaxBlockN || plan->split_k != 1 || plan->cluster_k) return;
+  if (k < (epilogue_work ? 16384 : 4096) || n < 2 * fnn::kPairWideBlockN) return;
+  const long long tiles_m = ceil_div(m, fnn::kPairBlockM);
+  const long long u256 = 1ll * batch * tiles_m * ceil_div(n, fnn::kMaxBlockN);
+  const long long u512 = 1ll * batch * tiles_m * ceil_div(n, fnn::kPairWideBlockN);
+  const long long slots = max_clusters > 0 ? max_clusters : 1;
+  // share of tile slots doing useful columns: wave quantisation times padding of the last tile
+  const double e256 = static_cast<double>(u256) / (((u256 + slots - 1) / slots) * slots) * n /
+                      (ceil_div(n, fnn::kMaxBlockN) * 1.0 * fnn::kMaxBlockN);
+  const double e512 = static_cast<double>(u512) / (((u512 + slots - 1) / slots) * slots) * n /
+                      (ceil_div(n, fnn::kPairWideBlockN) * 1.0 * fnn::kPairWideBlockN);
+  if (e512 >= e256 - 0.03) plan->block_n = fnn::kPairWideBlockN;
+}
+
 // choose_plan walks ~250 candidates (2-3 microseconds of host time, as much as the launch itself
 // for a small GEMM), and training loops repeat a handful of shapes: remember the answers.  The
 // slot tables are per device and constant after init, so the device's state pointer stands for
@@ -517,7 +544,11 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   Plan plan = choose_plan_cached(st, g.m, g.n, g.k + (dual ? g.k2 : 0), g.batch, st->num_sms,
                                  st->max_clusters, a_mn, b_mn, pair_mode,
                                  ck_allowed ? st->ck_slots : nullptr, st->ck_slots_half);
+  if (!tune.no_wide)
+    widen_pair_tile(&plan, g.m, g.n, g.k, g.batch, st->max_clusters,
+                    g.bias != nullptr || g.act != 0 || backward);
   if (pol.block_n > 0) plan.block_n = pol.block_n;
+  if (!plan.pair && plan.block_n > fnn::kMaxBlockN) plan.block_n = fnn::kMaxBlockN;
   if (pol.split_k > 0) { plan.split_k = pol.split_k; plan.cluster_k = false; }
   if (pol.policy == 5) plan.cluster_k = ck_allowed;            // forced: split_k is the cluster size
   if (backward || gather) { plan.split_k = 1; plan.cluster_k = false; }
@@ -541,6 +572,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   // cost (wait, commit, loop) is then paid once per eight MMAs instead of once per four
   int kb_per_stage = (plan.pair && plan.block_n == 256 && kbps >= 8) ? 2 : 1;
   if (plan.pair && tune.kb_per_stage >= 1 && tune.kb_per_stage <= 4) kb_per_stage = tune.kb_per_stage;
+  if (plan.block_n > fnn::kMaxBlockN) kb_per_stage = 1;     // a wide stage already holds eight MMAs
   plan.stages = stages_for(plan.block_n, plan.pair, kb_per_stage);
   if (plan.stages < 2) { kb_per_stage = 1; plan.stages = stages_for(plan.block_n, plan.pair, 1); }
   if (tune.stages >= 1 && tune.stages < plan.stages) plan.stages = tune.stages;
@@ -648,7 +680,9 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
       ok = encode_map(&tmA, g.a, g.m, g.k, B, g.lda * 4ull, sa_bytes, 32, fnn::kBlockK, true);
     }
   }
-  const int b_cols = plan.pair ? plan.block_n / 2 : plan.block_n;   // B columns one CTA loads
+  // B columns one load brings: a CTA's half of one MMA group (a wide tile is two groups of 256)
+  const int b_cols = plan.pair ? (plan.block_n > fnn::kMaxBlockN ? fnn::kMaxBlockN : plan.block_n) / 2
+                               : plan.block_n;
   if (!p.b_mn_major)
     ok = ok && encode_map(&tmB, g.b, g.k, g.n, B, g.ldb * 4ull, sb_bytes, fnn::kBlockK, b_cols);
   else {
@@ -1402,32 +1436,62 @@ extern "C" int fastnn_cuda_conv2d_forward(const float* input, const float* weigh
                                     pad_w, 0, nullptr);
 }
 
-extern "C" int fastnn_b200_attention_forward(const float* q, const float* k, const float* v, float* o,
-                                             int batch_heads, int t_q, int t_k, int head_dim,
-                                             float scale, int causal, void* stream) {
+// The attention core for every shape: the fused kernel when it covers the call and the caller
+// does not want the probabilities, else FastNN's own composition on this library's GEMMs --
+// batched scale * Q.K^T, masked row softmax in place, batched P.V.
+static int attention_impl(const float* q, const float* k, const float* v, float* o, float* attn_weights,
+                          const float* mask, int batch_heads, int t_q, int t_k, int head_dim, float scale,
+                          int causal, void* stream) {
   if (batch_heads < 0 || t_q < 0 || t_k < 1 || head_dim < 1) return -1;
   if (batch_heads == 0 || t_q == 0) return 0;
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr) return -1;
-  // what the fused kernel covers; anything else is for the caller to compose from the GEMMs
-  if ((head_dim % 32) != 0 || head_dim > 128 || t_k > 256 || !(scale > 0.0f)) return -1;
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return -1;
+  DeviceState* st = current_state();
+  if (st == nullptr) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int tk_pad = ceil_div(t_k, 32) * 32;
   // Q/K/V sets in flight per CTA: a set is held from its load until P.V has read V, so the loads
   // of later units need sets of their own to run ahead; as many as fit, up to four.
   int nsets = fnn::kAttnMaxSets;
-  fnn::AttnSmem plan = fnn::attn_smem_plan(head_dim, tk_pad, nsets);
-  while (plan.total > kMaxDynSmem && nsets > 1) plan = fnn::attn_smem_plan(head_dim, tk_pad, --nsets);
-  if (plan.total > kMaxDynSmem) return -1;
-  DeviceState* st = current_state();
-  if (st == nullptr) return -1;
+  fnn::AttnSmem plan;
+  std::memset(&plan, 0, sizeof(plan));
+  bool fused = attn_weights == nullptr && (head_dim % 32) == 0 && head_dim <= 128 && t_k <= 256 &&
+               scale > 0.0f && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) &&
+               1ll * batch_heads * ceil_div(t_q, 128) <= 0x7fffffffll;
+  if (fused) {
+    plan = fnn::attn_smem_plan(head_dim, tk_pad, nsets);
+    while (plan.total > kMaxDynSmem && nsets > 1) plan = fnn::attn_smem_plan(head_dim, tk_pad, --nsets);
+    fused = plan.total <= kMaxDynSmem;
+  }
+  if (!fused) {
+    // scores: the caller's attn_weights, or this stream's scratch
+    const long long rows = 1ll * batch_heads * t_q;
+    if (rows * t_k > (1ll << 40)) return -1;
+    float* scores = attn_weights;
+    if (scores == nullptr &&
+        workspace_reserve(st, st->attn_ws, s, sizeof(float) * static_cast<size_t>(rows) * t_k, &scores) != 0)
+      return -1;
+    GemmArgs g1{FASTNN_B200_NT, q, k, scores, t_q, t_k, head_dim, batch_heads, head_dim, head_dim, t_k,
+                1ll * t_q * head_dim, 1ll * t_k * head_dim, 1ll * t_q * t_k, scale, 0.0f, nullptr, 0, s};
+    int rc = gemm_dispatch(g1);
+    if (rc != 0) return rc;
+    long long blocks = (rows + 7) / 8;                       // eight rows (warps) per block
+    if (blocks > 32ll * st->num_sms) blocks = 32ll * st->num_sms;
+    fnn::masked_softmax_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(scores, mask, rows, t_q, t_k,
+                                                                                causal ? 1 : 0);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    FNN_CUDA_OK(cudaGetLastError());
+    GemmArgs g2{FASTNN_B200_NN, scores, v, o, t_q, head_dim, t_k, batch_heads, t_k, head_dim, head_dim,
+                1ll * t_q * t_k, 1ll * t_k * head_dim, 1ll * t_q * head_dim, 1.0f, 0.0f, nullptr, 0, s};
+    rc = gemm_dispatch(g2);
+    if (rc == 0) t_last.path = 8;
+    return rc;
+  }
   fnn::AttnParams p;
   std::memset(&p, 0, sizeof(p));
   p.heads = batch_heads; p.tq = t_q; p.tk = t_k; p.d = head_dim; p.tk_pad = tk_pad;
   p.q_tiles = ceil_div(t_q, 128);
-  const long long units = 1ll * batch_heads * p.q_tiles;
-  if (units > 0x7fffffffll) return -1;
-  p.total_units = static_cast<int>(units);
-  p.scale = scale; p.causal = causal ? 1 : 0; p.nsets = nsets;
+  p.total_units = static_cast<int>(1ll * batch_heads * p.q_tiles);
+  p.scale = scale; p.causal = causal ? 1 : 0; p.nsets = nsets; p.mask = mask;
   p.status = st->status; p.spin_budget = st->spin_budget;
   CUtensorMap tmQ, tmK, tmV, tmO;
   const uint64_t D = head_dim, H = batch_heads;
@@ -1445,7 +1509,7 @@ extern "C" int fastnn_b200_attention_forward(const float* q, const float* k, con
     cfg.gridDim = dim3(grid, 1, 1);
     cfg.blockDim = dim3(fnn::kAttnThreads, 1, 1);
     cfg.dynamicSmemBytes = plan.total;
-    cfg.stream = static_cast<cudaStream_t>(stream);
+    cfg.stream = s;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
@@ -1457,6 +1521,32 @@ extern "C" int fastnn_b200_attention_forward(const float* q, const float* k, con
   FNN_CUDA_OK(cudaGetLastError());
   t_last = LastCall{4, tk_pad, 1, grid};
   return 0;
+}
+
+extern "C" int fastnn_b200_attention_forward(const float* q, const float* k, const float* v, float* o,
+                                             int batch_heads, int t_q, int t_k, int head_dim,
+                                             float scale, int causal, void* stream) {
+  return attention_impl(q, k, v, o, nullptr, nullptr, batch_heads, t_q, t_k, head_dim, scale, causal, stream);
+}
+
+extern "C" int fastnn_b200_attention_forward_ex(const float* q, const float* k, const float* v, float* o,
+                                                float* attn_weights, const float* mask, int batch_heads,
+                                                int t_q, int t_k, int head_dim, float scale, int causal,
+                                                void* stream) {
+  return attention_impl(q, k, v, o, attn_weights, mask, batch_heads, t_q, t_k, head_dim, scale, causal, stream);
+}
+
+// FastNN's own entry (cuda/kernels.cu:1707-1776): same arguments, default stream.  There the
+// causal flag and the mask are accepted and ignored (the masking code is dead); here both work.
+extern "C" int fastnn_cuda_scaled_dot_product_attention(const float* query, const float* key,
+                                                        const float* value, float* output,
+                                                        float* attn_weights, const float* mask,
+                                                        int batch_size, int num_heads, int seq_len_q,
+                                                        int seq_len_k, int head_dim, float scale,
+                                                        int causal) {
+  if (batch_size < 0 || num_heads < 0 || 1ll * batch_size * num_heads > 0x7fffffffll) return -1;
+  return attention_impl(query, key, value, output, attn_weights, mask, batch_size * num_heads, seq_len_q,
+                        seq_len_k, head_dim, scale, causal, nullptr);
 }
 
 extern "C" int fastnn_b200_reduce_partials(const float* partials, float* c, int m, int n, int count,
@@ -1487,7 +1577,8 @@ extern "C" int fastnn_b200_reduce_partials(const float* partials, float* c, int 
 
 extern "C" int fastnn_b200_set_policy(int policy, int block_n, int split_k) {
   if (policy < 0 || policy > 6) return -1;
-  if (block_n < 0 || block_n > fnn::kMaxBlockN || (block_n % 32) != 0) return -1;
+  if (block_n < 0 || (block_n % 32) != 0) return -1;
+  if (block_n > fnn::kMaxBlockN && !(policy == 4 && block_n == fnn::kPairWideBlockN)) return -1;
   if (split_k < 0) return -1;
   t_policy.policy = policy;
   t_policy.block_n = block_n;
@@ -1523,7 +1614,8 @@ extern "C" int fastnn_b200_plan_query(int layout, int m, int n, int k, int batch
   }
   const bool a_mn = layout == FASTNN_B200_TN && (m % 32) != 0;
   const bool b_mn = layout != FASTNN_B200_NT && (n % 32) != 0;
-  const Plan plan = choose_plan(m, n, k, batch, num_sms, max_clusters, a_mn, b_mn, 0, slots, slots_half);
+  Plan plan = choose_plan(m, n, k, batch, num_sms, max_clusters, a_mn, b_mn, 0, slots, slots_half);
+  if (!tunables().no_wide) widen_pair_tile(&plan, m, n, k, batch, max_clusters, false);
   if (block_n) *block_n = plan.block_n;
   if (split_k) *split_k = plan.split_k;
   if (cta_pair) *cta_pair = plan.pair ? 1 : 0;

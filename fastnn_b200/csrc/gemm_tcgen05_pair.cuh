@@ -8,6 +8,13 @@
 // per output element by a third, which is what the MN-major (transposed) operand layouts need
 // to keep the tensor pipe fed.
 //
+// Wide tiles (block_n = 512): the pair computes 256 x 512 as TWO 256-wide MMA groups that share the
+// A stage -- per 32-deep k-block a CTA then loads 16 KiB of A and 2 x 16 KiB of B for 1024 cycles of
+// tensor work, 48 B/clk, where the 256 x 256 tile needs 64 B/clk: exactly what one SM can take in
+// from L2, so that form waits for its loads whenever anything jitters.  The 512 accumulator
+// columns are all of a CTA's tensor memory: one accumulator set, the epilogue of a tile and the
+// main loop of the next no longer overlap (a per cent or two at the K this form is chosen for).
+//
 // Roles per CTA as in the single-CTA kernel; differences:
 //   * both producers credit the LEADER CTA's (cluster rank 0) full barrier, which therefore
 //     expects two arrivals per stage;
@@ -42,12 +49,17 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
   const uint32_t rank = ptx::cluster_ctarank();          // 0 = leader
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
-  const int half_n = p.block_n >> 1;                     // B columns this CTA loads
+  // one MMA group is at most 256 columns wide; a 512-wide tile is two groups over the same A
+  const int n_sub = p.block_n > kMaxBlockN ? 2 : 1;
+  const int mma_n = p.block_n / n_sub;                   // N of one tcgen05.mma
+  const int half_n = mma_n >> 1;                         // B columns of one group this CTA loads
+  const int n_acc = n_sub == 2 ? 1 : 2;                  // accumulator sets that fit 512 TMEM columns
 
   // A stage holds kb_per_stage consecutive 32-deep k-blocks, each as [A 16 KiB][B half]; one
   // barrier round trip (wait, commit) then covers 4 * kb_per_stage MMAs.
   const int R = p.kb_per_stage;
-  const uint32_t sub_bytes = kStageABytes + static_cast<uint32_t>(half_n) * kBlockK * 4;
+  const uint32_t half_bytes = static_cast<uint32_t>(half_n) * kBlockK * 4;
+  const uint32_t sub_bytes = kStageABytes + static_cast<uint32_t>(n_sub) * half_bytes;
   const uint32_t stage_bytes = static_cast<uint32_t>(R) * sub_bytes;
   const uint32_t staging_base = smem_base + p.num_stages * stage_bytes;
   const uint32_t bar_base = staging_base + kStagingBytes;
@@ -102,7 +114,7 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
       for (int u = cluster_id; u < p.total_units && ok; u += num_clusters) {
         const Unit w = decode_unit_pair(p, u);
         const int m0 = w.mt * kPairBlockM + static_cast<int>(rank) * kBlockM;
-        const int n0 = w.nt * p.block_n + static_cast<int>(rank) * half_n;
+        const int n_tile = w.nt * p.block_n + static_cast<int>(rank) * half_n;
         const int kb0 = w.s * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; kb += R) {
@@ -124,13 +136,17 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
             for (int c = 0; c < kBlockM / 32; ++c)
               ptx::tma_load_3d_pair(sa + c * kChunkBytes, &tmA, fb, m0 + 32 * c, k0, w.b, pol_a);
           }
-          if (!p.b_mn_major) {
-            ptx::tma_load_3d_pair(sb, &tmB, fb, k0, n0, w.b, pol_b);  // box 32 x (block_n / 2)
-          } else if (p.b_chunked) {
-            ptx::tma_load_4d_pair(sb, &tmB, fb, 0, k0, n0 >> 5, w.b, pol_b);
-          } else {
-            for (int c = 0; c < half_n / 32; ++c)
-              ptx::tma_load_3d_pair(sb + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b, pol_b);
+          for (int h = 0; h < n_sub; ++h) {
+            const int n0 = n_tile + h * mma_n;              // this CTA's half of MMA group h
+            const uint32_t sbh = sb + h * half_bytes;
+            if (!p.b_mn_major) {
+              ptx::tma_load_3d_pair(sbh, &tmB, fb, k0, n0, w.b, pol_b);  // box 32 x half_n
+            } else if (p.b_chunked) {
+              ptx::tma_load_4d_pair(sbh, &tmB, fb, 0, k0, n0 >> 5, w.b, pol_b);
+            } else {
+              for (int c = 0; c < half_n / 32; ++c)
+                ptx::tma_load_3d_pair(sbh + c * kChunkBytes, &tmB, fb, n0 + 32 * c, k0, w.b, pol_b);
+            }
           }
           }
           if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
@@ -145,7 +161,7 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
   } else if (warp == 1) {
     // ------------------------------------------------- MMA issuer (leader only) ---
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = ptx::idesc_tf32(kPairBlockM, p.block_n, p.a_mn_major, p.b_mn_major);
+      const uint32_t idesc = ptx::idesc_tf32(kPairBlockM, mma_n, p.a_mn_major, p.b_mn_major);
       const uint64_t a_desc0 = ptx::smem_desc_sw128(
           smem_base, p.a_mn_major ? kChunkBytes : 16u, p.a_mn_major ? 512u : 1024u,
           p.a_mn_major ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128);
@@ -156,6 +172,7 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
       const uint64_t b_kstep = (p.b_mn_major ? 1024u : kUmmaK * 4u) >> 4;
       const uint64_t stage_step = stage_bytes >> 4;
       const uint64_t sub_step = sub_bytes >> 4;
+      const uint64_t half_step = half_bytes >> 4;
       // the two CTAs' copies of a barrier differ by a constant in the cluster address space
       const uint32_t bar0 = ptx::mapa_shared(bar_base, 0);
       const uint32_t bar1 = ptx::mapa_shared(bar_base, 1);
@@ -172,7 +189,7 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBlockN);
-        uint32_t accumulate = 0u;                     // 0 on the unit's first MMA: overwrite
+        uint32_t accumulate = 0u;                     // 0 on the unit's first k-block: overwrite
         for (int kb = kb0; kb < kb1; kb += R) {
           ok = wait_barrier(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout);
           if (!ok) break;
@@ -180,11 +197,15 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
           for (int r = 0; r < nsub; ++r) {
             const uint64_t da = a_desc0 + stage * stage_step + r * sub_step;
             const uint64_t db = b_desc0 + stage * stage_step + r * sub_step;
+            for (int h = 0; h < n_sub; ++h) {         // MMA groups over the same A stage
+              const uint32_t td = tmem_d + static_cast<uint32_t>(h * mma_n);
+              const uint64_t dbh = db + h * half_step;
+              ptx::mma_tf32_2cta(td, da, dbh, idesc, accumulate);
 #pragma unroll
-            for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
-              ptx::mma_tf32_2cta(tmem_d, da + ks * a_kstep, db + ks * b_kstep, idesc, accumulate);
-              accumulate = 1u;
+              for (int ks = 1; ks < kBlockK / kUmmaK; ++ks)
+                ptx::mma_tf32_2cta(td, da + ks * a_kstep, dbh + ks * b_kstep, idesc, 1u);
             }
+            accumulate = 1u;
           }
           ptx::mma_commit_2cta(bar0 + 64u + 8u * stage);    // empty[stage], leader
           ptx::mma_commit_2cta(bar1 + 64u + 8u * stage);    // empty[stage], peer
@@ -193,7 +214,7 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
         if (!ok) break;
         ptx::mma_commit_2cta(bar0 + 128u + 8u * acc);       // accumulator full, leader
         ptx::mma_commit_2cta(bar1 + 128u + 8u * acc);       // accumulator full, peer
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        if (++acc == n_acc) { acc = 0; acc_phase ^= 1u; }
       }
     }
   } else {
@@ -222,7 +243,7 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(acc), 0));
-      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      if (++acc == n_acc) { acc = 0; acc_phase ^= 1u; }
     }
     if (p.store_mode == 0 && lane == 0) ptx::tma_store_wait_all<0>();
   }
@@ -262,5 +283,6 @@ inline size_t gemm_pair_smem_bytes(int block_n, int num_stages, int kb_per_stage
                     (kStageABytes + (block_n / 2) * kBlockK * 4) +
          kStagingBytes + kBarrierBytes;
 }
+constexpr int kPairWideBlockN = 2 * kMaxBlockN;      // 256 x 512 tiles: two MMA groups per A stage
 
 }  // namespace fnn

@@ -398,9 +398,13 @@ def current_stream_ptr() -> int:
     return int(torch.cuda.current_stream().cuda_stream)
 
 
-def attention_forward(q, k, v, scale=None, causal=False, out=None, stream=0):
-    """softmax(scale * q.k^T + causal mask) . v for q [.., t_q, d], k, v [.., t_k, d] in one
-    launch (the core of MultiHeadAttention::forward_attn, src/nn/transformer.rs:87-115)."""
+def attention_forward(q, k, v, scale=None, causal=False, out=None, stream=0, mask=None,
+                      return_weights=False):
+    """softmax(scale * q.k^T + mask) . v for q [.., t_q, d], k, v [.., t_k, d]: the core of
+    MultiHeadAttention::forward_attn (src/nn/transformer.rs:87-115).  ``causal`` hides key j from
+    query i when j > i; ``mask`` is an additive [t_q, t_k] tensor shared by all heads.  One fused
+    launch when the shape allows it and the probabilities are not wanted, FastNN's composition on
+    this library's GEMMs otherwise.  With ``return_weights`` returns (o, probabilities)."""
     _check(q, "q"); _check(k, "k"); _check(v, "v")
     _ensure_ctx(q)
     tq, d = int(q.shape[-2]), int(q.shape[-1])
@@ -408,14 +412,20 @@ def attention_forward(q, k, v, scale=None, causal=False, out=None, stream=0):
     heads = _batch_of(q)
     if tuple(k.shape) != tuple(v.shape) or int(k.shape[-1]) != d or _batch_of(k) != heads:
         raise ValueError("attention shape mismatch")
+    if mask is not None:
+        _check(mask, "mask")
+        if tuple(mask.shape) != (tq, tk):
+            raise ValueError("mask must be [t_q, t_k]")
     if scale is None:
         scale = 1.0 / (d ** 0.5)
     o = _out(tuple(q.shape), q, out)
-    rc = lib().fastnn_b200_attention_forward(_ptr(q), _ptr(k), _ptr(v), _ptr(o), heads, tq, tk, d,
-                                             float(scale), 1 if causal else 0, ctypes.c_void_p(stream))
+    w = torch.empty(tuple(q.shape[:-1]) + (tk,), dtype=torch.float32, device=q.device) if return_weights else None
+    rc = lib().fastnn_b200_attention_forward_ex(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(w), _ptr(mask), heads,
+                                                tq, tk, d, float(scale), 1 if causal else 0,
+                                                ctypes.c_void_p(stream))
     if rc != 0:
-        raise CudaError("CUDA attention_forward failed (shape outside the fused kernel's range?)")
-    return o
+        raise CudaError("CUDA attention_forward failed")
+    return (o, w) if return_weights else o
 
 
 def reduce_partials(partials_ptr, c_ptr, m, n, count, ldc=None, alpha=1.0, beta=0.0, bias_ptr=0,

@@ -198,19 +198,41 @@ FASTNN_B200_API int fastnn_b200_conv2d_backward_weight(const float* input, const
                                                        int kernel_h, int kernel_w, int stride_h,
                                                        int stride_w, int pad_h, int pad_w, void* stream);
 
-/* Fused attention core, per head h in [0, batch_heads):
+/* Attention core, per head h in [0, batch_heads):
  *   O[h] = softmax( scale * Q[h] . K[h]^T + mask ) . V[h]
  * q [batch_heads, t_q, head_dim], k and v [batch_heads, t_k, head_dim], o like q, all dense.
- * mask: with causal != 0, key j is hidden from query i when j > i (FastNN adds -1e9 there,
- * src/nn/transformer.rs:22-27); softmax over keys as src/tensor/ops.rs:273-284.  One launch
- * instead of FastNN's batched matmul + mul_scalar + add + softmax + batched matmul
- * (src/nn/transformer.rs:87-115); the [batch_heads, t_q, t_k] scores never reach memory.
- * Covers head_dim in {32, 64, 96, 128}, t_k <= 256, scale > 0 and shapes whose working set
- * fits shared memory; returns -1 for anything else (compose it from the GEMM entries). */
+ * With causal != 0, key j is hidden from query i when j > i (FastNN adds -1e9 there,
+ * src/nn/transformer.rs:22-27); `mask` (the _ex form and FastNN's symbol; may be NULL) is an
+ * additive [t_q, t_k] matrix shared by all heads, the form FastNN's cached mask has
+ * (src/nn/transformer.rs:15-30, 99-105); softmax over keys as src/tensor/ops.rs:273-284.
+ * attn_weights (may be NULL) receives the probabilities [batch_heads, t_q, t_k].
+ *
+ * Fused form -- one launch instead of FastNN's batched matmul + mul_scalar + add + softmax +
+ * batched matmul (src/nn/transformer.rs:87-115), the scores never reach memory: taken when the
+ * probabilities are not asked for and head_dim is in {32, 64, 96, 128}, t_k <= 256, scale > 0,
+ * the operands are 16-byte aligned and the working set fits shared memory.
+ * Every other call runs FastNN's own composition on this library's kernels: batched
+ * scale * Q.K^T (NT GEMM), a masked row softmax in place, batched P.V (NN GEMM); the scores live
+ * in attn_weights or in a per-stream scratch buffer.
+ *
+ * fastnn_cuda_scaled_dot_product_attention has the signature of FastNN's own entry
+ * (cuda/include/kernels.h:209, cuda/kernels.cu:1707-1776: transpose + cuBLAS + softmax + cuBLAS
+ * with a cudaMalloc per call) and replaces it.  There `causal` and `mask` are accepted and ignored
+ * (the masking code is dead); here both are applied. */
 FASTNN_B200_API int fastnn_b200_attention_forward(const float* q, const float* k, const float* v,
                                                   float* o, int batch_heads, int t_q, int t_k,
                                                   int head_dim, float scale, int causal,
                                                   void* stream);
+FASTNN_B200_API int fastnn_b200_attention_forward_ex(const float* q, const float* k, const float* v,
+                                                     float* o, float* attn_weights, const float* mask,
+                                                     int batch_heads, int t_q, int t_k, int head_dim,
+                                                     float scale, int causal, void* stream);
+FASTNN_B200_API int fastnn_cuda_scaled_dot_product_attention(const float* query, const float* key,
+                                                             const float* value, float* output,
+                                                             float* attn_weights, const float* mask,
+                                                             int batch_size, int num_heads,
+                                                             int seq_len_q, int seq_len_k, int head_dim,
+                                                             float scale, int causal);
 
 /* The general GEMM with an all-gather of C fused into its epilogue, for the multi-GPU form of the
  * path in which the rows of C (or the batches) are split over GPUs and a caller wants all of C on
@@ -298,12 +320,13 @@ FASTNN_B200_API int fastnn_b200_memcpy_d2h_async(float* dst, const float* src, s
  * serve -- fewer 32-deep k-blocks than split_k, a backward epilogue -- takes the workspace form
  * of the same split), 6 = automatic, but never the cluster form.  3 and 4 never take it either.
  * block_n in {0 (auto), 32, 64, 96, ..., 256} (rounded up to a multiple of 64 for CTA
- * pairs); split_k >= 0 (0 = auto). */
+ * pairs; with policy 4 also 512, the 256 x 512 pair tile); split_k >= 0 (0 = auto). */
 FASTNN_B200_API int fastnn_b200_set_policy(int policy, int block_n, int split_k);
 
 /* Which path the most recent call on this thread took: 1 = SIMT, 2 = tcgen05 1-CTA, 3 = tcgen05
  * 2-CTA, 4 = fused attention, 5 = conv2d, 6 = tcgen05 1-CTA with the K split inside clusters
- * (one launch, no workspace), 7 = a direct (FP32 FMA) convolution kernel; 0 before any call.
+ * (one launch, no workspace), 7 = a direct (FP32 FMA) convolution kernel, 8 = attention composed
+ * from two batched GEMMs and a row softmax; 0 before any call.
  * Also reports its tile and split choice. */
 FASTNN_B200_API int fastnn_b200_last_path(int* block_n, int* split_k, int* num_ctas);
 

@@ -294,6 +294,28 @@ ORACLE_API void oracle_masked_softmax(float* s, size_t batch, size_t tq, size_t 
     }
 }
 
+/* The same with a general additive mask [tq, tk] shared by every batch entry, the form of
+ * FastNN's cached mask tensor (src/nn/transformer.rs:15-30; added by `scores.add(&mask)`, :99-105):
+ * mul_scalar(scale) -> + mask (+ the causal 0/-1e9 term) -> row softmax.  mask may be NULL. */
+ORACLE_API void oracle_masked_softmax_add(float* s, size_t batch, size_t tq, size_t tk, float scale,
+                                          int causal, const float* mask) {
+  for (size_t b = 0; b < batch; ++b)
+    for (size_t qi = 0; qi < tq; ++qi) {
+      float* row = s + (b * tq + qi) * tk;
+      for (size_t ki = 0; ki < tk; ++ki) {
+        float v = row[ki] * scale;
+        if (mask) v = v + mask[qi * tk + ki];
+        if (causal) v = v + (ki > qi ? -1e9f : 0.0f);
+        row[ki] = v;
+      }
+      float mx = -INFINITY;
+      for (size_t ki = 0; ki < tk; ++ki) mx = row[ki] > mx ? row[ki] : mx;
+      float sum = 0.0f;
+      for (size_t ki = 0; ki < tk; ++ki) sum += expf(row[ki] - mx);
+      for (size_t ki = 0; ki < tk; ++ki) row[ki] = expf(row[ki] - mx) / sum;
+    }
+}
+
 /* ---------------------------------------------------------------------------
  * Row-parallel twin.  NOT in the reference (its rayon dependency is never
  * called): the outer row loop of the same nest is split over threads, each row

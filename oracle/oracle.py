@@ -281,18 +281,23 @@ def causal_softmax(scores: np.ndarray, scale: float) -> np.ndarray:
     return s
 
 
-def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, causal: bool) -> np.ndarray:
+def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, causal: bool, mask=None,
+              return_weights: bool = False):
     """The attention core of MultiHeadAttention::forward_attn on CPU tensors
     (src/nn/transformer.rs:87-115): matmul(q, k^T) * scale (+ mask) -> softmax -> matmul(., v).
-    q [heads, t_q, d], k and v [heads, t_k, d]."""
+    q [heads, t_q, d], k and v [heads, t_k, d]; ``mask`` an additive [t_q, t_k] array shared by
+    all heads, or None.  With ``return_weights`` also returns the probabilities."""
     q, k, v = _f32(q), _f32(k), _f32(v)
     s = matmul(q, transpose(k))                 # forward uses the NN entry on a materialised K^T
     heads, tq, tk = s.shape
     lib = _load()
-    lib.oracle_masked_softmax.argtypes = [_fp, _sz, _sz, _sz, ctypes.c_float, ctypes.c_int]
-    lib.oracle_masked_softmax.restype = None
-    lib.oracle_masked_softmax(_p(s), heads, tq, tk, ctypes.c_float(scale), 1 if causal else 0)
-    return matmul(s, v)
+    lib.oracle_masked_softmax_add.argtypes = [_fp, _sz, _sz, _sz, ctypes.c_float, ctypes.c_int, _fp]
+    lib.oracle_masked_softmax_add.restype = None
+    m32 = _f32(mask) if mask is not None else None
+    mp = _p(m32) if m32 is not None else ctypes.cast(None, _fp)
+    lib.oracle_masked_softmax_add(_p(s), heads, tq, tk, ctypes.c_float(scale), 1 if causal else 0, mp)
+    o = matmul(s, v)
+    return (o, s) if return_weights else o
 
 
 def ref_gpu_library_path():

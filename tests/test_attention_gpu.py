@@ -90,14 +90,108 @@ def test_fused_attention_agrees_with_the_unfused_gpu_path(gpu):
     _check(got, want, 128, v.cpu().numpy(), "fused vs unfused GPU")
 
 
-def test_fused_attention_rejects_what_it_does_not_cover(gpu):
+def _operands(heads, tq, tk, d, seed):
+    rng = np.random.default_rng(seed)
+    return (rng.standard_normal((heads, tq, d), dtype=np.float32),
+            rng.standard_normal((heads, tk, d), dtype=np.float32),
+            rng.standard_normal((heads, tk, d), dtype=np.float32))
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("shape", [(6, 128, 128, 32), (3, 200, 136, 64), (2, 64, 40, 32)])
+def test_fused_attention_with_an_additive_mask(gpu, shape, causal):
+    """A general additive [t_q, t_k] mask (the form of FastNN's cached mask tensor,
+    src/nn/transformer.rs:15-30, 99-105) inside the fused kernel: finite biases and -1e9 entries,
+    one row hidden completely except one key."""
+    import torch
+    f = gpu
+    heads, tq, tk, d = shape
+    q, k, v = _operands(heads, tq, tk, d, sum(shape) + int(causal))
+    rng = np.random.default_rng(77)
+    mask = rng.standard_normal((tq, tk)).astype(np.float32)
+    mask[rng.random((tq, tk)) < 0.2] = -1e9
+    mask[:, 0] = 0.0                                    # every query keeps one visible key
+    mask[5, 1:] = -1e9
+    scale = 1.0 / np.sqrt(d)
+    got = f.attention_forward(torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(),
+                              scale=scale, causal=causal, mask=torch.from_numpy(mask).cuda())
+    assert f.last_path()["path"] == 4
+    want = oracle.attention(q, k, v, scale, causal, mask=mask)
+    _check(got.cpu().numpy(), want, tk, v, f"masked {shape} causal={causal}")
+    assert np.allclose(got.cpu().numpy()[:, 5, :], v[:, 0, :], rtol=2e-3, atol=1e-6)
+    assert f.device_status() == 0
+
+
+@pytest.mark.parametrize("shape", [
+    (2, 300, 300, 32),      # more keys than the fused kernel's 256
+    (3, 128, 1024, 64),     # long key range
+    (2, 50, 70, 48),        # head_dim not a multiple of 32
+    (2, 33, 17, 20),        # nothing aligned for TMA: both GEMMs on the SIMT kernel
+    (4, 128, 128, 160),     # head_dim above 128
+])
+def test_attention_outside_the_fused_kernel_is_composed_from_the_gemms(gpu, shape):
+    """What the fused kernel does not cover runs FastNN's own composition (batched scale * Q.K^T,
+    masked row softmax, batched P.V) on this library's kernels -- no shape is refused."""
+    import torch
+    f = gpu
+    heads, tq, tk, d = shape
+    q, k, v = _operands(heads, tq, tk, d, sum(shape))
+    scale = 1.0 / np.sqrt(d)
+    for causal, use_mask in ((True, False), (False, True), (False, False)):
+        mask = None
+        if use_mask:
+            mask = np.random.default_rng(5).standard_normal((tq, tk)).astype(np.float32)
+        got = f.attention_forward(torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(),
+                                  torch.from_numpy(v).cuda(), scale=scale, causal=causal,
+                                  mask=None if mask is None else torch.from_numpy(mask).cuda())
+        assert f.last_path()["path"] == 8
+        want = oracle.attention(q, k, v, scale, causal, mask=mask)
+        _check(got.cpu().numpy(), want, tk, v, f"composed {shape} causal={causal} mask={use_mask}")
+    assert f.device_status() == 0
+
+
+def test_reference_symbol_returns_output_and_probabilities(gpu):
+    """fastnn_cuda_scaled_dot_product_attention with FastNN's argument list: output and
+    attn_weights, with a causal flag and a mask that take effect (FastNN's entry ignores both)."""
     import torch
     f = gpu
     lib = f.lib()
-    t = torch.zeros(4 * 300 * 48, device="cuda")
+    batch, nheads, tq, tk, d = 2, 3, 96, 96, 32
+    q, k, v = _operands(batch * nheads, tq, tk, d, 41)
+    mask = np.random.default_rng(6).standard_normal((tq, tk)).astype(np.float32)
+    scale = 1.0 / np.sqrt(d)
+    dq, dk, dv, dm = (torch.from_numpy(t).cuda() for t in (q, k, v, mask))
+    vp = lambda t: ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+    for causal, m, dmask in ((1, None, None), (0, mask, dm), (1, mask, dm)):
+        o = torch.full((batch * nheads, tq, d), float("nan"), device="cuda")
+        w = torch.full((batch * nheads, tq, tk), float("nan"), device="cuda")
+        assert lib.fastnn_cuda_scaled_dot_product_attention(vp(dq), vp(dk), vp(dv), vp(o), vp(w), vp(dmask), batch,
+                                                            nheads, tq, tk, d, scale, causal) == 0
+        torch.cuda.synchronize()
+        want_o, want_w = oracle.attention(q, k, v, scale, bool(causal), mask=m, return_weights=True)
+        _check(o.cpu().numpy(), want_o, tk, v, f"reference symbol causal={causal}")
+        wg = w.cpu().numpy()
+        assert np.abs(wg - want_w).max() <= 2e-3              # probabilities from TF32 scores
+        assert np.abs(wg.sum(-1) - 1.0).max() <= 1e-5
+        if causal:
+            iu = np.triu_indices(tq, 1)
+            assert (wg[:, iu[0], iu[1]] == 0.0).all()
+    # without attn_weights the same symbol takes the fused kernel
+    o = torch.empty((batch * nheads, tq, d), device="cuda")
+    assert lib.fastnn_cuda_scaled_dot_product_attention(vp(dq), vp(dk), vp(dv), vp(o), None, None, batch, nheads,
+                                                        tq, tk, d, scale, 1) == 0
+    assert f.last_path()["path"] == 4
+    _check(o.cpu().numpy(), oracle.attention(q, k, v, scale, True), tk, v, "reference symbol, fused")
+    assert f.device_status() == 0
+
+
+def test_attention_checks_its_arguments(gpu):
+    import torch
+    f = gpu
+    lib = f.lib()
+    t = torch.zeros(1024, device="cuda")
     p = ctypes.c_void_p(t.data_ptr())
-    assert lib.fastnn_b200_attention_forward(p, p, p, p, 1, 16, 16, 48, 1.0, 0, None) == -1   # head_dim
-    assert lib.fastnn_b200_attention_forward(p, p, p, p, 1, 16, 300, 32, 1.0, 0, None) == -1  # t_k
-    assert lib.fastnn_b200_attention_forward(p, p, p, p, 1, 16, 256, 128, 1.0, 0, None) == -1  # smem
-    assert lib.fastnn_b200_attention_forward(p, p, p, p, 1, 16, 16, 32, 0.0, 0, None) == -1   # scale
+    assert lib.fastnn_b200_attention_forward(p, p, p, p, 1, 16, 0, 32, 1.0, 0, None) == -1    # no keys
+    assert lib.fastnn_b200_attention_forward(p, p, p, p, 1, 16, 16, 0, 1.0, 0, None) == -1    # head_dim
+    assert lib.fastnn_b200_attention_forward(p, p, p, None, 1, 16, 16, 32, 1.0, 0, None) == -1  # null output
     assert lib.fastnn_b200_attention_forward(p, p, p, p, 0, 16, 16, 32, 1.0, 0, None) == 0    # empty

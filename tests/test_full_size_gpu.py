@@ -4,7 +4,8 @@ At 8192^3 and 32768 x 16384 x 4096 the CPU oracle needs minutes per product, so 
 (1) exact integer arithmetic: small-integer operands are exact in TF32 and their dot products are
     exact in FP32, so row/column checksums of C must equal checksums computed from A and B alone
     ("checksum of checksums"), bit for bit;
-(2) a slab of rows recomputed by the oracle on the real-valued inputs (TF32 tolerance);
+(2) a contiguous slab of rows plus 64 rows drawn at random, recomputed by the oracle on the
+    real-valued inputs (TF32 tolerance); the checked fraction of the output is printed;
 (3) agreement of the three layouts on the same logical operands.
 """
 import numpy as np
@@ -23,6 +24,13 @@ def _int_operands(torch, m, n, k, seed):
     a = torch.randint(-3, 4, (m, k), device="cuda", generator=g).float()
     b = torch.randint(-3, 4, (k, n), device="cuda", generator=g).float()
     return a, b
+
+
+def _slab_and_random_rows(total, slab0, slab_rows, extra, seed):
+    """A contiguous slab [slab0, slab0 + slab_rows) and `extra` further rows drawn at random."""
+    slab = np.arange(slab0, slab0 + slab_rows)
+    rest = np.setdiff1d(np.arange(total), slab)
+    return np.sort(np.concatenate([slab, np.random.default_rng(seed).choice(rest, extra, replace=False)]))
 
 
 def _run(f, layout, a, b):
@@ -61,7 +69,8 @@ def test_square_8192_real_inputs_row_slab_and_layout_agreement(gpu):
     a = torch.randn(m, k, device="cuda", generator=g)
     b = torch.randn(k, n, device="cuda", generator=g)
     c_nn, c_nt, c_tn = (_run(f, L, a, b) for L in (NN, NT, TN))
-    rows = np.sort(np.random.default_rng(1).choice(m, 48, replace=False))
+    rows = _slab_and_random_rows(m, 3072, 512, 64, seed=1)
+    print(f"8192^3: {len(rows)} of {m} rows checked against the oracle ({100.0 * len(rows) / m:.1f} % of C)")
     ah = a[torch.from_numpy(rows).cuda()].cpu().numpy()
     bh = b.cpu().numpy()
     want = oracle.matmul(ah, bh, threads=oracle.host_threads())
@@ -86,7 +95,8 @@ def test_scaled_linear_gelu_full_size(gpu):
     bias = (torch.rand(n, device="cuda", generator=g) * 2 - 1) * 0.01
     y = f.linear_forward(x, w, bias, act=2, layout=NN)
     assert f.last_path()["path"] in (2, 3)
-    rows = np.sort(np.random.default_rng(2).choice(m, 32, replace=False))
+    rows = _slab_and_random_rows(m, 16384, 128, 64, seed=2)
+    print(f"linear+GELU forward: {len(rows)} of {m} rows checked against the oracle")
     ridx = torch.from_numpy(rows).cuda()
     xh, wh, bh = x[ridx].cpu().numpy(), w.cpu().numpy(), bias.cpu().numpy()
     pre = oracle.bias_act(oracle.matmul(xh, wh, threads=oracle.host_threads()), bh, 0)
@@ -96,17 +106,45 @@ def test_scaled_linear_gelu_full_size(gpu):
     assert err.max() <= 1e-2 * np.sqrt(k) * np.abs(xh).max() * np.abs(wh).max()
     assert np.linalg.norm(err) / np.linalg.norm(pre) <= 5e-3
     del y
-    # backward shapes on integer operands: exact checksums
-    dy = torch.randint(-2, 3, (m, n), device="cuda", generator=g).float()
-    wi = torch.randint(-2, 3, (k, n), device="cuda", generator=g).float()
-    dx = f.matmul_nt(dy, wi)                                  # dX = dY . W^T   [m, k]
-    ones = torch.ones(k, 1, device="cuda", dtype=torch.float64)
-    assert torch.equal(dx.double() @ ones, dy.double() @ (wi.double().t() @ ones))
+    # the two backward products on the configured real-valued inputs (dY ~ N(0, 1e-3)), rows and
+    # columns recomputed by the oracle
+    dy = torch.randn(m, n, device="cuda", generator=g) * 1e-3
+    threads = oracle.host_threads()
+    dx = f.matmul_nt(dy, w)                                   # dX = dY . W^T   [m, k], contraction n
+    assert f.last_path()["path"] in (2, 3)
+    rows = _slab_and_random_rows(m, 8192, 32, 64, seed=3)
+    ridx = torch.from_numpy(rows).cuda()
+    dyh = dy[ridx].cpu().numpy()
+    want = oracle.matmul(dyh, np.ascontiguousarray(wh.T), threads=threads)
+    check_tf32_parity(dx[ridx].cpu().numpy(), want, n, dyh, wh, what="dX = dY . W^T rows")
+    print(f"dX: {len(rows)} of {m} rows checked against the oracle")
     del dx
+    dwt = f.matmul_tn(x, dy)                                  # dW = X^T . dY   [k, n], contraction m
+    assert f.last_path()["path"] in (2, 3)
+    cols = _slab_and_random_rows(k, 1024, 32, 64, seed=4)     # rows of dW = columns of the stored X
+    cidx = torch.from_numpy(cols).cuda()
+    xt = np.ascontiguousarray(x[:, cidx].cpu().numpy().T)     # [len(cols), m]
+    dy_host = dy.cpu().numpy()
+    want = oracle.matmul(xt, dy_host, threads=threads)
+    check_tf32_parity(dwt[cidx].cpu().numpy(), want, m, xt, dy_host, what="dW = X^T . dY rows")
+    print(f"dW: {len(cols)} of {k} rows checked against the oracle")
+    del dwt, dy_host, want
+    # and on integer operands: exact row, column and +-1-probe checksums
+    dyi = torch.randint(-2, 3, (m, n), device="cuda", generator=g).float()
+    wi = torch.randint(-2, 3, (k, n), device="cuda", generator=g).float()
     xi = torch.randint(-2, 3, (m, k), device="cuda", generator=g).float()
-    dwt = f.matmul_tn(xi, dy)                                 # dW = X^T . dY   [k, n]
-    ones = torch.ones(n, 1, device="cuda", dtype=torch.float64)
-    assert torch.equal(dwt.double() @ ones, xi.double().t() @ (dy.double() @ ones))
+    probe = lambda size: (torch.randint(0, 2, (size, 1), device="cuda", generator=g) * 2 - 1).double()
+    dx = f.matmul_nt(dyi, wi).double()                        # [m, k]; |entries| <= 4 * 16384 < 2^24
+    for s_k in (torch.ones(k, 1, device="cuda", dtype=torch.float64), probe(k)):
+        assert torch.equal(dx @ s_k, dyi.double() @ (wi.double().t() @ s_k)), "dX row checksum"
+    ones_m = torch.ones(1, m, device="cuda", dtype=torch.float64)
+    assert torch.equal(ones_m @ dx, (ones_m @ dyi.double()) @ wi.double().t()), "dX column checksum"
+    del dx
+    dwt = f.matmul_tn(xi, dyi).double()                       # [k, n]; |entries| <= 4 * 32768 < 2^24
+    for s_n in (torch.ones(n, 1, device="cuda", dtype=torch.float64), probe(n)):
+        assert torch.equal(dwt @ s_n, xi.double().t() @ (dyi.double() @ s_n)), "dW row checksum"
+    ones_k = torch.ones(1, k, device="cuda", dtype=torch.float64)
+    assert torch.equal(ones_k @ dwt, (ones_k @ xi.double().t()) @ dyi.double()), "dW column checksum"
 
 
 def test_run_to_run_determinism(gpu):

@@ -95,6 +95,51 @@ def test_tensor_core_path_matches_oracle(gpu, layout, shape, policy):
     check_tf32_parity(_host(got), _oracle(layout, a, b), k, a, b, what=f"L{layout} {shape}")
 
 
+WIDE = [(512, 1024, 256, 0), (300, 1100, 132, 0), (256, 512, 64, 3), (1000, 776, 516, 0), (640, 2048, 1056, 0)]
+
+
+@pytest.mark.parametrize("layout", [NN, NT, TN])
+@pytest.mark.parametrize("shape", WIDE)
+def test_wide_pair_tiles_match_oracle(gpu, layout, shape):
+    """256 x 512 tiles on CTA pairs: two MMA groups per A stage, one accumulator set over all 512
+    tensor-memory columns; ragged M, N (last tile half empty) and K, batched, with a K split."""
+    f = gpu
+    m, n, k, batch = shape
+    rng = np.random.default_rng(3000 + 7 * layout + m + n + k)
+    sa, sb = _shapes(layout, m, n, k, batch)
+    a = rng.standard_normal(sa, dtype=np.float32)
+    b = rng.standard_normal(sb, dtype=np.float32)
+    want = _oracle(layout, a, b)
+    for split in (1, 3):
+        f.set_policy(4, 512, split)
+        try:
+            got = _gpu_fn(f, layout)(_dev(a), _dev(b))
+        finally:
+            f.set_policy(0, 0, 0)
+        lp = f.last_path()
+        assert lp["path"] == 3 and lp["block_n"] == 512, lp
+        check_tf32_parity(_host(got), want, k, a, b, what=f"wide L{layout} {shape} split {split}")
+    assert f.device_status() == 0
+
+
+def test_wide_pair_tiles_with_bias_and_gelu(gpu):
+    f = gpu
+    m, n, k = 768, 1536, 512
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    f.set_policy(4, 512, 1)
+    try:
+        got = f.linear_forward(_dev(a), _dev(b), _dev(bias), act=f.ACT_GELU, layout=f.NN)
+    finally:
+        f.set_policy(0, 0, 0)
+    assert f.last_path()["block_n"] == 512
+    want = oracle.bias_act(oracle.matmul(a, b), bias, oracle.ACT_GELU)
+    assert np.abs(_host(got) - want).max() <= 1e-2 * np.sqrt(k) * np.abs(a).max() * np.abs(b).max()
+    assert f.device_status() == 0
+
+
 @pytest.mark.parametrize("layout", [NN, NT, TN])
 @pytest.mark.parametrize("shape", RAGGED + ALIGNED[:6])
 def test_simt_path_matches_oracle(gpu, layout, shape):

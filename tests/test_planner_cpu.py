@@ -14,10 +14,12 @@ def plan(built_library):
 def test_large_square_gemms_take_cta_pairs_with_the_widest_tile(plan):
     for layout in (NN, NT, TN):
         p = plan(layout, 8192, 8192, 8192)
-        assert p == {"block_n": 256, "split_k": 1, "cta_pair": True, "cluster_k": False}
+        assert p == {"block_n": 512, "split_k": 1, "cta_pair": True, "cluster_k": False}
     for shape in ((NN, 32768, 16384, 4096), (NT, 32768, 4096, 16384), (TN, 4096, 16384, 32768)):
         p = plan(*shape)
-        assert p["cta_pair"] and p["block_n"] == 256 and p["split_k"] == 1
+        assert p["cta_pair"] and p["block_n"] == 512 and p["split_k"] == 1
+    # the 256 x 512 tile only where it fills the machine about as well as 256 x 256 tiles do
+    assert plan(NN, 5120, 4096, 4096)["block_n"] == 256
 
 
 def test_transformer_block_forward_shapes_are_not_split(plan):
