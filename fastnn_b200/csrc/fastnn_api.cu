@@ -389,28 +389,44 @@ Plan choose_plan(int m, int n, int k, int batch, int num_sms, int max_clusters, 
   return best;
 }
 
-// Wide pair tiles (256 x 512, two MMA groups per A stage): where the planner takes CTA pairs with
-// 256-wide tiles and the whole K range per tile, a K deep enough that the no longer overlapped
-// epilogue is a per cent or two of a tile, and a tile count that fills the machine about as well
-// as the 256-wide tiling does.  A 256 x 256 tile needs 64 B/clk of L2 -> SM traffic per CTA at
-// full tensor rate, all an SM can take in; the wide tile needs 48.
-// Measured (8192^3 and 32768 x 16384 x 4096 with its two gradient products, interleaved runs on one
-// box): plain products +7 % at K = 8192, +10-18 % at K = 16384-32768; the fused bias + erf-GELU
-// forward at K = 4096 -10 % (its epilogue is a fifth of a tile's time once it no longer overlaps),
-// so a call with epilogue work keeps 256-wide tiles unless K is very deep.
-void widen_pair_tile(Plan* plan, int m, int n, int k, int batch, int max_clusters, bool epilogue_work) {
-  if (!plan->pair || plan->block_n != fnn::kMaxBlockN || plan->split_k != 1 || plan->cluster_k) return;
-  if (k < (epilogue_work ? 16384 : 4096) || n < 2 * fnn::kPairWideBlockN) return;
-  const long long tiles_m = ceil_div(m, fnn::kPairBlockM);
-  const long long u256 = 1ll * batch * tiles_m * ceil_div(n, fnn::kMaxBlockN);
-  const long long u512 = 1ll * batch * tiles_m * ceil_div(n, fnn::kPairWideBlockN);
-  const long long slots = max_clusters > 0 ? max_clusters : 1;
-  // share of tile slots doing useful columns: wave quantisation times padding of the last tile
-  const double e256 = static_cast<double>(u256) / (((u256 + slots - 1) / slots) * slots) * n /
-                      (ceil_div(n, fnn::kMaxBlockN) * 1.0 * fnn::kMaxBlockN);
-  const double e512 = static_cast<double>(u512) / (((u512 + slots - 1) / slots) * slots) * n /
-                      (ceil_div(n, fnn::kPairWideBlockN) * 1.0 * fnn::kPairWideBlockN);
-  if (e512 >= e256 - 0.03) plan->block_n = fnn::kPairWideBlockN;
+// Deep products with at least a machine-full of tiles: the kind of tile is chosen by waves.
+//   single CTAs, 128 x 256 tiles   one SM ingests 96 B/clk from L2 at full tensor rate (it can take 64)
+//   CTA pairs,   256 x 256 tiles   64 B/clk per SM
+//   CTA pairs,   256 x 512 tiles   48 B/clk per SM: two MMA groups share the A stage; the 512
+//                                  accumulator columns are all of tensor memory, so the epilogue of a
+//                                  tile no longer overlaps the next main loop
+// Time = waves x (tile area per CTA) / rate, with the rates measured on 1024 x 8192 x 8192 (a burst:
+// 630 / 681 / 732 TFLOP/s at 86 % tile-slot use, i.e. 1 : 1.08 : 1.16); the same figures rank
+// 2048, 4096 and 8192 rows and 32768 x 16384 x 4096 with its gradient products the way they
+// measured (8192^3: +7 % for the wide tile; K = 16384-32768: +10-18 %).  No K split: with this
+// many tiles the partial sums cost more than the idle slots they would fill.  The fused bias +
+// erf-GELU forward at K = 4096 lost 10 % on wide tiles (its epilogue is a fifth of a tile's time
+// once nothing overlaps it), so a call with epilogue work takes them only for very deep K.
+void refine_large_plan(Plan* plan, int m, int n, int k, int batch, int num_sms, int max_clusters,
+                       bool a_mn, bool b_mn, int pair_mode, bool epilogue_work, bool allow_wide) {
+  if (k < 2048 || a_mn || b_mn) return;       // per-chunk operand boxes are producer-bound: keep the model
+  const long long t_single = 1ll * batch * ceil_div(m, fnn::kBlockM) * ceil_div(n, fnn::kMaxBlockN);
+  if (t_single < num_sms) return;             // skinny outputs: the cost model's K split stands
+  const bool pair_ok = pair_mode != 1 && max_clusters >= 1 && m > fnn::kBlockM;
+  const long long t_pair = 1ll * batch * ceil_div(m, fnn::kPairBlockM) * ceil_div(n, fnn::kMaxBlockN);
+  const long long t_wide = 1ll * batch * ceil_div(m, fnn::kPairBlockM) * ceil_div(n, fnn::kPairWideBlockN);
+  auto waves = [](long long units, long long slots) { return static_cast<double>((units + slots - 1) / slots); };
+  double best = pair_mode == 2 ? 1e300 : waves(t_single, num_sms);
+  int kind = 0;                               // 0 single, 1 pair, 2 wide pair
+  if (pair_ok) {
+    const double c = waves(t_pair, max_clusters) / 1.08;
+    if (c < best) { best = c; kind = 1; }
+    if (allow_wide && n >= fnn::kPairWideBlockN && k >= (epilogue_work ? 16384 : 4096)) {
+      const double cw = waves(t_wide, max_clusters) * 2.0 / 1.16;
+      if (cw < best) { best = cw; kind = 2; }
+    }
+  }
+  plan->split_k = 1;
+  plan->cluster_k = false;
+  plan->pair = kind != 0;
+  if (kind == 1) plan->block_n = fnn::kMaxBlockN;
+  if (kind == 2) plan->block_n = fnn::kPairWideBlockN;
+  if (kind == 0 && plan->block_n > fnn::kMaxBlockN) plan->block_n = fnn::kMaxBlockN;
 }
 
 // choose_plan walks ~250 candidates (2-3 microseconds of host time, as much as the launch itself
@@ -544,9 +560,12 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   Plan plan = choose_plan_cached(st, g.m, g.n, g.k + (dual ? g.k2 : 0), g.batch, st->num_sms,
                                  st->max_clusters, a_mn, b_mn, pair_mode,
                                  ck_allowed ? st->ck_slots : nullptr, st->ck_slots_half);
-  if (!tune.no_wide)
-    widen_pair_tile(&plan, g.m, g.n, g.k, g.batch, st->max_clusters,
-                    g.bias != nullptr || g.act != 0 || backward);
+  if (!dual && !gather)
+    refine_large_plan(&plan, g.m, g.n, g.k, g.batch, st->num_sms, st->max_clusters, a_mn, b_mn, pair_mode,
+                      g.bias != nullptr || g.act != 0 || backward, !tune.no_wide);
+  else if (gather && !dual)        // tiles leave for the peers as they finish: same choice, never a K split
+    refine_large_plan(&plan, g.m, g.n, g.k, g.batch, st->num_sms, st->max_clusters, a_mn, b_mn, pair_mode,
+                      g.bias != nullptr || g.act != 0, !tune.no_wide);
   if (pol.block_n > 0) plan.block_n = pol.block_n;
   if (!plan.pair && plan.block_n > fnn::kMaxBlockN) plan.block_n = fnn::kMaxBlockN;
   if (pol.split_k > 0) { plan.split_k = pol.split_k; plan.cluster_k = false; }
@@ -1615,7 +1634,7 @@ extern "C" int fastnn_b200_plan_query(int layout, int m, int n, int k, int batch
   const bool a_mn = layout == FASTNN_B200_TN && (m % 32) != 0;
   const bool b_mn = layout != FASTNN_B200_NT && (n % 32) != 0;
   Plan plan = choose_plan(m, n, k, batch, num_sms, max_clusters, a_mn, b_mn, 0, slots, slots_half);
-  if (!tunables().no_wide) widen_pair_tile(&plan, m, n, k, batch, max_clusters, false);
+  refine_large_plan(&plan, m, n, k, batch, num_sms, max_clusters, a_mn, b_mn, 0, false, !tunables().no_wide);
   if (block_n) *block_n = plan.block_n;
   if (split_k) *split_k = plan.split_k;
   if (cta_pair) *cta_pair = plan.pair ? 1 : 0;

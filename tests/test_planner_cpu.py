@@ -18,8 +18,12 @@ def test_large_square_gemms_take_cta_pairs_with_the_widest_tile(plan):
     for shape in ((NN, 32768, 16384, 4096), (NT, 32768, 4096, 16384), (TN, 4096, 16384, 32768)):
         p = plan(*shape)
         assert p["cta_pair"] and p["block_n"] == 512 and p["split_k"] == 1
-    # the 256 x 512 tile only where it fills the machine about as well as 256 x 256 tiles do
+    # the 256 x 512 tile only where its waves take less time than those of 256 x 256 tiles
     assert plan(NN, 5120, 4096, 4096)["block_n"] == 256
+    assert plan(NN, 4096, 8192, 8192) == {"block_n": 256, "split_k": 1, "cta_pair": True, "cluster_k": False}
+    # the row shards of the 8192-row problem over 8 and 4 GPUs: one and two waves of wide tiles
+    for rows in (1024, 2048):
+        assert plan(NN, rows, 8192, 8192) == {"block_n": 512, "split_k": 1, "cta_pair": True, "cluster_k": False}
 
 
 def test_transformer_block_forward_shapes_are_not_split(plan):
@@ -53,14 +57,17 @@ def test_batched_attention_shapes(plan):
 
 @pytest.mark.parametrize("layout", [NN, NT, TN])
 def test_every_plan_is_launchable(plan, layout):
-    """Sweep: tile widths are multiples of 32 up to 256 (64 for pairs), every K slice has at least
-    one 32-deep k-block, clusters stay within the sizes the kernel reduces over."""
+    """Sweep: tile widths are multiples of 32 up to 256 (64 for pairs; 512 only for pairs, only with
+    the whole K range per tile and a deep K), every K slice has at least one 32-deep k-block,
+    clusters stay within the sizes the kernel reduces over."""
     for m in (1, 100, 128, 500, 4096):
         for n in (1, 32, 100, 260, 4096):
             for k in (1, 31, 64, 1000, 20000):
                 for batch in (1, 7):
                     p = plan(layout, m, n, k, batch)
-                    assert 32 <= p["block_n"] <= 256 and p["block_n"] % 32 == 0
+                    assert 32 <= p["block_n"] <= 512 and p["block_n"] % 32 == 0
+                    if p["block_n"] > 256:
+                        assert p["block_n"] == 512 and p["cta_pair"] and p["split_k"] == 1 and k >= 4096
                     if p["cta_pair"]:
                         assert p["block_n"] % 64 == 0 and m > 128
                     assert 1 <= p["split_k"] <= max(1, -(-k // 32))
