@@ -37,6 +37,12 @@ struct ConvParams {
                        // tap bit (high word), 0}; all zero for k >= ci*kh*kw (conv_ktab_kernel)
   const float* bias;   // [co] or null
   float* out;
+  // Where output position (oy, ox) of image n, channel c lands:
+  //   out + ((n * co + c) * dst_h + dst_y0 + oy * dst_sy) * dst_w + dst_x0 + ox * dst_sx
+  // The convolution itself writes a dense [oh, ow] plane (dst_h = oh, dst_w = ow, strides 1,
+  // offsets 0); a phase of a strided input gradient writes every dst_sy-th row and dst_sx-th column
+  // of the full gradient plane.
+  int dst_h, dst_w, dst_y0, dst_x0, dst_sy, dst_sx;
   int act;             // 0 none, 1 ReLU
   unsigned int* status;
   long long spin_budget;
@@ -200,8 +206,11 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int n0 = tile_n(u) * p.block_n;
       const bool row_ok = pos < p.positions;
       const long long img = row_ok ? pos / plane : 0;
-      const long long rem = row_ok ? pos - img * plane : 0;
-      float* obase = p.out + (img * p.co) * plane + rem;          // + channel * plane
+      const int rem = row_ok ? static_cast<int>(pos - img * plane) : 0;
+      const int e_oy = rem / p.ow, e_ox = rem - e_oy * p.ow;
+      const long long dplane = static_cast<long long>(p.dst_h) * p.dst_w;           // channel stride
+      float* obase = p.out + (img * p.co) * dplane +
+                     static_cast<long long>(p.dst_y0 + e_oy * p.dst_sy) * p.dst_w + p.dst_x0 + e_ox * p.dst_sx;
       ok = conv_wait(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -225,7 +234,7 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
           if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) obase[(co0 + j) * plane] = __uint_as_float(r[j]);
+            for (int j = 0; j < 32; ++j) obase[(co0 + j) * dplane] = __uint_as_float(r[j]);
           }
         } else {
 #pragma unroll
@@ -234,7 +243,7 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
               float v = __uint_as_float(r[j]);
               if (p.bias != nullptr) v += __ldg(p.bias + co0 + j);
               if (p.act == kActRelu) v = fmaxf(v, 0.0f);
-              obase[(co0 + j) * plane] = v;
+              obase[(co0 + j) * dplane] = v;
             }
           }
         }
@@ -394,6 +403,30 @@ flip_weights_kernel(const float* __restrict__ w, float* __restrict__ wp, int ic,
       const int r = kk - i * khw;
       const int a = r / kw, b = r - a * kw;
       v = w[((static_cast<long long>(i) * oc + o) * kh + (kh - 1 - a)) * kw + (kw - 1 - b)];
+    }
+    wp[e] = v;
+  }
+}
+
+// The same for one phase (ry, rx) of a strided input gradient: only the taps ki = ry + sh * t,
+// kj = rx + sw * u reach the input rows iy with (iy + pad_h) % sh == ry (likewise columns), so the
+// phase is a stride-1 convolution of the output gradient with the sub-kernel [ty, tx], reversed:
+// wp[oc][(ic*ty + a)*tx + b] = w[ic][oc][ry + sh*(ty-1-a)][rx + sw*(tx-1-b)], zero fill past k.
+__global__ void __launch_bounds__(256)
+flip_weights_phase_kernel(const float* __restrict__ w, float* __restrict__ wp, int ic, int oc, int kh, int kw,
+                          int ry, int rx, int sh, int sw, int ty, int tx, int k_pad) {
+  const int tt = ty * tx;
+  const int k = ic * tt;
+  const long long total = static_cast<long long>(oc) * k_pad;
+  for (long long e = blockIdx.x * 256ll + threadIdx.x; e < total; e += 256ll * gridDim.x) {
+    const int o = static_cast<int>(e / k_pad);
+    const int kk = static_cast<int>(e - static_cast<long long>(o) * k_pad);
+    float v = 0.0f;
+    if (kk < k) {
+      const int i = kk / tt;
+      const int r = kk - i * tt;
+      const int a = r / tx, b = r - a * tx;
+      v = w[((static_cast<long long>(i) * oc + o) * kh + (ry + sh * (ty - 1 - a))) * kw + (rx + sw * (tx - 1 - b))];
     }
     wp[e] = v;
   }

@@ -19,6 +19,7 @@
 #include "gemm_tcgen05_pair.cuh"
 #include "attention_tcgen05.cuh"
 #include "conv_tcgen05.cuh"
+#include "conv_wgrad_tcgen05.cuh"
 
 namespace {
 
@@ -962,6 +963,8 @@ extern "C" int fastnn_cuda_init(int device_id) {
                                    static_cast<int>(kMaxDynSmem)));
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::attention_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
+  FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_wgrad_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kMaxDynSmem)));
   st.num_sms = prop.multiProcessorCount;
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::gemm_tf32_clusterk_kernel,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1199,71 +1202,58 @@ extern "C" int fastnn_b200_rnn_gates_forward(const float* x_t, long long ld_x, c
   return dual_dispatch(g);
 }
 
-// The implicit-GEMM convolution.  flip_transpose = false: `weight` is [out, in, kh, kw].
-// flip_transpose = true: `weight` is [in, out, kh, kw] and is used with both kernel axes
-// reversed -- the form in which the gradient with respect to the input of a stride-1
-// convolution is itself a convolution of the output gradient.
-static int conv_forward_impl(const float* input, const float* weight, const float* bias, float* output,
-                             int batch_size, int in_channels, int out_channels, int input_h,
-                             int input_w, int kernel_h, int kernel_w, int stride_h, int stride_w,
-                             int pad_h, int pad_w, int act, void* stream, bool flip_transpose) {
-  if (batch_size < 0 || in_channels < 1 || out_channels < 1 || input_h < 1 || input_w < 1 ||
-      kernel_h < 1 || kernel_w < 1 || stride_h < 1 || stride_w < 1 || pad_h < 0 || pad_w < 0 ||
-      act < 0 || act > 1)
-    return -1;
-  if (input_h + 2 * pad_h < kernel_h || input_w + 2 * pad_w < kernel_w) return -1;
-  if (batch_size == 0) return 0;
-  if (input == nullptr || weight == nullptr || output == nullptr) return -1;
-  const int oh = (input_h + 2 * pad_h - kernel_h) / stride_h + 1;      // cuda/kernels.cu:903-904
-  const int ow = (input_w + 2 * pad_w - kernel_w) / stride_w + 1;
-  const long long k_ll = 1ll * in_channels * kernel_h * kernel_w;
-  const long long positions = 1ll * batch_size * oh * ow;
-  if (k_ll > (1ll << 30) || positions > (1ll << 40)) return -1;
-  const int k = static_cast<int>(k_ll);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+// One launch of the implicit-GEMM convolution kernel (plus its small table / weight pre-passes).
+struct ConvCall {
+  const float* input;            // [batch, ci, h, w]
+  const float* weight;           // as stored; how it is read depends on wmode
+  const float* bias;
+  float* output;
+  int batch, ci, co, h, w;       // input channels and size, output channels, of THIS launch
+  int kh, kw;                    // kernel this launch applies
+  int sh, sw, ph, pw;            // stride and padding (padding may be negative for a gradient phase)
+  int oh, ow;                    // output positions per image
+  int dst_h, dst_w, dst_y0, dst_x0, dst_sy, dst_sx;    // where they land (ConvParams)
+  int act;
+  // 0: weight is [co, ci, kh, kw], used as stored.  1: weight is [ci, co, kh, kw], used with both
+  // kernel axes reversed (input gradient of a stride-1 convolution).  2: weight is
+  // [ci, co, full_kh, full_kw]; this launch applies the reversed sub-kernel of the taps
+  // (ry + wsh * t, rx + wsw * u) -- one phase of a strided input gradient.
+  int wmode;
+  int full_kh, full_kw, ry, rx, wsh, wsw;
+};
 
-  DeviceState* st = current_state();
-  if (st == nullptr) return -1;
-  // The gather packs (offset inside the image, tap index) into 32 bits and keeps a 64-bit tap
-  // mask.  Kernels of 64 taps or more and images of 2^25 elements or more go to the direct kernel
-  // (FP32 FMA, one thread per output element): rare shapes, served rather than refused.
-  if (1ll * kernel_h * kernel_w > 63 || 1ll * in_channels * input_h * input_w >= (1ll << 25)) {
-    const long long total = positions * out_channels;
-    long long blocks = (total + 255) / 256;
-    if (blocks > 64ll * st->num_sms) blocks = 64ll * st->num_sms;
-    fnn::conv2d_direct_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-        input, weight, bias, output, batch_size, in_channels, out_channels, input_h, input_w, kernel_h,
-        kernel_w, stride_h, stride_w, pad_h, pad_w, oh, ow, act, flip_transpose ? 1 : 0);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    FNN_CUDA_OK(cudaGetLastError());
-    t_last = LastCall{7, 0, 1, static_cast<int>(blocks)};
-    return 0;
-  }
+static int conv_launch(DeviceState* st, const ConvCall& c, cudaStream_t s) {
+  const long long k_ll = 1ll * c.ci * c.kh * c.kw;
+  const long long positions = 1ll * c.batch * c.oh * c.ow;
+  if (k_ll > (1ll << 30) || positions > (1ll << 40) || positions < 1) return -1;
+  const int k = static_cast<int>(k_ll);
   // weights are [co, k] row-major: K-major for the tensor core as they stand.  TMA needs 16-byte
   // rows; otherwise (k = 27 for a 3x3 kernel on RGB) a zero-padded copy goes to the workspace.
-  const float* wsrc = weight;
+  const float* wsrc = c.weight;
   long long w_ld = k;
   const int num_kb = ceil_div(k, fnn::kBlockK);
-  const bool copy_w = flip_transpose || (k & 3) != 0 || !aligned16(weight);
+  const bool copy_w = c.wmode != 0 || (k & 3) != 0 || !aligned16(c.weight);
   const int k_pad = num_kb * fnn::kBlockK;
   // workspace of this stream: [the gather's table, one int4 per k] [padded / flipped weights]
   const size_t tab_bytes = sizeof(int4) * static_cast<size_t>(k_pad);
-  const size_t w_bytes = copy_w ? sizeof(float) * static_cast<size_t>(out_channels) * k_pad : 0;
+  const size_t w_bytes = copy_w ? sizeof(float) * static_cast<size_t>(c.co) * k_pad : 0;
   float* ws_ptr = nullptr;
   if (workspace_reserve(st, st->workspaces, s, tab_bytes + w_bytes, &ws_ptr) != 0) return -1;
   int4* ktab = reinterpret_cast<int4*>(ws_ptr);
-  fnn::conv_ktab_kernel<<<ceil_div(k_pad, 256), 256, 0, s>>>(ktab, k_pad, k, kernel_h, kernel_w, input_h,
-                                                            input_w);
+  fnn::conv_ktab_kernel<<<ceil_div(k_pad, 256), 256, 0, s>>>(ktab, k_pad, k, c.kh, c.kw, c.h, c.w);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   if (copy_w) {
     float* wdst = reinterpret_cast<float*>(reinterpret_cast<char*>(ws_ptr) + tab_bytes);
-    long long blocks = (1ll * out_channels * k_pad + 255) / 256;
+    long long blocks = (1ll * c.co * k_pad + 255) / 256;
     if (blocks > 1024) blocks = 1024;
-    if (flip_transpose)
+    if (c.wmode == 1)
       fnn::flip_weights_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-          weight, wdst, in_channels, out_channels, kernel_h, kernel_w, k_pad);
+          c.weight, wdst, c.ci, c.co, c.kh, c.kw, k_pad);
+    else if (c.wmode == 2)
+      fnn::flip_weights_phase_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+          c.weight, wdst, c.ci, c.co, c.full_kh, c.full_kw, c.ry, c.rx, c.wsh, c.wsw, c.kh, c.kw, k_pad);
     else
-      fnn::pad_weights_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(weight, wdst, out_channels, k, k_pad);
+      fnn::pad_weights_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(c.weight, wdst, c.co, k, k_pad);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     wsrc = wdst;
     w_ld = k_pad;
@@ -1271,23 +1261,25 @@ static int conv_forward_impl(const float* input, const float* weight, const floa
   FNN_CUDA_OK(cudaGetLastError());
   fnn::ConvParams p;
   std::memset(&p, 0, sizeof(p));
-  p.batch = batch_size; p.ci = in_channels; p.co = out_channels; p.h = input_h; p.w = input_w;
-  p.kh = kernel_h; p.kw = kernel_w; p.sh = stride_h; p.sw = stride_w; p.ph = pad_h; p.pw = pad_w;
-  p.oh = oh; p.ow = ow; p.k = k; p.num_kb = ceil_div(k, fnn::kBlockK); p.positions = positions;
-  p.block_n = out_channels >= fnn::kMaxBlockN ? fnn::kMaxBlockN : ceil_div(out_channels, 32) * 32;
+  p.batch = c.batch; p.ci = c.ci; p.co = c.co; p.h = c.h; p.w = c.w;
+  p.kh = c.kh; p.kw = c.kw; p.sh = c.sh; p.sw = c.sw; p.ph = c.ph; p.pw = c.pw;
+  p.oh = c.oh; p.ow = c.ow; p.k = k; p.num_kb = num_kb; p.positions = positions;
+  p.dst_h = c.dst_h; p.dst_w = c.dst_w; p.dst_y0 = c.dst_y0; p.dst_x0 = c.dst_x0;
+  p.dst_sy = c.dst_sy; p.dst_sx = c.dst_sx;
+  p.block_n = c.co >= fnn::kMaxBlockN ? fnn::kMaxBlockN : ceil_div(c.co, 32) * 32;
   const long long tiles_p = (positions + fnn::kBlockM - 1) / fnn::kBlockM;
-  p.tiles_n = ceil_div(out_channels, p.block_n);
+  p.tiles_n = ceil_div(c.co, p.block_n);
   if (tiles_p * p.tiles_n > 0x7fffffffll) return -1;
   p.tiles_p = static_cast<int>(tiles_p);
   p.total_units = static_cast<int>(tiles_p * p.tiles_n);
   const size_t stage = fnn::kStageABytes + static_cast<size_t>(p.block_n) * fnn::kBlockK * 4;
   int stages = static_cast<int>((kMaxDynSmem - 1024 - fnn::kBarrierBytes) / stage);
   p.num_stages = stages > fnn::kMaxStages ? fnn::kMaxStages : stages;
-  p.x = input; p.ktab = ktab; p.bias = bias; p.out = output; p.act = act;
+  p.x = c.input; p.ktab = ktab; p.bias = c.bias; p.out = c.output; p.act = c.act;
   p.status = st->status; p.spin_budget = st->spin_budget;
   CUtensorMap tmW;
-  if (!encode_map(&tmW, wsrc, static_cast<uint64_t>(w_ld == k ? k : w_ld), out_channels, 1, w_ld * 4ull,
-                  w_ld * 4ull * out_channels, fnn::kBlockK, p.block_n))
+  if (!encode_map(&tmW, wsrc, static_cast<uint64_t>(w_ld == k ? k : w_ld), c.co, 1, w_ld * 4ull,
+                  w_ld * 4ull * c.co, fnn::kBlockK, p.block_n))
     return -1;
   const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
   cudaLaunchConfig_t cfg;
@@ -1307,6 +1299,57 @@ static int conv_forward_impl(const float* input, const float* weight, const floa
   return 0;
 }
 
+// What the implicit-GEMM gather can encode: (offset inside the image, tap index) in 32 bits and a
+// 64-bit tap mask.
+static bool conv_gather_covers(int channels, int h, int w, int kh, int kw) {
+  return 1ll * kh * kw <= 63 && 1ll * channels * h * w < (1ll << 25);
+}
+
+// The convolution.  flip_transpose = false: `weight` is [out, in, kh, kw].  flip_transpose = true:
+// `weight` is [in, out, kh, kw] and is used with both kernel axes reversed -- the form in which
+// the gradient with respect to the input of a stride-1 convolution is itself a convolution of the
+// output gradient.
+static int conv_forward_impl(const float* input, const float* weight, const float* bias, float* output,
+                             int batch_size, int in_channels, int out_channels, int input_h,
+                             int input_w, int kernel_h, int kernel_w, int stride_h, int stride_w,
+                             int pad_h, int pad_w, int act, void* stream, bool flip_transpose) {
+  if (batch_size < 0 || in_channels < 1 || out_channels < 1 || input_h < 1 || input_w < 1 ||
+      kernel_h < 1 || kernel_w < 1 || stride_h < 1 || stride_w < 1 || pad_h < 0 || pad_w < 0 ||
+      act < 0 || act > 1)
+    return -1;
+  if (input_h + 2 * pad_h < kernel_h || input_w + 2 * pad_w < kernel_w) return -1;
+  if (batch_size == 0) return 0;
+  if (input == nullptr || weight == nullptr || output == nullptr) return -1;
+  const int oh = (input_h + 2 * pad_h - kernel_h) / stride_h + 1;      // cuda/kernels.cu:903-904
+  const int ow = (input_w + 2 * pad_w - kernel_w) / stride_w + 1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  DeviceState* st = current_state();
+  if (st == nullptr) return -1;
+  // Kernels of 64 taps or more and images of 2^25 elements or more go to the direct kernel (FP32
+  // FMA, one thread per output element): rare shapes, served rather than refused.
+  if (!conv_gather_covers(in_channels, input_h, input_w, kernel_h, kernel_w)) {
+    const long long total = 1ll * batch_size * oh * ow * out_channels;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 64ll * st->num_sms) blocks = 64ll * st->num_sms;
+    fnn::conv2d_direct_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        input, weight, bias, output, batch_size, in_channels, out_channels, input_h, input_w, kernel_h,
+        kernel_w, stride_h, stride_w, pad_h, pad_w, oh, ow, act, flip_transpose ? 1 : 0);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    FNN_CUDA_OK(cudaGetLastError());
+    t_last = LastCall{7, 0, 1, static_cast<int>(blocks)};
+    return 0;
+  }
+  ConvCall c;
+  std::memset(&c, 0, sizeof(c));
+  c.input = input; c.weight = weight; c.bias = bias; c.output = output;
+  c.batch = batch_size; c.ci = in_channels; c.co = out_channels; c.h = input_h; c.w = input_w;
+  c.kh = kernel_h; c.kw = kernel_w; c.sh = stride_h; c.sw = stride_w; c.ph = pad_h; c.pw = pad_w;
+  c.oh = oh; c.ow = ow;
+  c.dst_h = oh; c.dst_w = ow; c.dst_y0 = 0; c.dst_x0 = 0; c.dst_sy = 1; c.dst_sx = 1;
+  c.act = act; c.wmode = flip_transpose ? 1 : 0;
+  return conv_launch(st, c, s);
+}
+
 extern "C" int fastnn_b200_conv2d_forward(const float* input, const float* weight, const float* bias,
                                           float* output, int batch_size, int in_channels,
                                           int out_channels, int input_h, int input_w, int kernel_h,
@@ -1320,10 +1363,15 @@ extern "C" int fastnn_b200_conv2d_forward(const float* input, const float* weigh
 // grad_input[n, ci, iy, ix] = sum over (co, ki, kj) of grad_output[n, co, iy + ph - ki, ix + pw - kj]
 // * weight[co, ci, ki, kj] for a stride-1 convolution: with ki' = kh-1-ki this is the forward
 // kernel run on grad_output (co channels in, ci out) with the kernel reversed and padding
-// kh-1-ph.  Any other stride, and padding beyond kernel - 1, take the gather-form kernel: every
-// grad_input element adds up the (co, ki, kj) terms whose output position (iy + ph - ki) / stride
-// exists -- what FastNN's GEMM + col2im computes (cuda/kernels.cu:862-893, 949-987), without the
-// column matrix and without atomics.
+// kh-1-ph.
+// Stride (sh, sw): input row iy receives only the taps ki = ry + sh * t with ry = (iy + ph) % sh,
+// from output row (iy + ph - ki) / sh.  The rows of one residue ry (and columns of one rx) form a
+// PHASE, and a phase is again a stride-1 convolution of grad_output -- with the reversed sub-kernel
+// of those taps -- whose results land on every sh-th row and sw-th column of grad_input.  So the
+// gradient is sh * sw launches of the same implicit-GEMM kernel, no multiplication by a zero, no
+// column matrix, no atomics (what FastNN's GEMM + col2im computes, cuda/kernels.cu:862-893,
+// 949-987).  Phases no tap reaches (stride larger than the kernel) are zeros.
+// Shapes the gather cannot encode fall back to the gather-form FP32 kernel.
 extern "C" int fastnn_b200_conv2d_backward_data(const float* grad_output, const float* weight,
                                                 float* grad_input, int batch_size, int in_channels,
                                                 int out_channels, int input_h, int input_w,
@@ -1347,6 +1395,38 @@ extern "C" int fastnn_b200_conv2d_backward_data(const float* grad_output, const 
   if (st == nullptr) return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long total = 1ll * batch_size * in_channels * input_h * input_w;
+  if (conv_gather_covers(out_channels, output_h, output_w, kernel_h, kernel_w) && t_policy.policy != 1) {
+    if (stride_h > kernel_h || stride_w > kernel_w)        // some phases get no tap at all
+      FNN_CUDA_OK(cudaMemsetAsync(grad_input, 0, sizeof(float) * total, s));
+    for (int ry = 0; ry < stride_h && ry < kernel_h; ++ry) {
+      const int ty = (kernel_h - ry + stride_h - 1) / stride_h;             // taps ki = ry, ry + sh, ...
+      const int iy_first = ((ry - pad_h) % stride_h + stride_h) % stride_h; // first input row of the phase
+      if (iy_first >= input_h) continue;
+      const int rows = (input_h - 1 - iy_first) / stride_h + 1;
+      const int a_min = (iy_first + pad_h - ry) / stride_h;                 // its (iy + ph - ry) / sh
+      for (int rx = 0; rx < stride_w && rx < kernel_w; ++rx) {
+        const int tx = (kernel_w - rx + stride_w - 1) / stride_w;
+        const int ix_first = ((rx - pad_w) % stride_w + stride_w) % stride_w;
+        if (ix_first >= input_w) continue;
+        const int cols = (input_w - 1 - ix_first) / stride_w + 1;
+        const int b_min = (ix_first + pad_w - rx) / stride_w;
+        ConvCall c;
+        std::memset(&c, 0, sizeof(c));
+        c.input = grad_output; c.weight = weight; c.bias = nullptr; c.output = grad_input;
+        c.batch = batch_size; c.ci = out_channels; c.co = in_channels; c.h = output_h; c.w = output_w;
+        c.kh = ty; c.kw = tx; c.sh = 1; c.sw = 1;
+        c.ph = ty - 1 - a_min; c.pw = tx - 1 - b_min;       // may be negative: the gather only tests bounds
+        c.oh = rows; c.ow = cols;
+        c.dst_h = input_h; c.dst_w = input_w; c.dst_y0 = iy_first; c.dst_x0 = ix_first;
+        c.dst_sy = stride_h; c.dst_sx = stride_w;
+        c.act = 0; c.wmode = 2;
+        c.full_kh = kernel_h; c.full_kw = kernel_w; c.ry = ry; c.rx = rx; c.wsh = stride_h; c.wsw = stride_w;
+        const int rc = conv_launch(st, c, s);
+        if (rc != 0) return rc;
+      }
+    }
+    return 0;
+  }
   long long blocks = (total + 255) / 256;
   if (blocks > 64ll * st->num_sms) blocks = 64ll * st->num_sms;
   fnn::conv2d_backward_data_direct_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
@@ -1371,8 +1451,86 @@ extern "C" int fastnn_cuda_conv2d_backward_data(const float* grad_output, const 
 }
 
 // grad_weight[co, k] = sum over images n and positions p of grad_output[n, co, p] * col[n, k, p].
-// Explicit: one im2col launch for all images (tap-major, positions contiguous), one batched NT
-// GEMM grad_output[n] . col[n]^T into per-image partials -- both operands contiguous along the
+// Implicit GEMM (conv_wgrad_tcgen05.cuh): grad_output tiles by TMA, the column values gathered
+// straight into the B stages, the contraction over all positions of all images cut into slices so
+// that every SM has a unit; slices are added in order by the split-K reduce kernel.  Needs
+// out_h * out_w to be a multiple of 4 (16-byte rows of grad_output for TMA).
+static int conv_wgrad_implicit(DeviceState* st, const float* input, const float* grad_output, float* grad_weight,
+                               int batch_size, int in_channels, int out_channels, int input_h, int input_w,
+                               int output_h, int output_w, int kernel_h, int kernel_w, int stride_h,
+                               int stride_w, int pad_h, int pad_w, int k, cudaStream_t s) {
+  fnn::WgradParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.batch = batch_size; p.ci = in_channels; p.co = out_channels; p.h = input_h; p.w = input_w;
+  p.kh = kernel_h; p.kw = kernel_w; p.sh = stride_h; p.sw = stride_w; p.ph = pad_h; p.pw = pad_w;
+  p.oh = output_h; p.ow = output_w; p.k = k; p.plane = output_h * output_w;
+  p.kb_per_image = ceil_div(p.plane, fnn::kBlockK);
+  p.total_kb = 1ll * batch_size * p.kb_per_image;
+  const int n32 = ceil_div(k, 32) * 32;
+  p.tiles_n = ceil_div(n32, fnn::kMaxBlockN);
+  p.block_n = ceil_div(ceil_div(n32, p.tiles_n), 32) * 32;
+  p.tiles_m = ceil_div(out_channels, fnn::kBlockM);
+  // slices: one unit per SM when the tiles alone are fewer, at least eight k-blocks each
+  long long slices = st->num_sms / (1ll * p.tiles_m * p.tiles_n);
+  if (slices > p.total_kb / 8) slices = p.total_kb / 8;
+  if (slices < 1) slices = 1;
+  p.kb_per_slice = (p.total_kb + slices - 1) / slices;
+  p.slices = static_cast<int>((p.total_kb + p.kb_per_slice - 1) / p.kb_per_slice);   // none empty
+  const long long units = 1ll * p.tiles_m * p.tiles_n * p.slices;
+  if (units > 0x7fffffffll) return -1;
+  p.total_units = static_cast<int>(units);
+  const size_t stage = fnn::kStageABytes + static_cast<size_t>(p.block_n) * fnn::kBlockK * 4;
+  const int stages = static_cast<int>((kMaxDynSmem - 1024 - fnn::kBarrierBytes) / stage);
+  p.num_stages = stages > fnn::kMaxStages ? fnn::kMaxStages : stages;
+  // this stream's scratch: [tap table] [partial sums of the slices]
+  const size_t tab_entries = static_cast<size_t>(p.tiles_n) * p.block_n;
+  const size_t tab_bytes = sizeof(int4) * tab_entries;
+  const size_t part_floats = p.slices > 1 ? static_cast<size_t>(p.slices) * out_channels * k : 0;
+  float* ws = nullptr;
+  if (workspace_reserve(st, st->conv_ws, s, tab_bytes + sizeof(float) * part_floats, &ws) != 0) return -1;
+  int4* ktab = reinterpret_cast<int4*>(ws);
+  float* partials = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + tab_bytes);
+  fnn::wgrad_ktab_kernel<<<ceil_div(static_cast<int>(tab_entries), 256), 256, 0, s>>>(
+      ktab, static_cast<int>(tab_entries), k, kernel_h, kernel_w, input_h, input_w);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  FNN_CUDA_OK(cudaGetLastError());
+  p.x = input; p.ktab = ktab; p.out = p.slices > 1 ? partials : grad_weight;
+  p.status = st->status; p.spin_budget = st->spin_budget;
+  CUtensorMap tmG;
+  const uint64_t plane = static_cast<uint64_t>(p.plane);
+  if (!encode_map(&tmG, grad_output, plane, out_channels, batch_size, plane * 4ull,
+                  plane * 4ull * out_channels, fnn::kBlockK, fnn::kBlockM))
+    return -1;
+  const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(fnn::kWgradThreads, 1, 1);
+  cfg.dynamicSmemBytes = fnn::conv_smem_bytes(p.block_n, p.num_stages);
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::conv2d_wgrad_tf32_kernel, tmG, p));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (p.slices > 1) {
+    const long long total = 1ll * out_channels * k;
+    long long rblocks = (total + 255) / 256;
+    if (rblocks > 8ll * st->num_sms) rblocks = 8ll * st->num_sms;
+    fnn::splitk_reduce_kernel<<<static_cast<unsigned>(rblocks), 256, 0, s>>>(
+        partials, grad_weight, nullptr, out_channels, k, 1, p.slices, k, total, 1.0f, 0.0f, 0);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
+  FNN_CUDA_OK(cudaGetLastError());
+  t_last = LastCall{5, p.block_n, p.slices, grid};
+  return 0;
+}
+
+// The explicit form, kept for outputs whose plane is not a multiple of four positions: one
+// im2col launch for all images (tap-major, positions contiguous), one batched NT GEMM
+// grad_output[n] . col[n]^T into per-image partials -- both operands contiguous along the
 // contraction -- and one fixed-order sum over the images.
 extern "C" int fastnn_b200_conv2d_backward_weight(const float* input, const float* grad_output,
                                                   float* grad_weight, int batch_size, int in_channels,
@@ -1398,6 +1556,15 @@ extern "C" int fastnn_b200_conv2d_backward_weight(const float* input, const floa
     return 0;
   }
   if (input == nullptr || grad_output == nullptr) return -1;
+  {
+    DeviceState* st0 = current_state();
+    if (st0 == nullptr) return -1;
+    if ((plane & 3) == 0 && aligned16(grad_output) && 1ll * in_channels * input_h * input_w < (1ll << 30) &&
+        t_policy.policy != 1)
+      return conv_wgrad_implicit(st0, input, grad_output, grad_weight, batch_size, in_channels, out_channels,
+                                 input_h, input_w, output_h, output_w, kernel_h, kernel_w, stride_h, stride_w,
+                                 pad_h, pad_w, k, s);
+  }
   const int ldp = ceil_div(static_cast<int>(plane), 4) * 4;      // 16-byte rows for TMA
   const size_t col_floats = static_cast<size_t>(batch_size) * k * ldp;
   const size_t part_floats = static_cast<size_t>(batch_size) * out_channels * k;

@@ -170,9 +170,12 @@ FASTNN_B200_API int fastnn_b200_conv2d_forward(const float* input, const float* 
  * grad_output with the kernel reversed and channels swapped; for every other stride and padding a
  * gather-form kernel in which each grad_input element adds its (co, ki, kj) terms (the sums
  * FastNN's GEMM + col2im forms, cuda/kernels.cu:862-893) -- no column matrix, no atomics.
- * backward_weight is explicit in this version: one im2col launch for all images (tap-major, as
- * FastNN's kernel_im2col lays it out), one batched NT GEMM into per-image partials, one
- * fixed-order sum (deterministic); any stride. */
+ * backward_weight, any stride: an implicit GEMM over all positions of all images -- grad_output
+ * tiles by TMA, the input values under every kernel tap gathered straight into the tensor core's
+ * operand stages, no column matrix -- cut into slices that are added in a fixed order
+ * (deterministic).  Outputs whose out_h * out_w is not a multiple of 4 take the explicit form: one
+ * im2col launch for all images (tap-major, as FastNN's kernel_im2col lays it out), one batched NT
+ * GEMM into per-image partials, one fixed-order sum. */
 FASTNN_B200_API int fastnn_cuda_conv2d_backward_data(const float* grad_output, const float* weight,
                                                      float* grad_input, int batch_size, int in_channels,
                                                      int out_channels, int input_h, int input_w,
