@@ -232,12 +232,21 @@ conv2d_wgrad_tf32_kernel(const __grid_constant__ CUtensorMap tmG, const __grid_c
     }
   } else {
     // ---------------------------------------------------------------- gather ---
+    // The gather is bound by instruction issue, so what can be hoisted is: the warp's table entries
+    // sit in shared memory (one broadcast read with an immediate offset per element), rows go in
+    // groups of four with nothing but the group test between them, and a row's shared-memory
+    // address is a per-warp constant plus 2 KiB per step (row r = g + 16 i has r & 7 = g & 7, so
+    // the swizzle term does not change from row to row).
     ptx::grid_dep_wait();
     const int g = warp - kWgradGatherWarp0;
-    const int rows_per_warp = p.block_n / kWgradGatherWarps;         // block_n is a multiple of 32
+    const int row_groups = p.block_n / (4 * kWgradGatherWarps);      // block_n is a multiple of 64
     const int hw = p.h * p.w;
     const int step_y = kBlockK / p.ow, step_x = kBlockK - step_y * p.ow;   // 32 positions further on
     const int lane_oy0 = lane / p.ow, lane_ox0 = lane - lane_oy0 * p.ow;
+    const uint32_t tab_s = bar_base + kBarrierBytes + static_cast<uint32_t>(g) * (kWgradMaxRowsPerWarp * 16u);
+    const uint32_t row_off = kStageABytes + static_cast<uint32_t>(g) * 128u +
+                             ((static_cast<uint32_t>(lane >> 2) ^ static_cast<uint32_t>(g & 7)) << 4) +
+                             (static_cast<uint32_t>(lane & 3) << 2);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -245,7 +254,16 @@ conv2d_wgrad_tf32_kernel(const __grid_constant__ CUtensorMap tmG, const __grid_c
       const int n0 = tile_n(u) * p.block_n;
       long long kb0, kb1;
       kb_range(u, kb0, kb1);
-      const int4* tab = p.ktab + n0 + g;                            // this warp's rows: g, g + 16, ...
+      if (kb0 >= kb1) continue;
+      // this warp's rows g, g + 16, ... of the tap table -> its slice of shared memory
+      __syncwarp();
+      if (lane < 4 * row_groups) {
+        const int4 t = __ldg(p.ktab + n0 + g + lane * kWgradGatherWarps);
+        asm volatile("st.shared.v4.s32 [%0], {%1, %2, %3, %4};" ::"r"(tab_s + lane * 16u), "r"(t.x), "r"(t.y),
+                     "r"(t.z), "r"(t.w)
+                     : "memory");
+      }
+      __syncwarp();
       float na[kWgradMaxRowsPerWarp], nb[kWgradMaxRowsPerWarp];
       // Cursor over the k-blocks the loads are issued for (one ahead of the one being written):
       // image, k-block inside it and this lane's output position, stepped without divisions.
@@ -256,17 +274,26 @@ conv2d_wgrad_tf32_kernel(const __grid_constant__ CUtensorMap tmG, const __grid_c
       // loads of one k-block: this lane's position under every tap row of this warp
       auto issue_loads = [&](float (&dst)[kWgradMaxRowsPerWarp]) {
         const int iy0 = c_oy * p.sh - p.ph, ix0 = c_ox * p.sw - p.pw;
-        const uint32_t pos_ok = c_pos < p.plane ? 1u : 0u;
+        // a position past the end of the image fails every row test
+        const unsigned hlim = c_pos < p.plane ? static_cast<unsigned>(p.h) : 0u;
         // never dereferenced for a tap outside the image
         const float* xp = p.x + static_cast<long long>(c_img) * p.ci * hw + iy0 * p.w + ix0;
 #pragma unroll
-        for (int i = 0; i < kWgradMaxRowsPerWarp; ++i) {
-          if (i < rows_per_warp) {              // warp-uniform
-            const int4 t = __ldg(tab + i * kWgradGatherWarps);
-            const uint32_t in = pos_ok & static_cast<uint32_t>(t.w) &
-                                (static_cast<unsigned>(iy0 + t.y) < static_cast<unsigned>(p.h) ? 1u : 0u) &
-                                (static_cast<unsigned>(ix0 + t.z) < static_cast<unsigned>(p.w) ? 1u : 0u);
-            dst[i] = ldg_if(xp + t.x, in);
+        for (int grp = 0; grp < kWgradMaxRowsPerWarp / 4; ++grp) {
+          if (grp < row_groups) {               // warp-uniform
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int i = grp * 4 + j;
+              int tx, ty, tz, tw;
+              asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(tx), "=r"(ty), "=r"(tz), "=r"(tw)
+                           : "r"(tab_s + i * 16u));
+              // tw = 1 for a real tap, 0 for the padding rows past k
+              const uint32_t in = (static_cast<unsigned>(iy0 + ty) < hlim ? 1u : 0u) &
+                                  (static_cast<unsigned>(ix0 + tz) < static_cast<unsigned>(p.w) ? 1u : 0u) &
+                                  static_cast<uint32_t>(tw);
+              dst[i] = ldg_if(xp + tx, in);
+            }
           }
         }
         // next k-block: 32 positions on, or the first positions of the next image
@@ -282,16 +309,18 @@ conv2d_wgrad_tf32_kernel(const __grid_constant__ CUtensorMap tmG, const __grid_c
         int okw = 1;
         if (lane == 0) okw = wgrad_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather) ? 1 : 0;
         if (__shfl_sync(0xffffffffu, okw, 0) == 0) return false;
-        // row r of the B stage: 32 floats, 16-byte chunk c at c ^ (r & 7); this lane's float is
-        // chunk lane / 4, word lane % 4
-        const uint32_t sb = smem_base + stage * stage_bytes + kStageABytes;
+        // row r = g + 16 i of the B stage: 32 floats, 16-byte chunk c at c ^ (r & 7); this lane's
+        // float is chunk lane / 4, word lane % 4
+        const uint32_t dst0 = smem_base + stage * stage_bytes + row_off;
 #pragma unroll
-        for (int i = 0; i < kWgradMaxRowsPerWarp; ++i) {
-          if (i < rows_per_warp) {
-            const uint32_t r = static_cast<uint32_t>(g + i * kWgradGatherWarps);
-            const uint32_t addr = sb + r * 128u + ((static_cast<uint32_t>(lane >> 2) ^ (r & 7u)) << 4) +
-                                  (static_cast<uint32_t>(lane & 3) << 2);
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(e[i]) : "memory");
+        for (int grp = 0; grp < kWgradMaxRowsPerWarp / 4; ++grp) {
+          if (grp < row_groups) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int i = grp * 4 + j;
+              asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst0 + i * (kWgradGatherWarps * 128u)), "f"(e[i])
+                           : "memory");
+            }
           }
         }
         ptx::fence_proxy_async_smem();               // generic writes -> visible to the tensor core
@@ -300,7 +329,6 @@ conv2d_wgrad_tf32_kernel(const __grid_constant__ CUtensorMap tmG, const __grid_c
         if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
         return true;
       };
-      if (kb0 >= kb1) continue;
       issue_loads(na);
       for (long long kb = kb0; kb < kb1; kb += 2) {
         if (kb + 1 < kb1) issue_loads(nb);
@@ -341,6 +369,12 @@ wgrad_ktab_kernel(int4* __restrict__ tab, int entries, int k, int kh, int kw, in
     }
     tab[e] = t;
   }
+}
+
+// Dynamic shared memory of the weight-gradient kernel: stages, barriers, the gather warps' table slices.
+constexpr int kWgradTableBytes = kWgradGatherWarps * kWgradMaxRowsPerWarp * 16;     // 4 KiB
+inline size_t wgrad_smem_bytes(int block_n, int num_stages) {
+  return conv_smem_bytes(block_n, num_stages) + kWgradTableBytes;
 }
 
 }  // namespace fnn

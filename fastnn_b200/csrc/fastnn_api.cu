@@ -1466,9 +1466,10 @@ static int conv_wgrad_implicit(DeviceState* st, const float* input, const float*
   p.oh = output_h; p.ow = output_w; p.k = k; p.plane = output_h * output_w;
   p.kb_per_image = ceil_div(p.plane, fnn::kBlockK);
   p.total_kb = 1ll * batch_size * p.kb_per_image;
-  const int n32 = ceil_div(k, 32) * 32;
-  p.tiles_n = ceil_div(n32, fnn::kMaxBlockN);
-  p.block_n = ceil_div(ceil_div(n32, p.tiles_n), 32) * 32;
+  // tap tiles: equal widths, multiples of 64 (the gather warps take rows in groups of four)
+  const int n64 = ceil_div(k, 64) * 64;
+  p.tiles_n = ceil_div(n64, fnn::kMaxBlockN);
+  p.block_n = ceil_div(ceil_div(n64, p.tiles_n), 64) * 64;
   p.tiles_m = ceil_div(out_channels, fnn::kBlockM);
   // slices: one unit per SM when the tiles alone are fewer, at least eight k-blocks each
   long long slices = st->num_sms / (1ll * p.tiles_m * p.tiles_n);
@@ -1480,7 +1481,7 @@ static int conv_wgrad_implicit(DeviceState* st, const float* input, const float*
   if (units > 0x7fffffffll) return -1;
   p.total_units = static_cast<int>(units);
   const size_t stage = fnn::kStageABytes + static_cast<size_t>(p.block_n) * fnn::kBlockK * 4;
-  const int stages = static_cast<int>((kMaxDynSmem - 1024 - fnn::kBarrierBytes) / stage);
+  const int stages = static_cast<int>((kMaxDynSmem - 1024 - fnn::kBarrierBytes - fnn::kWgradTableBytes) / stage);
   p.num_stages = stages > fnn::kMaxStages ? fnn::kMaxStages : stages;
   // this stream's scratch: [tap table] [partial sums of the slices]
   const size_t tab_entries = static_cast<size_t>(p.tiles_n) * p.block_n;
@@ -1506,7 +1507,7 @@ static int conv_wgrad_implicit(DeviceState* st, const float* input, const float*
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(fnn::kWgradThreads, 1, 1);
-  cfg.dynamicSmemBytes = fnn::conv_smem_bytes(p.block_n, p.num_stages);
+  cfg.dynamicSmemBytes = fnn::wgrad_smem_bytes(p.block_n, p.num_stages);
   cfg.stream = s;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1517,10 +1518,17 @@ static int conv_wgrad_implicit(DeviceState* st, const float* input, const float*
   g_launches.fetch_add(1, std::memory_order_relaxed);
   if (p.slices > 1) {
     const long long total = 1ll * out_channels * k;
-    long long rblocks = (total + 255) / 256;
+    const bool vec = (k & 3) == 0 && aligned16(grad_weight) && aligned16(partials);
+    long long rblocks = ((vec ? total / 4 : total) + 255) / 256;
     if (rblocks > 8ll * st->num_sms) rblocks = 8ll * st->num_sms;
-    fnn::splitk_reduce_kernel<<<static_cast<unsigned>(rblocks), 256, 0, s>>>(
-        partials, grad_weight, nullptr, out_channels, k, 1, p.slices, k, total, 1.0f, 0.0f, 0);
+    if (rblocks < 1) rblocks = 1;
+    if (vec)
+      fnn::splitk_reduce_vec4_kernel<<<static_cast<unsigned>(rblocks), 256, 0, s>>>(
+          reinterpret_cast<const float4*>(partials), grad_weight, nullptr, out_channels, k, 1, p.slices, k, total,
+          1.0f, 0.0f, 0);
+    else
+      fnn::splitk_reduce_kernel<<<static_cast<unsigned>(rblocks), 256, 0, s>>>(
+          partials, grad_weight, nullptr, out_channels, k, 1, p.slices, k, total, 1.0f, 0.0f, 0);
     g_launches.fetch_add(1, std::memory_order_relaxed);
   }
   FNN_CUDA_OK(cudaGetLastError());
