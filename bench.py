@@ -707,6 +707,13 @@ def run_ours(args, rank, world, local_rank):
         roof["traffic"] = None
         roof["traffic_source"] = "no capture of this kernel and plan in profiles/dram_traffic.md"
     roof["algorithmic_bytes"] = gemm_bytes(ts)
+    if roof["bound"] == "tensor" and same_work and clocks and clocks.get("sm_mhz"):
+        # what the tensor cores can do at the clock the power cap left during the timed region:
+        # SMs x 4096 dense TF32 flop per clock x the median sampled SM clock
+        sms = torch.cuda.get_device_properties(local_rank).multi_processor_count
+        at_clock = sms * 4096 * clocks["sm_mhz"] * 1e6 / 1e12
+        roof["tensor_peak_at_sampled_clock"] = at_clock
+        roof["frac_of_peak_at_sampled_clock"] = roof["achieved"] / at_clock
 
     line = {
         "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,

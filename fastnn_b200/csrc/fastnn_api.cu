@@ -564,9 +564,19 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   if (!dual && !gather)
     refine_large_plan(&plan, g.m, g.n, g.k, g.batch, st->num_sms, st->max_clusters, a_mn, b_mn, pair_mode,
                       g.bias != nullptr || g.act != 0 || backward, !tune.no_wide);
-  else if (gather && !dual)        // tiles leave for the peers as they finish: same choice, never a K split
-    refine_large_plan(&plan, g.m, g.n, g.k, g.batch, st->num_sms, st->max_clusters, a_mn, b_mn, pair_mode,
+  else if (gather && !dual) {
+    // Tiles leave for the peers as they finish, so a K split is out, and when the links rather than
+    // the tensor cores bound the launch (peer bytes at ~0.7 TB/s against the product at ~0.7
+    // PFLOP/s) what counts is how soon the first tiles are done and how evenly the rest follow:
+    // single-CTA 128 x 256 tiles finish in half the time of a CTA pair's tile and come in twice as
+    // many waves, so the stores of one wave overlap the main loops of the next.
+    const double t_link = 4.0 * g.m * g.n * g.batch * g.n_peers / 0.7e12;
+    const double t_math = 2.0 * g.m * g.n * g.batch * static_cast<double>(g.k) / 0.7e15;
+    const int mode = (t_link > 0.6 * t_math && pair_mode == 0) ? 1 : pair_mode;
+    refine_large_plan(&plan, g.m, g.n, g.k, g.batch, st->num_sms, st->max_clusters, a_mn, b_mn, mode,
                       g.bias != nullptr || g.act != 0, !tune.no_wide);
+    if (mode == 1 && pair_mode == 0) plan.pair = false;
+  }
   if (pol.block_n > 0) plan.block_n = pol.block_n;
   if (!plan.pair && plan.block_n > fnn::kMaxBlockN) plan.block_n = fnn::kMaxBlockN;
   if (pol.split_k > 0) { plan.split_k = pol.split_k; plan.cluster_k = false; }
