@@ -45,6 +45,7 @@ SIGNATURES = {
     "fastnn_b200_rnn_gates_forward": (_i, [_vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "fastnn_b200_memcpy_h2d_async": (_i, [_vp, _vp, ctypes.c_size_t, _vp]),
     "fastnn_b200_memcpy_d2h_async": (_i, [_vp, _vp, ctypes.c_size_t, _vp]),
+    "fastnn_b200_memcpy_d2d_async": (_i, [_vp, _vp, ctypes.c_size_t, _vp]),
     "fastnn_cuda_conv2d_forward": (_i, [_vp, _vp, _vp, _vp] + [_i] * 11),
     "fastnn_b200_conv2d_forward": (_i, [_vp, _vp, _vp, _vp] + [_i] * 12 + [_vp]),
     "fastnn_cuda_conv2d_backward_data": (_i, [_vp, _vp, _vp] + [_i] * 13),

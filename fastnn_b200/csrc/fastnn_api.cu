@@ -1099,6 +1099,12 @@ extern "C" int fastnn_b200_memcpy_d2h_async(float* dst, const float* src, size_t
   FNN_CUDA_OK(cudaMemcpyAsync(dst, src, size, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
   return 0;
 }
+extern "C" int fastnn_b200_memcpy_d2d_async(float* dst, const float* src, size_t size, void* stream) {
+  if (size == 0) return 0;
+  if (dst == nullptr || src == nullptr) return -1;
+  FNN_CUDA_OK(cudaMemcpyAsync(dst, src, size, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+  return 0;
+}
 extern "C" int fastnn_cuda_memcpy_d2d(float* dst, const float* src, size_t size) {
   FNN_CUDA_OK(cudaMemcpy(dst, src, size, cudaMemcpyDeviceToDevice));
   return 0;

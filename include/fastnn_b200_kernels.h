@@ -313,6 +313,11 @@ FASTNN_B200_API int fastnn_b200_gemm_splitk_static(int layout, const float* a, c
  * The caller orders the streams with its own events. */
 FASTNN_B200_API int fastnn_b200_memcpy_h2d_async(float* dst, const float* src, size_t size, void* stream);
 FASTNN_B200_API int fastnn_b200_memcpy_d2h_async(float* dst, const float* src, size_t size, void* stream);
+/* The same for fastnn_cuda_memcpy_d2d (cuda/kernels.cu:89-92).  Source and destination may lie on
+ * different GPUs when both are mapped into this process (peer access / symmetric memory): the copy
+ * engines then move the bytes over NVLink without occupying an SM -- the multi-GPU gather uses this
+ * for finished row panels of C where the links, not the tensor cores, bound the step. */
+FASTNN_B200_API int fastnn_b200_memcpy_d2d_async(float* dst, const float* src, size_t size, void* stream);
 
 /* Kernel selection for tests and sweeps; applies to calls made by the CALLING THREAD only (other
  * threads keep the automatic choice).  policy: 0 = automatic (tcgen05 path whenever the
