@@ -222,6 +222,39 @@ def sharded_matmul_gathered(layout: int, a_shard: torch.Tensor, b: torch.Tensor,
     return out.tensor
 
 
+def sharded_matmul(layout: int, a_shard: torch.Tensor, b: torch.Tensor,
+                   local_matmul: Optional[Callable] = None) -> torch.Tensor:
+    """This rank's rows (or batches) of C.  ``b`` is replicated for 2-D products; for batched
+    products ``b`` is this rank's batches as well."""
+    fn = local_matmul or _cuda_local
+    return fn(layout, a_shard, b)
+
+
+def all_gather_rows(c_local: torch.Tensor, total_rows: int, group=None) -> torch.Tensor:
+    """All of C on every rank.  Equal shards use one all_gather_into_tensor; ragged shards
+    (total_rows not divisible by the world size) gather padded shards and trim."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    r0, r1 = row_partition(total_rows, world, rank)
+    if c_local.shape[0] != r1 - r0:
+        raise ValueError("c_local does not hold this rank's rows")
+    rest = tuple(c_local.shape[1:])
+    if total_rows % world == 0:
+        out = torch.empty((total_rows,) + rest, dtype=c_local.dtype, device=c_local.device)
+        dist.all_gather_into_tensor(out, c_local.contiguous(), group=group)
+        return out
+    most = -(-total_rows // world)
+    padded = torch.zeros((most,) + rest, dtype=c_local.dtype, device=c_local.device)
+    padded[: r1 - r0] = c_local
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded, group=group)
+    pieces = []
+    for r in range(world):
+        q0, q1 = row_partition(total_rows, world, r)
+        pieces.append(parts[r][: q1 - q0])
+    return torch.cat(pieces, dim=0)
+
+
 # ------------------------------------------------------------------------------------------
 # K-sharded weight gradient:  dW[m,n] = X^T . dY  with the CONTRACTION dimension split over ranks
 # (each rank holds its own rows of X[k,m] and dY[k,n] -- the data-parallel case of FastNN's
