@@ -488,15 +488,10 @@ def strong_scaling(torch, dist, f, sharding, rank, world, reps=10):
             t_cmp = timed(compute_only)
             out = sharding.GatheredOutput((m, n))
 
-            def gathered(method):
-                def run():
-                    sharding.sharded_matmul_gathered(lay, shard, bm, out, bias=bias, act=s["act"], method=method)
-                    out.barrier()
-                return run
-            t_epi = timed(gathered("epilogue"))
-            t_pan = timed(gathered("panels"))
-            auto = sharding.gather_method(r1 - r0, n, k, 1, world - 1)
-            t_fused = t_epi if auto == "epilogue" else t_pan
+            def fused():
+                sharding.sharded_matmul_gathered(lay, shard, bm, out, bias=bias, act=s["act"])
+                out.barrier()
+            t_fused = timed(fused)
             full = out.tensor          # reuse the buffer as the NCCL destination
 
             def unfused():
@@ -512,8 +507,7 @@ def strong_scaling(torch, dist, f, sharding, rank, world, reps=10):
             ingest = 4.0 * m * n * (world - 1) / world
             t_link = ingest / (NVLINK_PEER_GBS * 1e9) * 1e3
             per[s["label"]] = {
-                "t1_ms": t1, "compute_only_ms": t_cmp, "with_gather_ms": t_fused, "gather_method": auto,
-                "epilogue_stores_ms": t_epi, "panel_copies_ms": t_pan,
+                "t1_ms": t1, "compute_only_ms": t_cmp, "with_gather_ms": t_fused,
                 "gemm_then_nccl_allgather_ms": t_nccl, "allgather_ms": t_ag,
                 "compute_only_tflops": flops / (t_cmp * 1e-3) / 1e12,
                 "with_gather_tflops": flops / (t_fused * 1e-3) / 1e12,
@@ -535,12 +529,9 @@ def strong_scaling(torch, dist, f, sharding, rank, world, reps=10):
             "gemm_then_nccl_allgather_efficiency": tot["t1_ms"] / (world * tot["gemm_then_nccl_allgather_ms"]),
             "compute_only_tflops": sum(gemm_flops(s) for s in spec) / (tot["compute_only_ms"] * 1e-3) / 1e12,
             "with_gather_tflops": sum(gemm_flops(s) for s in spec) / (tot["with_gather_ms"] * 1e-3) / 1e12}
-    results["how"] = ("rows of C split over the ranks, B replicated; with_gather = all of C on every rank after one "
-                      "barrier per GEMM, by the method the library picks: epilogue_stores (every finished tile "
-                      "stored by the GEMM epilogue into all ranks' C, TMA stores to peer memory) or panel_copies "
-                      "(row panels of the shard, each copied to the peers by the copy engines while the next is "
-                      "computed); both timed; efficiency = t1 / (N * tN), t1 timed in this run; "
-                      "bound = max(t1 / N, NVLink ingest)")
+    results["how"] = ("rows of C split over the ranks, B replicated; with_gather = every finished tile stored by "
+                      "the GEMM epilogue into all ranks' C (TMA stores to peer memory) + one barrier per GEMM; "
+                      "efficiency = t1 / (N * tN), t1 timed in this run; bound = max(t1 / N, NVLink ingest)")
     return results
 
 

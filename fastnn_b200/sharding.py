@@ -101,32 +101,6 @@ def gather_plan(layout: int, a_shape, a_row_stride: int, b_shape, total: int, wo
                 sa=0, sb=0, sc=0, offset=r0 * n)
 
 
-# Rates behind the choice between the two forms of the gather (measured on 8 x B200 with NVSwitch):
-# tiles stored by the epilogue warps leave a GPU at about 0.35 TB/s (TMA stores of 32 x 32-float tiles:
-# 128-byte rows, one NVLink write each), the copy engines move whole row panels at about 0.77 TB/s.
-_SM_STORE_BYTES_PER_S = 0.35e12
-_TENSOR_FLOP_PER_S = 0.7e15
-
-
-def gather_method(m: int, n: int, k: int, batch: int, n_peers: int) -> str:
-    """'epilogue' when the peer stores of the GEMM's own epilogue hide under its main loop (two GPUs,
-    or deep K), else 'panels': row panels of the shard computed one launch each, every finished panel
-    copied to the peers by the copy engines while the next one is computed."""
-    if n_peers <= 0:
-        return "epilogue"
-    t_store = 4.0 * m * n * batch * n_peers / _SM_STORE_BYTES_PER_S
-    t_math = 2.0 * m * n * batch * k / _TENSOR_FLOP_PER_S
-    return "epilogue" if t_store <= t_math else "panels"
-
-
-def panel_rows(m: int, n: int, sms: int = 148) -> int:
-    """Rows of one panel of the panel-wise gather: a multiple of 128 that gives the GEMM of a panel
-    about a machine-full of 128 x 256 tiles (fewer leave SMs idle, more delay the first copy)."""
-    col_tiles = -(-n // 256)
-    row_tiles = max(1, -(-int(0.8 * sms) // col_tiles))
-    return min(m, 128 * row_tiles) if m > 0 else 0
-
-
 class GatheredOutput:
     """The full C of a sharded product in symmetric memory: the same ``shape`` on every rank, each
     rank's buffer mapped into every other rank's address space."""
@@ -142,31 +116,25 @@ class GatheredOutput:
                                      device=torch.device("cuda", torch.cuda.current_device()))
         self.handle = symm_mem.rendezvous(self.tensor, self.group)
         self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        self._copy_streams = None
 
     def barrier(self, channel: int = 0) -> None:
         """Every rank's GEMMs enqueued before this point are complete on every rank afterwards
         (runs on torch's current stream; no host synchronisation)."""
         self.handle.barrier(channel=channel)
 
-    def copy_streams(self):
-        """One side stream per peer for the panel copies (created on first use)."""
-        if self._copy_streams is None:
-            self._copy_streams = [torch.cuda.Stream() for _ in range(self.world - 1)]
-        return self._copy_streams
-
 
 def sharded_matmul_gathered(layout: int, a_shard: torch.Tensor, b: torch.Tensor, out: GatheredOutput,
                             bias: Optional[torch.Tensor] = None, act: int = cb.ACT_NONE,
-                            stream: Optional[int] = None, method: str = "auto") -> torch.Tensor:
-    """This rank's rows (or batches) of C = act(op(A).op(B) + bias), delivered into ``out`` on EVERY
-    rank.  Returns this rank's full-size buffer; rows computed by other ranks are valid after
-    ``out.barrier()``.
+                            stream: Optional[int] = None) -> torch.Tensor:
+    """This rank's rows (or batches) of C = act(op(A).op(B) + bias), written by the GEMM itself
+    into ``out`` on EVERY rank.  Returns this rank's full-size buffer; rows computed by other ranks
+    are valid after ``out.barrier()``.
 
-    method 'epilogue': one GEMM launch whose epilogue stores every finished tile to all ranks.
-    method 'panels'  : the shard in row panels, one launch each; a finished panel is copied to the
-    peers by the copy engines on side streams while the next panel is computed (2-D products).
-    'auto' picks by ``gather_method``."""
+    (A second form -- the shard in row panels, each finished panel copied to the peers with
+    cudaMemcpyAsync on side streams while the next panel is computed -- was built and measured:
+    the copies of peer-mapped memory did not overlap the persistent GEMM and moved no more bytes per
+    second than the epilogue's own stores, 0.61 ms against 0.61-0.62 ms per 8192-row GEMM on four
+    GPUs and 1.05 against 0.79 ms on two, so it was taken out again.)"""
     cb._ensure_ctx(b)
     total = int(out.tensor.shape[0])
     if a_shard.dim() == 3:
@@ -178,47 +146,13 @@ def sharded_matmul_gathered(layout: int, a_shard: torch.Tensor, b: torch.Tensor,
     if plan["m"] == 0 or plan["batch"] == 0:
         return out.tensor
     off = 4 * plan["offset"]
-    n_peers = out.world - 1
     # destinations start at the next rank, so that the ranks do not all write one GPU at a time
-    peer_ranks = [(out.rank + 1 + i) % out.world for i in range(n_peers)]
-    if method == "auto":
-        method = gather_method(plan["m"], plan["n"], plan["k"], plan["batch"], n_peers)
-    if plan["batch"] > 1 or n_peers == 0:
-        method = "epilogue"
-    bias_ptr = bias.data_ptr() if bias is not None else 0
-    cur = cb.current_stream_ptr() if stream is None else stream
-    own = out.base_ptrs[out.rank] + off
-    if method == "epilogue":
-        cb.gemm_gather_ex(layout, a_shard.data_ptr(), b.data_ptr(), own,
-                          plan["m"], plan["n"], plan["k"], plan["batch"], plan["lda"], plan["ldb"], plan["ldc"],
-                          plan["sa"], plan["sb"], plan["sc"], [out.base_ptrs[r] + off for r in peer_ranks],
-                          bias_ptr=bias_ptr, act=act, stream=cur)
-        return out.tensor
-    if method != "panels":
-        raise ValueError("method must be 'auto', 'epilogue' or 'panels'")
-    if stream is not None and stream != cb.current_stream_ptr():
-        raise ValueError("the panel-wise gather runs on torch's current stream")
-    m, n, k = plan["m"], plan["n"], plan["k"]
-    rows = panel_rows(m, n)
-    sides = out.copy_streams()
-    main = torch.cuda.current_stream()
-    for p0 in range(0, m, rows):
-        p1 = min(m, p0 + rows)
-        # rows [p0, p1) of the shard: rows of A for NN / NT, columns of the stored [k, m] for TN
-        a_ptr = a_shard.data_ptr() + 4 * (p0 if layout == TN else p0 * plan["lda"])
-        cb.gemm_ex(layout, a_ptr, b.data_ptr(), own + 4 * p0 * n, p1 - p0, n, k, 1, plan["lda"], plan["ldb"], n,
-                   0, 0, 0, 1.0, 0.0, bias_ptr, act, cur)
-        done = torch.cuda.Event()
-        done.record(main)
-        nbytes = 4 * (p1 - p0) * n
-        for side, r in zip(sides, peer_ranks):
-            side.wait_event(done)
-            rc = cb.lib().fastnn_b200_memcpy_d2d_async(out.base_ptrs[r] + off + 4 * p0 * n, own + 4 * p0 * n,
-                                                       nbytes, side.cuda_stream)
-            if rc != 0:
-                raise cb.CudaError("peer copy of a finished panel failed")
-    for side in sides:                      # what follows on the current stream follows the copies
-        main.wait_stream(side)
+    peers = [out.base_ptrs[(out.rank + 1 + i) % out.world] + off for i in range(out.world - 1)]
+    cb.gemm_gather_ex(layout, a_shard.data_ptr(), b.data_ptr(), out.base_ptrs[out.rank] + off,
+                      plan["m"], plan["n"], plan["k"], plan["batch"], plan["lda"], plan["ldb"], plan["ldc"],
+                      plan["sa"], plan["sb"], plan["sc"], peers,
+                      bias_ptr=bias.data_ptr() if bias is not None else 0, act=act,
+                      stream=cb.current_stream_ptr() if stream is None else stream)
     return out.tensor
 
 

@@ -176,21 +176,3 @@ def test_two_rank_gloo_fused_gather_layout():
         p.join(60)
         assert p.exitcode == 0
     assert got == [(0, True), (1, True)]
-
-
-def test_gather_method_and_panel_rows():
-    """Two GPUs (one peer, deep K): the epilogue's own stores hide under the main loop.  Four and
-    eight GPUs on the 8192-row problem: more peer bytes per flop than the epilogue stores can move,
-    so finished row panels go out through the copy engines.  A panel is about one machine-full of
-    128 x 256 tiles and a multiple of 128 rows."""
-    assert sharding.gather_method(4096, 8192, 8192, 1, 1) == "epilogue"
-    assert sharding.gather_method(2048, 8192, 8192, 1, 3) == "panels"
-    assert sharding.gather_method(1024, 8192, 8192, 1, 7) == "panels"
-    assert sharding.gather_method(1024, 8192, 8192, 1, 0) == "epilogue"
-    assert sharding.gather_method(16384, 16384, 4096, 1, 1) == "epilogue"
-    assert sharding.panel_rows(1024, 8192) == 512 and sharding.panel_rows(2048, 8192) == 512
-    assert sharding.panel_rows(4096, 16384) == 256
-    assert sharding.panel_rows(100, 8192) == 100 and sharding.panel_rows(0, 8192) == 0
-    for m, n in ((1024, 8192), (5000, 300), (130, 70000)):
-        r = sharding.panel_rows(m, n)
-        assert 0 < r <= m and (r % 128 == 0 or r == m)
