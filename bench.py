@@ -488,10 +488,16 @@ def strong_scaling(torch, dist, f, sharding, rank, world, reps=10):
             t_cmp = timed(compute_only)
             out = sharding.GatheredOutput((m, n))
 
-            def fused():
-                sharding.sharded_matmul_gathered(lay, shard, bm, out, bias=bias, act=s["act"])
-                out.barrier()
-            t_fused = timed(fused)
+            def fused(multicast):
+                def run():
+                    sharding.sharded_matmul_gathered(lay, shard, bm, out, bias=bias, act=s["act"],
+                                                     multicast=multicast)
+                    out.barrier()
+                return run
+            t_uni = timed(fused(False))
+            t_mc = timed(fused(True)) if out.mc_ptr != 0 else None
+            by_switch = t_mc is not None and world >= 3      # what multicast=None picks
+            t_fused = t_mc if by_switch else t_uni
             full = out.tensor          # reuse the buffer as the NCCL destination
 
             def unfused():
@@ -508,6 +514,8 @@ def strong_scaling(torch, dist, f, sharding, rank, world, reps=10):
             t_link = ingest / (NVLINK_PEER_GBS * 1e9) * 1e3
             per[s["label"]] = {
                 "t1_ms": t1, "compute_only_ms": t_cmp, "with_gather_ms": t_fused,
+                "gather_by": "multimem.st through the switch" if by_switch else "TMA stores to each peer",
+                "peer_stores_ms": t_uni, "multicast_stores_ms": t_mc,
                 "gemm_then_nccl_allgather_ms": t_nccl, "allgather_ms": t_ag,
                 "compute_only_tflops": flops / (t_cmp * 1e-3) / 1e12,
                 "with_gather_tflops": flops / (t_fused * 1e-3) / 1e12,
@@ -529,9 +537,11 @@ def strong_scaling(torch, dist, f, sharding, rank, world, reps=10):
             "gemm_then_nccl_allgather_efficiency": tot["t1_ms"] / (world * tot["gemm_then_nccl_allgather_ms"]),
             "compute_only_tflops": sum(gemm_flops(s) for s in spec) / (tot["compute_only_ms"] * 1e-3) / 1e12,
             "with_gather_tflops": sum(gemm_flops(s) for s in spec) / (tot["with_gather_ms"] * 1e-3) / 1e12}
-    results["how"] = ("rows of C split over the ranks, B replicated; with_gather = every finished tile stored by "
-                      "the GEMM epilogue into all ranks' C (TMA stores to peer memory) + one barrier per GEMM; "
-                      "efficiency = t1 / (N * tN), t1 timed in this run; bound = max(t1 / N, NVLink ingest)")
+    results["how"] = ("rows of C split over the ranks, B replicated; with_gather = every finished tile sent by the GEMM "
+                      "epilogue into all ranks' C + one barrier per GEMM, the way the library picks: one TMA store "
+                      "per peer (two ranks) or one multimem.st through the NVSwitch (three ranks and more); both "
+                      "are timed (peer_stores_ms, multicast_stores_ms); efficiency = t1 / (N * tN), t1 timed in "
+                      "this run; bound = max(t1 / N, NVLink ingest)")
     return results
 
 
@@ -548,7 +558,6 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     f.cuda_init(local_rank)
     if world > 1:
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")     # plain peer mappings only
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     spec = workload_spec(args.workload)
 

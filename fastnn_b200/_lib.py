@@ -58,6 +58,8 @@ SIGNATURES = {
     "fastnn_cuda_scaled_dot_product_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i]),
     "fastnn_b200_gemm_gather_ex": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll,
                                         _f, _vp, _i, ctypes.POINTER(_vp), _i, _vp]),
+    "fastnn_b200_gemm_gather_mc_ex": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll,
+                                           _f, _vp, _i, _vp, _vp]),
     "fastnn_b200_selftest_bounded_wait": (_i, [ctypes.c_uint, ctypes.POINTER(ctypes.c_uint)]),
     "fastnn_b200_reduce_partials": (_i, [_vp, _vp, _i, _i, _i, _ll, _f, _f, _vp, _i, _vp]),
     "fastnn_b200_set_policy": (_i, [_i, _i, _i]),

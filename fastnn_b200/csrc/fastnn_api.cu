@@ -497,6 +497,9 @@ struct GemmArgs {
   // every finished tile is stored there as well as to c
   float* const* peer_c = nullptr;
   int n_peers = 0;
+  // or, instead of the peers: the NVLink multicast address of those rows (one multimem.st per
+  // 16 bytes reaches every GPU's C, this one's included; c itself is then not written directly)
+  float* mc_c = nullptr;
 };
 
 bool tma_operands_ok(const GemmArgs& g) {
@@ -551,7 +554,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   const bool a_mn = (g.layout == FASTNN_B200_TN) && ((g.m % 32) != 0 || no_chunk);
   const bool b_mn = (g.layout != FASTNN_B200_NT) && ((g.n % 32) != 0 || no_chunk);
   const bool dual = g.a2 != nullptr;       // C = A.B + A2.B2: single-CTA kernel, one K range
-  const bool gather = g.n_peers > 0;       // tiles also go to other GPUs: whole K per tile, TMA stores
+  const bool gather = g.n_peers > 0 || g.mc_c != nullptr;   // tiles also go to other GPUs: whole K per tile
   const int pair_mode = dual ? 1 : ((pol.policy == 3 || pol.policy >= 5) ? 1 : (pol.policy == 4 ? 2 : 0));
   // the backward epilogue is not linear in the partial sums, and the column sums use the workspace
   const bool backward = g.aux != nullptr || g.colsum != nullptr;
@@ -570,7 +573,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     // PFLOP/s) what counts is how soon the first tiles are done and how evenly the rest follow:
     // single-CTA 128 x 256 tiles finish in half the time of a CTA pair's tile and come in twice as
     // many waves, so the stores of one wave overlap the main loops of the next.
-    const double t_link = 4.0 * g.m * g.n * g.batch * g.n_peers / 0.7e12;
+    const double t_link = 4.0 * g.m * g.n * g.batch * (g.mc_c != nullptr ? 1 : g.n_peers) / 0.7e12;
     const double t_math = 2.0 * g.m * g.n * g.batch * static_cast<double>(g.k) / 0.7e15;
     const int mode = (t_link > 0.6 * t_math && pair_mode == 0) ? 1 : pair_mode;
     refine_large_plan(&plan, g.m, g.n, g.k, g.batch, st->num_sms, st->max_clusters, a_mn, b_mn, mode,
@@ -664,6 +667,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   long long out_z = g.batch;
   p.cluster_k = plan.cluster_k ? 1 : 0;
   p.n_peers = g.n_peers;
+  p.mc_c = g.mc_c;
   p.tmem_cols = ck_tmem_cols;
   p.cluster_vec = (plan.cluster_k && (g.n & 3) == 0 && aligned16(g.c) && (g.ldc & 3) == 0 &&
                    (g.batch == 1 || (g.sc & 3) == 0)) ? 1 : 0;
@@ -741,9 +745,9 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
                           fnn::kBlockK, b_cols);
   }
   fnn::PeerMaps peers;
-  if (gather) {
+  if (gather) std::memset(&peers, 0, sizeof(peers));
+  if (g.n_peers > 0) {
     // the same rows of C on the other GPUs: identical shape and strides, another base address
-    std::memset(&peers, 0, sizeof(peers));
     const uint64_t sc_bytes = (out_z > 1 ? out_bs : out_ld * g.m) * 4ull;
     for (int i = 0; i < g.n_peers && ok; ++i)
       ok = g.peer_c[i] != nullptr && aligned16(g.peer_c[i]) &&
@@ -903,11 +907,16 @@ int gemm_dispatch(const GemmArgs& g) {
   if (st == nullptr) return -1;                                   // fastnn_cuda_init not called
   const Policy pol = t_policy;
   const bool can_tma = tma_operands_ok(g);
-  if (g.n_peers > 0) {
+  if (g.n_peers > 0 || g.mc_c != nullptr) {
     bool stores_ok = can_tma && pol.policy != 1 && g.beta == 0.0f && aligned16(g.c) && (g.ldc & 3) == 0 &&
                      (g.batch == 1 || (g.sc & 3) == 0) && g.ldc < (1ll << 38) && g.sc < (1ll << 38);
     for (int i = 0; i < g.n_peers && stores_ok; ++i) stores_ok = g.peer_c[i] != nullptr && aligned16(g.peer_c[i]);
-    if (!stores_ok) return gather_by_copies(g);
+    if (g.mc_c != nullptr) {
+      // 16-byte multicast stores of whole row segments; no other form exists for this destination
+      if (g.n_peers > 0 || !stores_ok || !aligned16(g.mc_c) || (g.n & 3) != 0) return -1;
+    } else if (!stores_ok) {
+      return gather_by_copies(g);
+    }
   }
   if (pol.policy >= 2 && !can_tma) return -1;
   if (pol.policy == 1 || !can_tma) return launch_simt(g);
@@ -1885,6 +1894,18 @@ extern "C" int fastnn_b200_selftest_bounded_wait(unsigned int budget_us, unsigne
   (void)cudaFree(out);
   if (waited_us) *waited_us = static_cast<unsigned int>(1000ull * host[1] / static_cast<unsigned>(khz));
   return rc;
+}
+
+extern "C" int fastnn_b200_gemm_gather_mc_ex(int layout, const float* a, const float* b, float* c, int m,
+                                             int n, int k, int batch, long long lda, long long ldb,
+                                             long long ldc, long long stride_a, long long stride_b,
+                                             long long stride_c, float alpha, const float* bias, int act,
+                                             float* mc_c, void* stream) {
+  if (mc_c == nullptr) return -1;
+  GemmArgs g{layout, a, b, c, m, n, k, batch, lda, ldb, ldc, stride_a, stride_b, stride_c,
+             alpha, 0.0f, bias, act, static_cast<cudaStream_t>(stream)};
+  g.mc_c = mc_c;
+  return gemm_dispatch(g);
 }
 
 extern "C" int fastnn_b200_gemm_gather_ex(int layout, const float* a, const float* b, float* c, int m,

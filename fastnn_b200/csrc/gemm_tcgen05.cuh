@@ -71,6 +71,9 @@ struct GemmParams {
   int tmem_cols;       // that kernel's TMEM allocation: one accumulator, a power of two >= block_n
   int n_peers;         // gather kernels: every finished tile is also stored through this many extra
                        // tensor maps (the same rows of C in other GPUs' memory); 0 elsewhere
+  float* mc_c;         // gather kernels, instead of the tensor maps: the NVLink multicast address of
+                       // C (same ldc and batch stride as c); every finished tile is written ONCE, with
+                       // multimem.st, and the switch delivers it to every GPU's C, this one's included
   int kb_per_stage;    // 32-deep k-blocks per pipeline stage (CTA-pair kernel only; else 1)
   int total_units;     // batch * tiles_m * tiles_n * split_k
   int a_mn_major;      // A stored [k, m]
@@ -174,6 +177,23 @@ __device__ __forceinline__ void staging_wait(int nbuf) {
   else ptx::tma_store_wait_read<0>();
 }
 
+// A finished 32 x 32 staging tile (128B-swizzled, 16-byte chunk j of row r at chunk j ^ (r & 7)) sent
+// once through the multicast address of C: every lane reads 16 bytes back, eight lanes cover one
+// 128-byte row segment, four rows per step.  n is a multiple of 4 (checked on the host).
+__device__ __forceinline__ void multicast_store_tile(const GemmParams& p, const uint8_t* tile, int m0,
+                                                     int col0, int cz, int lane) {
+  float* base = p.mc_c + static_cast<long long>(cz) * p.c_batch_stride;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int idx = it * 32 + lane;
+    const int r = idx >> 3, c = idx & 7;
+    const float4 v = *reinterpret_cast<const float4*>(tile + r * 128 + ((c ^ (r & 7)) << 4));
+    const int grow = m0 + r, gcol = col0 + c * 4;
+    if (grow < p.m && gcol < p.n)
+      ptx::multimem_st_f4(base + static_cast<long long>(grow) * p.ldc + gcol, v);
+  }
+}
+
 // Drains one accumulator tile (this warp's 32 TMEM lanes x block_n columns) when nothing but
 // alpha / beta applies: a swizzled staging tile + TMA store, or predicated global stores.
 // m0 is the first output row of this warp, n0 the first column of the tile, cz the outer
@@ -219,16 +239,22 @@ __device__ __forceinline__ void epilogue_drain_plain(const GemmParams& p, const 
         float4 f = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         *reinterpret_cast<float4*>(dst_row + ((j ^ (lane & 7)) << 4)) = f;
       }
-      ptx::fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        if (p.l2_c != 0) ptx::tma_store_3d_hint(tmC, staging + buf * 4096, col0, m0, cz,
-                                                 ptx::make_l2_policy(p.l2_c));
-        else ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
-        // gather launches: the same tile into the same rows of C on every other GPU, one bulk
-        // group with the local store, so the staging tile is free once all of them have read it
-        for (int i = 0; i < n_peers; ++i) ptx::tma_store_3d(peers + i, staging + buf * 4096, col0, m0, cz);
-        ptx::tma_store_commit();
+      if (p.mc_c != nullptr) {                      // warp-uniform
+        __syncwarp();                               // the tile is complete before any lane reads it back
+        multicast_store_tile(p, staging_gen + buf * 4096, m0, col0, cz, lane);
+        __syncwarp();                               // and read by every lane before it is overwritten
+      } else {
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (p.l2_c != 0) ptx::tma_store_3d_hint(tmC, staging + buf * 4096, col0, m0, cz,
+                                                   ptx::make_l2_policy(p.l2_c));
+          else ptx::tma_store_3d(tmC, staging + buf * 4096, col0, m0, cz);
+          // gather launches: the same tile into the same rows of C on every other GPU, one bulk
+          // group with the local store, so the staging tile is free once all of them have read it
+          for (int i = 0; i < n_peers; ++i) ptx::tma_store_3d(peers + i, staging + buf * 4096, col0, m0, cz);
+          ptx::tma_store_commit();
+        }
       }
       buf = (buf + 1) & (nbuf - 1);
     } else if (row < p.m) {
@@ -371,7 +397,11 @@ __device__ __forceinline__ void epilogue_drain_by_column(const GemmParams& p, co
             if (m0 + rr < p.m) ccol[rr * p.ldc] = t[rr];
         }
       }
-      if (p.store_mode == 0) {
+      if (p.store_mode == 0 && p.mc_c != nullptr) {  // warp-uniform
+        __syncwarp();
+        multicast_store_tile(p, tile, m0, col0, cz, lane);
+        __syncwarp();
+      } else if (p.store_mode == 0) {
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -706,6 +736,7 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
     if (p.store_mode == 0 && lane == 0) ptx::tma_store_wait_all<0>();
+    if (p.mc_c != nullptr) __threadfence_system();   // multicast stores are ordered before the kernel's end
   }
 
   if constexpr (kClusterK) {

@@ -246,6 +246,7 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
       if (++acc == n_acc) { acc = 0; acc_phase ^= 1u; }
     }
     if (p.store_mode == 0 && lane == 0) ptx::tma_store_wait_all<0>();
+    if (p.mc_c != nullptr) __threadfence_system();
   }
 
   // ---------------------------------------------------------------- teardown ---

@@ -301,6 +301,14 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// One 16-byte store through an NVLink multicast address: the switch writes it to the same offset of
+// every GPU's buffer bound to that multicast object (this GPU's own included).
+__device__ __forceinline__ void multimem_st_f4(float* mc_addr, float4 v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(v.x), "f"(v.y),
+               "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
 // ----------------------------------------------------------------- cluster ---
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

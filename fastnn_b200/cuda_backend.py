@@ -383,6 +383,18 @@ def gemm_gather_ex(layout, a_ptr, b_ptr, c_ptr, m, n, k, batch, lda, ldb, ldc, s
         raise CudaError("fastnn_b200_gemm_gather_ex failed")
 
 
+def gemm_gather_mc_ex(layout, a_ptr, b_ptr, c_ptr, m, n, k, batch, lda, ldb, ldc, sa, sb, sc, mc_ptr,
+                      alpha=1.0, bias_ptr=0, act=ACT_NONE, stream=0) -> None:
+    """The gather through the switch: every finished tile goes once, with multimem.st, to the NVLink
+    multicast address ``mc_ptr`` of these rows of C and arrives in every GPU's buffer."""
+    rc = lib().fastnn_b200_gemm_gather_mc_ex(layout, ctypes.c_void_p(a_ptr), ctypes.c_void_p(b_ptr),
+                                             ctypes.c_void_p(c_ptr), m, n, k, batch, lda, ldb, ldc, sa, sb, sc,
+                                             alpha, ctypes.c_void_p(bias_ptr), act, ctypes.c_void_p(mc_ptr),
+                                             ctypes.c_void_p(stream))
+    if rc != 0:
+        raise CudaError("fastnn_b200_gemm_gather_mc_ex failed")
+
+
 def selftest_bounded_wait(budget_us: int = 1000) -> int:
     """Runs the one-warp kernel whose bounded wait must run out; returns how long it waited (us).
     Afterwards ``device_status()`` returns 0x1F0 once and then 0 again."""

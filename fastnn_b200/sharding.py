@@ -116,6 +116,8 @@ class GatheredOutput:
                                      device=torch.device("cuda", torch.cuda.current_device()))
         self.handle = symm_mem.rendezvous(self.tensor, self.group)
         self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        # NVLink multicast address of the buffer (0 when the fabric or the driver offers none)
+        self.mc_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
 
     def barrier(self, channel: int = 0) -> None:
         """Every rank's GEMMs enqueued before this point are complete on every rank afterwards
@@ -125,10 +127,16 @@ class GatheredOutput:
 
 def sharded_matmul_gathered(layout: int, a_shard: torch.Tensor, b: torch.Tensor, out: GatheredOutput,
                             bias: Optional[torch.Tensor] = None, act: int = cb.ACT_NONE,
-                            stream: Optional[int] = None) -> torch.Tensor:
+                            stream: Optional[int] = None, multicast: Optional[bool] = None) -> torch.Tensor:
     """This rank's rows (or batches) of C = act(op(A).op(B) + bias), written by the GEMM itself
     into ``out`` on EVERY rank.  Returns this rank's full-size buffer; rows computed by other ranks
     are valid after ``out.barrier()``.
+
+    ``multicast``: True sends every tile once through the NVSwitch (multimem.st to the buffer's
+    multicast address), False stores it to each peer in turn (TMA stores); None picks multicast
+    from three ranks on when the buffer has a multicast address and the shape allows it -- with two
+    ranks a rank sends the same bytes either way and the unicast stores skip the trip to the switch
+    for the local copy.
 
     (A second form -- the shard in row panels, each finished panel copied to the peers with
     cudaMemcpyAsync on side streams while the next panel is computed -- was built and measured:
@@ -146,13 +154,24 @@ def sharded_matmul_gathered(layout: int, a_shard: torch.Tensor, b: torch.Tensor,
     if plan["m"] == 0 or plan["batch"] == 0:
         return out.tensor
     off = 4 * plan["offset"]
+    cur = cb.current_stream_ptr() if stream is None else stream
+    mc_ok = out.mc_ptr != 0 and plan["n"] % 4 == 0 and a_shard.data_ptr() % 16 == 0 and plan["lda"] % 4 == 0
+    if multicast is None:
+        multicast = mc_ok and out.world >= 3
+    if multicast:
+        if not mc_ok:
+            raise ValueError("no multicast address for this buffer, or a shape multimem.st cannot serve")
+        cb.gemm_gather_mc_ex(layout, a_shard.data_ptr(), b.data_ptr(), out.base_ptrs[out.rank] + off,
+                             plan["m"], plan["n"], plan["k"], plan["batch"], plan["lda"], plan["ldb"],
+                             plan["ldc"], plan["sa"], plan["sb"], plan["sc"], out.mc_ptr + off,
+                             bias_ptr=bias.data_ptr() if bias is not None else 0, act=act, stream=cur)
+        return out.tensor
     # destinations start at the next rank, so that the ranks do not all write one GPU at a time
     peers = [out.base_ptrs[(out.rank + 1 + i) % out.world] + off for i in range(out.world - 1)]
     cb.gemm_gather_ex(layout, a_shard.data_ptr(), b.data_ptr(), out.base_ptrs[out.rank] + off,
                       plan["m"], plan["n"], plan["k"], plan["batch"], plan["lda"], plan["ldb"], plan["ldc"],
                       plan["sa"], plan["sb"], plan["sc"], peers,
-                      bias_ptr=bias.data_ptr() if bias is not None else 0, act=act,
-                      stream=cb.current_stream_ptr() if stream is None else stream)
+                      bias_ptr=bias.data_ptr() if bias is not None else 0, act=act, stream=cur)
     return out.tensor
 
 

@@ -261,6 +261,23 @@ FASTNN_B200_API int fastnn_b200_gemm_gather_ex(int layout, const float* a, const
                                                int act, float* const* peer_c, int n_peers,
                                                void* stream);
 
+/* The same gather through the NVSwitch: mc_c is the NVLink MULTICAST address of the rows this rank
+ * computes (a multicast object bound to every rank's C buffer, e.g. the multicast pointer of torch's
+ * symmetric memory, plus the shard's offset).  Every finished tile is written ONCE, 16 bytes per
+ * multimem.st, and the switch delivers it to every GPU's C -- this GPU's own included, so c (which
+ * must be this rank's local address of the same rows, and supplies alignment and shape) is not
+ * written directly.  A rank then sends 1/N of C instead of (N-1)/N: the form for four GPUs and
+ * more, where the unicast stores of fastnn_b200_gemm_gather_ex, not the tensor cores, set the time.
+ * Needs TMA-addressable operands, 16-byte aligned c and mc_c, n and ldc multiples of 4 (-1
+ * otherwise: use the unicast entry).  Completion as above: kernel end on every rank, then one
+ * barrier among the ranks.  No counterpart in FastNN. */
+FASTNN_B200_API int fastnn_b200_gemm_gather_mc_ex(int layout, const float* a, const float* b, float* c,
+                                                  int m, int n, int k, int batch,
+                                                  long long lda, long long ldb, long long ldc,
+                                                  long long stride_a, long long stride_b,
+                                                  long long stride_c, float alpha, const float* bias,
+                                                  int act, float* mc_c, void* stream);
+
 /* c[m,n] = act( alpha * (partials[0] + partials[1] + ... + partials[count-1]) + beta * c + bias ),
  * partials stored back to back as count dense [m,n] matrices, added in ascending order.
  * The reduce step of split-K, exposed for the multi-GPU weight-gradient path where the K

@@ -22,7 +22,6 @@ def _worker(rank, world, port, queue):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")      # plain peer mappings only
     torch.cuda.set_device(rank)
     f.cuda_init(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -84,11 +83,16 @@ def _work(rank, world, queue, torch, dist, f, sharding):
             da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
             shard = sharding.shard_left_operand(layout, da, world, rank)
             full = sharding.GatheredOutput((m, n))
-            for _ in range(2):
+            # unicast stores twice (the buffer is reused), then -- where the fabric offers a multicast
+            # address and the shape allows 16-byte stores -- once through the switch
+            modes = [False, False] + ([True] if full.mc_ptr != 0 and n % 4 == 0 and shard.stride(0) % 4 == 0 else [])
+            for mc in modes:
                 full.tensor.fill_(float("nan"))
                 full.barrier()
-                sharding.sharded_matmul_gathered(layout, shard, db, full)
+                sharding.sharded_matmul_gathered(layout, shard, db, full, multicast=mc)
                 full.barrier()
+                torch.cuda.synchronize()
+                assert not torch.isnan(full.tensor).any(), f"multicast={mc}: rows missing on rank {rank}"
             gathered[(layout, m, n, k)] = (full.tensor.cpu().numpy(), a, b)
         gb = sharding.GatheredOutput((6, 128, 128))
         gb.tensor.fill_(float("nan"))
