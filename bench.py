@@ -496,8 +496,8 @@ def strong_scaling(torch, dist, f, sharding, rank, world, reps=10):
                 return run
             t_uni = timed(fused(False))
             t_mc = timed(fused(True)) if out.mc_ptr != 0 else None
-            by_switch = t_mc is not None and world >= 3      # what multicast=None picks
-            t_fused = t_mc if by_switch else t_uni
+            by_switch = False                                # the library's default: unicast peer stores
+            t_fused = t_uni
             full = out.tensor          # reuse the buffer as the NCCL destination
 
             def unfused():
@@ -538,9 +538,9 @@ def strong_scaling(torch, dist, f, sharding, rank, world, reps=10):
             "compute_only_tflops": sum(gemm_flops(s) for s in spec) / (tot["compute_only_ms"] * 1e-3) / 1e12,
             "with_gather_tflops": sum(gemm_flops(s) for s in spec) / (tot["with_gather_ms"] * 1e-3) / 1e12}
     results["how"] = ("rows of C split over the ranks, B replicated; with_gather = every finished tile sent by the GEMM "
-                      "epilogue into all ranks' C + one barrier per GEMM, the way the library picks: one TMA store "
-                      "per peer (two ranks) or one multimem.st through the NVSwitch (three ranks and more); both "
-                      "are timed (peer_stores_ms, multicast_stores_ms); efficiency = t1 / (N * tN), t1 timed in "
+                      "epilogue into all ranks' C + one barrier per GEMM: one TMA store per peer (the default, "
+                      "peer_stores_ms = with_gather_ms); the optional form, one multimem.st through the NVSwitch, "
+                      "is timed beside it (multicast_stores_ms); efficiency = t1 / (N * tN), t1 timed in "
                       "this run; bound = max(t1 / N, NVLink ingest)")
     return results
 
