@@ -77,6 +77,7 @@ struct Tunables {
   int group_m = 0;              // FASTNN_B200_GROUP_M: tile rows per rasterisation group
   int l2 = -1;                  // FASTNN_B200_L2=<C><A><B>: eviction policies of stores and loads
   bool no_wide = false;         // FASTNN_B200_WIDE=0: CTA pairs keep 256-wide tiles
+  int pace = 7;                 // FASTNN_B200_PACE=<0..8>: eighths of a tile's time its gather stores are spread over
 };
 const Tunables& tunables() {
   static const Tunables t = [] {
@@ -93,6 +94,8 @@ const Tunables& tunables() {
     v.group_m = num("FASTNN_B200_GROUP_M", 0);
     v.l2 = num("FASTNN_B200_L2", -1);
     v.no_wide = num("FASTNN_B200_WIDE", 1) == 0;
+    v.pace = num("FASTNN_B200_PACE", 7);
+    if (v.pace < 0 || v.pace > 8) v.pace = 7;
     return v;
   }();
   return t;
@@ -754,6 +757,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
            encode_map(&peers.m[i], g.peer_c[i], g.n, g.m, static_cast<uint64_t>(out_z), out_ld * 4ull,
                       sc_bytes, 32, 32);
   }
+  if (gather) p.pace_gather = tune.pace;
   if (!ok) return -1;
 
   int grid;

@@ -74,6 +74,8 @@ struct GemmParams {
   float* mc_c;         // gather kernels, instead of the tensor maps: the NVLink multicast address of
                        // C (same ldc and batch stride as c); every finished tile is written ONCE, with
                        // multimem.st, and the switch delivers it to every GPU's C, this one's included
+  int pace_gather;     // gather kernels: spread each tile's stores over this many eighths of the time its
+                       // main loop took (0: send every tile at once)
   int kb_per_stage;    // 32-deep k-blocks per pipeline stage (CTA-pair kernel only; else 1)
   int total_units;     // batch * tiles_m * tiles_n * split_k
   int a_mn_major;      // A stored [k, m]
@@ -194,6 +196,23 @@ __device__ __forceinline__ void multicast_store_tile(const GemmParams& p, const 
   }
 }
 
+// Pacing of a gather epilogue: chunk i of a tile is not started before t0 + i * step (SM clock
+// ticks).  All CTAs finish their tiles at about the same time; sent at once, the peer tiles of a
+// whole wave fill the queues towards NVLink, and the operand loads of the next tile wait behind
+// them.  Spread over most of the next tile's main loop they never queue.  step = 0: no pacing.
+struct Pace {
+  long long t0 = 0, step = 0;
+};
+__device__ __forceinline__ void pace_chunk(const Pace& pace, int i, int lane) {
+  if (pace.step > 0) {
+    if (lane == 0) {
+      const long long due = pace.t0 + static_cast<long long>(i) * pace.step;
+      while (clock64() < due) __nanosleep(128);
+    }
+    __syncwarp();
+  }
+}
+
 // Drains one accumulator tile (this warp's 32 TMEM lanes x block_n columns) when nothing but
 // alpha / beta applies: a swizzled staging tile + TMA store, or predicated global stores.
 // m0 is the first output row of this warp, n0 the first column of the tile, cz the outer
@@ -205,11 +224,14 @@ __device__ __forceinline__ void epilogue_drain_plain(const GemmParams& p, const 
                                                      uint8_t* staging_gen, int& buf, int m0, int n0,
                                                      int cz, int cb, bool raw, int lane, int c_first,
                                                      int c_step, int nbuf,
-                                                     const CUtensorMap* peers, int n_peers) {
+                                                     const CUtensorMap* peers, int n_peers,
+                                                     const Pace& pace) {
   const int row = m0 + lane;
+  int ci = 0;
   for (int c = c_first; c < p.block_n / 32; c += c_step) {
     const int col0 = n0 + c * 32;
     if (col0 >= p.n) break;                      // warp-uniform
+    pace_chunk(pace, ci++, lane);
     uint32_t r[32];
     ptx::tmem_ld_32x32(taddr0 + c * 32, r);
     ptx::tmem_ld_wait();
@@ -278,7 +300,8 @@ __device__ __forceinline__ void epilogue_drain_by_column(const GemmParams& p, co
                                                       uint8_t* staging_gen, int& buf, int m0, int n0,
                                                       int cz, int cb, bool raw, int lane,
                                                       int c_first, int c_step, int nbuf,
-                                                      const CUtensorMap* peers, int n_peers) {
+                                                      const CUtensorMap* peers, int n_peers,
+                                                      const Pace& pace) {
   const int row = m0 + lane;
   const bool grad = !raw && (p.act == kActReluGrad || p.act == kActGeluGrad);
   const bool want_colsum = p.colsum != nullptr && !raw;
@@ -302,9 +325,11 @@ __device__ __forceinline__ void epilogue_drain_by_column(const GemmParams& p, co
         dst[r] = (col < p.n && m0 + r < p.m) ? __ldg(acol + r * p.ld_aux) : 0.0f;
     }
   };
+  int ci = 0;
   for (int c = c_first; c < nchunks; c += c_step) {
     const int col0 = n0 + c * 32;
     if (col0 >= p.n) break;                      // warp-uniform
+    pace_chunk(pace, ci++, lane);
     const bool col_ok = col0 + lane < p.n;
     // aux of this chunk: the lines were prefetched into L2 when the tile's main loop started, and
     // these loads have the TMEM read and the row-wise staging write to complete under
@@ -431,14 +456,14 @@ __device__ __forceinline__ void epilogue_drain_tile(const GemmParams& p, const C
                                                     int cz, int cb, bool raw, int lane,
                                                     int c_first = 0, int c_step = 1, int nbuf = 2,
                                                     const CUtensorMap* peers = nullptr,
-                                                    int n_peers = 0) {
+                                                    int n_peers = 0, const Pace& pace = Pace()) {
   const bool by_column = !raw && (p.bias != nullptr || p.act != kActNone || p.colsum != nullptr);
   if (by_column)
     epilogue_drain_by_column(p, tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, cb, raw, lane,
-                             c_first, c_step, nbuf, peers, n_peers);
+                             c_first, c_step, nbuf, peers, n_peers, pace);
   else
     epilogue_drain_plain(p, tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, cb, raw, lane,
-                         c_first, c_step, nbuf, peers, n_peers);
+                         c_first, c_step, nbuf, peers, n_peers, pace);
 }
 
 // Pitch in bytes of one row of the partial tile a cluster split-K CTA leaves in shared memory:
@@ -688,6 +713,7 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
     uint32_t acc_phase = 0;
     int buf = 0;
     bool ok = true;
+    long long t_prev_full = clock64();              // gather pacing: when the previous accumulator was complete
     const bool raw = p.split_k > 1;                 // partial sums: no scale / bias / activation
     if constexpr (kClusterK) {
       // One unit.  The accumulator goes, unscaled, to a row-major partial tile at the start of
@@ -727,8 +753,21 @@ __device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUt
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                               static_cast<uint32_t>(acc * kMaxBlockN);
       const int cz = raw ? (w.b * p.split_k + w.s) : w.b;   // outer coordinate of the store
+      Pace pace;
+      if constexpr (kGather) {
+        // every tile of every wave but the grid's last is drained over 7/8 of the time the main
+        // loop took to produce it (the next wave takes as long, on this SM or on others); the
+        // last wave has nothing left to hide behind
+        const long long now = clock64();
+        if (p.pace_gather && u / static_cast<int>(gridDim.x) < (p.total_units - 1) / static_cast<int>(gridDim.x)) {
+          const int my_chunks = (p.block_n / 32 + groups - 1) / groups;
+          pace.t0 = now;
+          pace.step = (now - t_prev_full) * p.pace_gather / (8 * my_chunks);
+        }
+        t_prev_full = now;
+      }
       epilogue_drain_tile(p, &tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, w.b, raw, lane,
-                          group, groups, nbuf, kGather ? peers : nullptr, kGather ? p.n_peers : 0);
+                          group, groups, nbuf, kGather ? peers : nullptr, kGather ? p.n_peers : 0, pace);
       // accumulator drained: hand it back to the MMA warp
       ptx::tc_fence_before_sync();
       __syncwarp();

@@ -226,6 +226,7 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
     uint32_t acc_phase = 0;
     int buf = 0;
     bool ok = true;
+    long long t_prev_full = clock64();
     const bool raw = p.split_k > 1;
     for (int u = cluster_id; u < p.total_units && ok; u += num_clusters) {
       const Unit w = decode_unit_pair(p, u);
@@ -238,8 +239,19 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                               static_cast<uint32_t>(acc * kMaxBlockN);
       const int cz = raw ? (w.b * p.split_k + w.s) : w.b;
+      Pace pace;
+      if constexpr (kGather) {
+        // as in the single-CTA kernel: the tiles of all waves but the last leave over 7/8 of a
+        // main loop's time; only with two accumulators, where the drain is off the critical path
+        const long long now = clock64();
+        if (p.pace_gather && n_acc == 2 && u / num_clusters < (p.total_units - 1) / num_clusters) {
+          pace.t0 = now;
+          pace.step = (now - t_prev_full) * p.pace_gather / (8 * (p.block_n / 32));
+        }
+        t_prev_full = now;
+      }
       epilogue_drain_tile(p, &tmC, taddr0, staging, staging_gen, buf, m0, n0, cz, w.b, raw, lane, 0, 1, 2,
-                          kGather ? peers : nullptr, kGather ? p.n_peers : 0);
+                          kGather ? peers : nullptr, kGather ? p.n_peers : 0, pace);
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(acc), 0));
