@@ -20,6 +20,15 @@
 //   warps 2-5  drain the accumulator: lane = position, column = channel, so for one channel a
 //              warp's 32 lanes write 32 consecutive NCHW elements (coalesced), bias (+ReLU) fused.
 // One persistent CTA per SM, two accumulators in TMEM, every wait bounded as in the GEMM kernels.
+//
+// Slab form (conv2d_tf32_slab_kernel), taken when the shape allows: position tiles lie inside one
+// image, and the input rows a tile needs -- 32 channels at a time, every row padded by four zero
+// columns on either side -- are brought into shared memory by ONE TMA load per chunk (x coordinate
+// -4: 16-byte aligned; rows above and below the image and the side columns arrive as zeros, so no
+// tap mask is needed).  The gather warps then read shared memory instead of L2: per element one
+// add and one load, the tap offsets from a table in shared memory that is the same for every
+// chunk (k = (ci, ki, kj), so 32 channels are exactly kh*kw k-blocks).  Two slab slots take turns;
+// the weight producer loads chunk j + 1 when the main loop reaches chunk j.
 #pragma once
 #include "gemm_tcgen05.cuh"
 
@@ -44,11 +53,20 @@ struct ConvParams {
   // of the full gradient plane.
   int dst_h, dst_w, dst_y0, dst_x0, dst_sy, dst_sx;
   int act;             // 0 none, 1 ReLU
+  // slab form only
+  int tiles_pi;        // position tiles per image: ceil(oh * ow / 128)
+  int taps;            // kh * kw = k-blocks per chunk of 32 channels
+  int n_chunks;        // ceil(ci / 32)
+  int slab_rows;       // input rows one tile can need: (output rows a tile can touch - 1) * sh + kh
+  int slab_pitch;      // floats per row in shared memory: w + 8 (four zero columns on either side)
+  int slab_bytes;      // 32 * slab_rows * slab_pitch * 4
   unsigned int* status;
   long long spin_budget;
 };
 
-enum : unsigned int { kStatusConvGather = 0x301 };
+enum : unsigned int { kStatusConvGather = 0x301, kStatusConvSlab = 0x302 };
+constexpr int kConvSlabChannels = 32;
+constexpr int kConvSlabHalo = 4;      // zero columns either side of a row (keeps the TMA x coordinate aligned)
 constexpr int kConvGatherWarps = 16;
 constexpr int kConvThreads = 32 * (6 + kConvGatherWarps);   // producer, MMA issuer, 4 epilogue warps, gather warps
 constexpr int kConvKPerThread = kBlockK / (kConvGatherWarps / 4);   // k's of a stage row one gather thread fills
@@ -88,8 +106,9 @@ __device__ __forceinline__ bool conv_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-__global__ void __launch_bounds__(kConvThreads, 1)
-conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ ConvParams p) {
+template <bool kSlab>
+__device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const CUtensorMap& tmX,
+                                                 const ConvParams& p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -98,8 +117,14 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   const uint32_t stage_b_bytes = static_cast<uint32_t>(p.block_n) * kBlockK * 4;
   const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
-  const uint32_t bar_base = smem_base + p.num_stages * stage_bytes;
+  // slab form: [stages][slab slot 0][slab slot 1][tap offsets, taps * 32 ints][barriers]
+  const uint32_t slab_base = smem_base + p.num_stages * stage_bytes;
+  const uint32_t tab_base = slab_base + (kSlab ? 2u * static_cast<uint32_t>(p.slab_bytes) : 0u);
+  const uint32_t bar_base = tab_base + (kSlab ? ((static_cast<uint32_t>(p.taps) * 128u + 127u) & ~127u) : 0u);
   // barriers: full[8] @0, empty[8] @64, tmem_full[2] @128, tmem_empty[2] @144 | tmem slot @160 | abort @168
+  //           | slab_full[2] @176, slab_empty[2] @192
+  auto slab_full_bar = [&](int s) { return bar_base + 176u + 8u * s; };
+  auto slab_empty_bar = [&](int s) { return bar_base + 192u + 8u * s; };
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 64u + 8u * s; };
   auto tfull_bar = [&](int a) { return bar_base + 128u + 8u * a; };
@@ -117,11 +142,26 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
       ptx::mbar_init(tempty_bar(a), 4);
+      if constexpr (kSlab) {
+        ptx::mbar_init(slab_full_bar(a), 1);
+        ptx::mbar_init(slab_empty_bar(a), kConvGatherWarps);
+      }
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_smem();
     ptx::prefetch_tensormap(&tmW);
+    if constexpr (kSlab) ptx::prefetch_tensormap(&tmX);
+  }
+  if constexpr (kSlab) {
+    // byte offset of local k = c * taps + (ki * kw + kj) inside a slab: the same for every chunk
+    int* tab = reinterpret_cast<int*>(smem_gen + (tab_base - smem_base));
+    for (int e = threadIdx.x; e < p.taps * kBlockK; e += blockDim.x) {
+      const int c = e / p.taps;
+      const int tap = e - c * p.taps;
+      const int ki = tap / p.kw, kj = tap - ki * p.kw;
+      tab[e] = ((c * p.slab_rows + ki) * p.slab_pitch + kj) * 4;
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc_1cta(tmem_slot, kTmemCols);
@@ -136,6 +176,8 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   // unit u -> (position tile, channel tile); channel tiles of one position tile are neighbours
   auto tile_p = [&](int u) { return u / p.tiles_n; };
   auto tile_n = [&](int u) { return u % p.tiles_n; };
+  // slab form: position tile tp = (image, tile inside the image)
+  const int plane_i = p.oh * p.ow;
 
   if (warp == 0) {
     // ------------------------------------------------------- weight producer ---
@@ -145,9 +187,35 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // slab form: the next chunk to load, as (unit, chunk) with a running count for slot and parity
+      int slab_u = blockIdx.x, slab_j = 0, slab_count = 0;
+      auto issue_slab = [&]() -> bool {
+        if (slab_u >= p.total_units) return true;
+        const int slot = slab_count & 1;
+        if (!conv_wait(slab_empty_bar(slot), ((slab_count >> 1) & 1u) ^ 1u, abort_flag, p, kStatusConvSlab))
+          return false;
+        const int tp = tile_p(slab_u);
+        const int img = tp / p.tiles_pi;
+        const int oy_first = ((tp - img * p.tiles_pi) * kBlockM) / p.ow;
+        ptx::mbar_expect_tx(slab_full_bar(slot), static_cast<uint32_t>(p.slab_bytes));
+        ptx::tma_load_4d_hint(slab_base + slot * p.slab_bytes, &tmX, slab_full_bar(slot), -kConvSlabHalo,
+                              oy_first * p.sh - p.ph, slab_j * kConvSlabChannels, img, pol);
+        ++slab_count;
+        if (++slab_j == p.n_chunks) { slab_j = 0; slab_u += gridDim.x; }
+        return true;
+      };
+      if constexpr (kSlab) ok = issue_slab();
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         const int n0 = tile_n(u) * p.block_n;
+        int next_chunk_kb = 0;
         for (int kb = 0; kb < p.num_kb; ++kb) {
+          if constexpr (kSlab) {
+            if (kb == next_chunk_kb) {               // the main loop enters a chunk: fetch the one after it
+              next_chunk_kb += p.taps;
+              ok = issue_slab();
+              if (!ok) break;
+            }
+          }
           ok = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
           if (!ok) break;
           const uint32_t sb = smem_base + stage * stage_bytes + kStageABytes;
@@ -202,11 +270,22 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
-      const long long pos = static_cast<long long>(tile_p(u)) * kBlockM + q * 32 + lane;
       const int n0 = tile_n(u) * p.block_n;
-      const bool row_ok = pos < p.positions;
-      const long long img = row_ok ? pos / plane : 0;
-      const int rem = row_ok ? static_cast<int>(pos - img * plane) : 0;
+      bool row_ok;
+      long long img;
+      int rem;
+      if constexpr (kSlab) {
+        const int tp = tile_p(u);
+        img = tp / p.tiles_pi;
+        rem = (tp - static_cast<int>(img) * p.tiles_pi) * kBlockM + q * 32 + lane;
+        row_ok = rem < plane_i;
+        if (!row_ok) rem = 0;
+      } else {
+        const long long pos = static_cast<long long>(tile_p(u)) * kBlockM + q * 32 + lane;
+        row_ok = pos < p.positions;
+        img = row_ok ? pos / plane : 0;
+        rem = row_ok ? static_cast<int>(pos - img * plane) : 0;
+      }
       const int e_oy = rem / p.ow, e_ox = rem - e_oy * p.ow;
       const long long dplane = static_cast<long long>(p.dst_h) * p.dst_w;           // channel stride
       float* obase = p.out + (img * p.co) * dplane +
@@ -272,6 +351,72 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    // waits for a free stage, writes this thread's part of the row, hands the stage over
+    auto emit = [&](const float (&e)[kConvKPerThread]) -> bool {
+      // one lane per warp polls; the shuffle orders the other lanes' writes after its observation
+      int okw = 1;
+      if (lane == 0) okw = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather) ? 1 : 0;
+      if (__shfl_sync(0xffffffffu, okw, 0) == 0) return false;
+      // 32-bit shared-window addresses: row r of the stage, 16-byte chunk c at c ^ (r & 7)
+      const uint32_t row = smem_base + stage * stage_bytes + r * 128;
+#pragma unroll
+      for (int j = 0; j < kConvKPerThread / 4; ++j)
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(
+                         row + (((part * (kConvKPerThread / 4) + j) ^ (r & 7)) << 4)),
+                     "f"(e[4 * j]), "f"(e[4 * j + 1]), "f"(e[4 * j + 2]), "f"(e[4 * j + 3])
+                     : "memory");
+      ptx::fence_proxy_async_smem();               // generic writes -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(full_bar(stage));
+      if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+      return true;
+    };
+    if constexpr (kSlab) {
+      // ------------------------------------------- gather from the slab in shared memory ---
+      const int* tab = reinterpret_cast<const int*>(smem_gen + (tab_base - smem_base));
+      int chunk_count = 0;                           // chunks consumed: slot and parity of the slab barriers
+      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+        const int tp = tile_p(u);
+        const int img = tp / p.tiles_pi;
+        const int p0 = (tp - img * p.tiles_pi) * kBlockM;
+        const int oy_first = p0 / p.ow;
+        const int rem = p0 + r;
+        // rows past the end of the image read the tile's first position: their products are never stored
+        const int oy = rem < plane_i ? rem / p.ow : oy_first;
+        const int ox = rem < plane_i ? rem - oy * p.ow : 0;
+        // byte offset, inside a slab, of tap (0, 0) of channel 0 for this position (column 0 of the
+        // image is column kConvSlabHalo of the slab row)
+        const uint32_t pos_off = static_cast<uint32_t>(((oy - oy_first) * p.sh * p.slab_pitch +
+                                                        ox * p.sw - p.pw + kConvSlabHalo) * 4);
+        int kb = 0;
+        for (int j = 0; j < p.n_chunks && ok; ++j) {
+          const int slot = chunk_count & 1;
+          int okw = 1;
+          if (lane == 0)
+            okw = conv_wait(slab_full_bar(slot), (chunk_count >> 1) & 1u, abort_flag, p, kStatusConvSlab) ? 1 : 0;
+          if (__shfl_sync(0xffffffffu, okw, 0) == 0) { ok = false; break; }
+          const uint32_t base = slab_base + static_cast<uint32_t>(slot) * p.slab_bytes + pos_off;
+          for (int t = 0; t < p.taps && kb < p.num_kb; ++t, ++kb) {
+            const int4* t4 = reinterpret_cast<const int4*>(tab + t * kBlockK + part * kConvKPerThread);
+            float e[kConvKPerThread];
+#pragma unroll
+            for (int i = 0; i < kConvKPerThread / 4; ++i) {
+              const int4 o = t4[i];
+              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(e[4 * i]) : "r"(base + o.x));
+              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(e[4 * i + 1]) : "r"(base + o.y));
+              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(e[4 * i + 2]) : "r"(base + o.z));
+              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(e[4 * i + 3]) : "r"(base + o.w));
+            }
+            ok = emit(e);
+            if (!ok) break;
+          }
+          // the slab has been read (its values went through this warp's stores above): hand it back
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(slab_empty_bar(slot));
+          ++chunk_count;
+        }
+      }
+    } else
     for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
       const long long pos = static_cast<long long>(tile_p(u)) * kBlockM + r;
       const bool row_ok = pos < p.positions;
@@ -311,26 +456,6 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
         }
       };
-      // waits for a free stage, writes this thread's part of the row, hands the stage over
-      auto emit = [&](const float (&e)[kConvKPerThread]) -> bool {
-        // one lane per warp polls; the shuffle orders the other lanes' writes after its observation
-        int okw = 1;
-        if (lane == 0) okw = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather) ? 1 : 0;
-        if (__shfl_sync(0xffffffffu, okw, 0) == 0) return false;
-        // 32-bit shared-window addresses: row r of the stage, 16-byte chunk c at c ^ (r & 7)
-        const uint32_t row = smem_base + stage * stage_bytes + r * 128;
-#pragma unroll
-        for (int j = 0; j < kConvKPerThread / 4; ++j)
-          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(
-                           row + (((part * (kConvKPerThread / 4) + j) ^ (r & 7)) << 4)),
-                       "f"(e[4 * j]), "f"(e[4 * j + 1]), "f"(e[4 * j + 2]), "f"(e[4 * j + 3])
-                       : "memory");
-        ptx::fence_proxy_async_smem();               // generic writes -> visible to the tensor core
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(full_bar(stage));
-        if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
-        return true;
-      };
       issue_loads(0, na);
       for (int kb = 0; kb < p.num_kb; kb += 2) {
         if (kb + 1 < p.num_kb) issue_loads(kb + 1, nb);
@@ -354,6 +479,18 @@ conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc_1cta(tmem_base, kTmemCols);
   }
+}
+
+__global__ void __launch_bounds__(kConvThreads, 1)
+conv2d_tf32_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ ConvParams p) {
+  conv2d_tf32_body<false>(tmW, tmW, p);
+}
+
+// tmX: the input as a 4-D tensor (w, h, ci, batch) with box (w + 8, slab_rows, 32, 1).
+__global__ void __launch_bounds__(kConvThreads, 1)
+conv2d_tf32_slab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                        const __grid_constant__ ConvParams p) {
+  conv2d_tf32_body<true>(tmW, tmX, p);
 }
 
 // What the gather needs per k = (ci, ki, kj): the offset of that tap from tap (0, 0) of channel 0
@@ -557,6 +694,13 @@ conv2d_backward_data_direct_kernel(const float* __restrict__ go, const float* __
 
 inline size_t conv_smem_bytes(int block_n, int num_stages) {
   return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + block_n * kBlockK * 4) + kBarrierBytes;
+}
+
+// The slab form: the stage ring, two slabs, the tap-offset table, the barriers.
+inline size_t conv_slab_smem_bytes(int block_n, int num_stages, int slab_bytes, int taps) {
+  return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + block_n * kBlockK * 4) +
+         2 * static_cast<size_t>(slab_bytes) + ((static_cast<size_t>(taps) * 128 + 127) & ~static_cast<size_t>(127)) +
+         kBarrierBytes;
 }
 
 }  // namespace fnn

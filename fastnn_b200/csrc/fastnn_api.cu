@@ -77,6 +77,7 @@ struct Tunables {
   int group_m = 0;              // FASTNN_B200_GROUP_M: tile rows per rasterisation group
   int l2 = -1;                  // FASTNN_B200_L2=<C><A><B>: eviction policies of stores and loads
   bool no_wide = false;         // FASTNN_B200_WIDE=0: CTA pairs keep 256-wide tiles
+  bool conv_no_slab = false;    // FASTNN_B200_CONV_SLAB=0: the convolution gathers from global memory only
   int pace = 7;                 // FASTNN_B200_PACE=<0..8>: eighths of a tile's time its gather stores are spread over
 };
 const Tunables& tunables() {
@@ -94,6 +95,7 @@ const Tunables& tunables() {
     v.group_m = num("FASTNN_B200_GROUP_M", 0);
     v.l2 = num("FASTNN_B200_L2", -1);
     v.no_wide = num("FASTNN_B200_WIDE", 1) == 0;
+    v.conv_no_slab = num("FASTNN_B200_CONV_SLAB", 1) == 0;
     v.pace = num("FASTNN_B200_PACE", 7);
     if (v.pace < 0 || v.pace > 8) v.pace = 7;
     return v;
@@ -984,6 +986,8 @@ extern "C" int fastnn_cuda_init(int device_id) {
                                    static_cast<int>(kMaxDynSmem)));
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
+  FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_tf32_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kMaxDynSmem)));
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::attention_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_wgrad_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1269,8 +1273,6 @@ static int conv_launch(DeviceState* st, const ConvCall& c, cudaStream_t s) {
   float* ws_ptr = nullptr;
   if (workspace_reserve(st, st->workspaces, s, tab_bytes + w_bytes, &ws_ptr) != 0) return -1;
   int4* ktab = reinterpret_cast<int4*>(ws_ptr);
-  fnn::conv_ktab_kernel<<<ceil_div(k_pad, 256), 256, 0, s>>>(ktab, k_pad, k, c.kh, c.kw, c.h, c.w);
-  g_launches.fetch_add(1, std::memory_order_relaxed);
   if (copy_w) {
     float* wdst = reinterpret_cast<float*>(reinterpret_cast<char*>(ws_ptr) + tab_bytes);
     long long blocks = (1ll * c.co * k_pad + 255) / 256;
@@ -1310,21 +1312,80 @@ static int conv_launch(DeviceState* st, const ConvCall& c, cudaStream_t s) {
   if (!encode_map(&tmW, wsrc, static_cast<uint64_t>(w_ld == k ? k : w_ld), c.co, 1, w_ld * 4ull,
                   w_ld * 4ull * c.co, fnn::kBlockK, p.block_n))
     return -1;
+  // The slab form (input rows of a tile staged in shared memory by TMA) when the rows can be
+  // addressed by a tensor map (16-byte row pitch and base), the kernel overhangs the image by at most
+  // the four halo columns on either side, and two slabs fit beside at least three pipeline stages.
+  CUtensorMap tmX;
+  bool slab = false;
+  const Tunables& tune = tunables();
+  const int plane = c.oh * c.ow;
+  if (!tune.conv_no_slab && (c.w & 3) == 0 && aligned16(c.input) && c.w + 2 * fnn::kConvSlabHalo <= 256 &&
+      c.pw <= fnn::kConvSlabHalo && (c.ow - 1) * c.sw - c.pw + c.kw - 1 <= c.w - 1 + fnn::kConvSlabHalo &&
+      c.pw > -(1 << 20) && c.batch <= 0x7fffffff / ((plane + fnn::kBlockM - 1) / fnn::kBlockM)) {
+    const int tiles_pi = (plane + fnn::kBlockM - 1) / fnn::kBlockM;
+    int rows_out = 1;                               // output rows one tile can touch
+    for (int t = 0; t < tiles_pi; ++t) {
+      const int first = t * fnn::kBlockM;
+      const int last = first + fnn::kBlockM - 1 < plane ? first + fnn::kBlockM - 1 : plane - 1;
+      const int rows = last / c.ow - first / c.ow + 1;
+      if (rows > rows_out) rows_out = rows;
+    }
+    const long long slab_rows = 1ll * (rows_out - 1) * c.sh + c.kh;
+    const int pitch = c.w + 2 * fnn::kConvSlabHalo;
+    const long long slab_bytes = 1ll * fnn::kConvSlabChannels * slab_rows * pitch * 4;
+    const int taps = c.kh * c.kw;
+    const long long fixed = 1024 + fnn::kBarrierBytes + ((taps * 128ll + 127) & ~127ll) + 2 * slab_bytes;
+    const long long room = static_cast<long long>(kMaxDynSmem) - fixed;
+    if (slab_rows <= 256 && room >= 3 * static_cast<long long>(stage)) {
+      int slab_stages = static_cast<int>(room / static_cast<long long>(stage));
+      if (slab_stages > fnn::kMaxStages) slab_stages = fnn::kMaxStages;
+      const EncodeTiledFn encode = g_encode.load(std::memory_order_acquire);
+      cuuint64_t dims[4] = {static_cast<cuuint64_t>(c.w), static_cast<cuuint64_t>(c.h),
+                            static_cast<cuuint64_t>(c.ci), static_cast<cuuint64_t>(c.batch)};
+      cuuint64_t strides[3] = {c.w * 4ull, 4ull * c.w * c.h, 4ull * c.w * c.h * c.ci};
+      cuuint32_t box[4] = {static_cast<cuuint32_t>(pitch), static_cast<cuuint32_t>(slab_rows),
+                           static_cast<cuuint32_t>(fnn::kConvSlabChannels), 1};
+      cuuint32_t estr[4] = {1, 1, 1, 1};
+      if (encode != nullptr && strides[2] < (1ull << 40) &&
+          encode(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(c.input), dims, strides, box,
+                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
+        slab = true;
+        p.tiles_pi = tiles_pi;
+        p.taps = taps;
+        p.n_chunks = ceil_div(c.ci, fnn::kConvSlabChannels);
+        p.slab_rows = static_cast<int>(slab_rows);
+        p.slab_pitch = pitch;
+        p.slab_bytes = static_cast<int>(slab_bytes);
+        p.num_stages = slab_stages;
+        p.tiles_p = c.batch * tiles_pi;
+        p.total_units = p.tiles_p * p.tiles_n;
+      }
+    }
+  }
   const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(fnn::kConvThreads, 1, 1);
-  cfg.dynamicSmemBytes = fnn::conv_smem_bytes(p.block_n, p.num_stages);
+  cfg.dynamicSmemBytes = slab ? fnn::conv_slab_smem_bytes(p.block_n, p.num_stages, p.slab_bytes, p.taps)
+                              : fnn::conv_smem_bytes(p.block_n, p.num_stages);
   cfg.stream = s;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::conv2d_tf32_kernel, tmW, p));
+  if (slab) {
+    FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::conv2d_tf32_slab_kernel, tmW, tmX, p));
+  } else {
+    // the global-memory gather reads what depends on k alone from a table written just before
+    fnn::conv_ktab_kernel<<<ceil_div(k_pad, 256), 256, 0, s>>>(ktab, k_pad, k, c.kh, c.kw, c.h, c.w);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::conv2d_tf32_kernel, tmW, p));
+  }
   g_launches.fetch_add(1, std::memory_order_relaxed);
-  t_last = LastCall{5, p.block_n, 1, grid};
+  t_last = LastCall{slab ? 9 : 5, p.block_n, 1, grid};
   return 0;
 }
 

@@ -48,7 +48,7 @@ def test_conv2d_matches_the_cpu_loops(gpu, cfg):
     got = f.conv2d_forward(torch.from_numpy(x).cuda(), torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda(),
                            stride=stride, padding=padding)
     torch.cuda.synchronize()
-    assert f.last_path()["path"] == 5
+    assert f.last_path()["path"] in (5, 9)
     _check(got.cpu().numpy(), want, ci * kh * kw, x, wt, str(cfg))
     assert f.device_status() == 0
 
@@ -101,3 +101,49 @@ def test_conv2d_with_a_seven_by_seven_kernel_and_stride_two(gpu):
     got = f.conv2d_forward(torch.from_numpy(x).cuda(), torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda(),
                            stride=(2, 2), padding=(3, 3))
     _check(got.cpu().numpy(), want, 3 * 49, x, wt, "7x7 stride 2")
+
+
+@pytest.mark.parametrize("cfg", [
+    # n, ci, co, h, w, kh, kw, stride, padding -- shapes whose rows a tensor map can address (w % 4 == 0)
+    (2, 64, 128, 56, 56, 3, 3, (1, 1), (1, 1)),      # the benchmark layer, two images: 2 chunks, tiles of 2.3 rows
+    (2, 48, 40, 24, 24, 3, 3, (1, 1), (1, 1)),       # second chunk half out of range (48 = 32 + 16 channels)
+    (3, 100, 300, 12, 12, 3, 3, (1, 1), (1, 1)),     # four chunks, three channel tiles, 144 positions per image
+    (2, 8, 16, 40, 36, 5, 5, (1, 1), (2, 2)),        # 25 taps, padding 2
+    (2, 3, 32, 12, 64, 7, 7, (1, 1), (3, 3)),        # 49 taps, padding 3 (three of the four halo columns)
+    (2, 16, 24, 20, 16, 3, 3, (2, 1), (0, 1)),       # mixed stride and padding
+    (5, 32, 64, 8, 8, 3, 3, (1, 1), (1, 1)),         # 64 positions per image: half of every tile is past the image
+    (1, 4, 8, 16, 248, 1, 3, (1, 1), (0, 1)),        # the widest row a slab takes (248 + 8 columns), one-row kernel
+    (2, 12, 20, 16, 16, 3, 4, (1, 1), (1, 4)),       # horizontal padding equal to the halo
+])
+def test_conv2d_from_rows_staged_in_shared_memory(gpu, cfg):
+    """The form that brings every tile's input rows into shared memory by TMA (path 9)."""
+    import torch
+    f = gpu
+    n, ci, co, h, w, kh, kw, stride, padding = cfg
+    x, wt, b = _case(n, ci, co, h, w, kh, kw, 100 + sum(cfg[:7]))
+    want = oracle.conv2d(x, wt, b, stride, padding)
+    got = f.conv2d_forward(torch.from_numpy(x).cuda(), torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda(),
+                           stride=stride, padding=padding)
+    torch.cuda.synchronize()
+    assert f.last_path()["path"] == 9, f.last_path()
+    _check(got.cpu().numpy(), want, ci * kh * kw, x, wt, str(cfg))
+    assert f.device_status() == 0
+
+
+@pytest.mark.parametrize("cfg", [
+    (2, 8, 16, 16, 16, 3, 3, (1, 1), (5, 5)),        # padding wider than the halo
+    (2, 8, 16, 16, 18, 3, 3, (1, 1), (1, 1)),        # row pitch not a multiple of 16 bytes
+    (1, 4, 8, 8, 260, 1, 3, (1, 1), (0, 1)),         # row wider than a TMA box
+    (2, 3, 32, 32, 32, 7, 7, (2, 2), (3, 3)),        # 21 input rows per tile: two slabs do not fit
+])
+def test_conv2d_shapes_the_staged_form_leaves_to_the_global_gather(gpu, cfg):
+    import torch
+    f = gpu
+    n, ci, co, h, w, kh, kw, stride, padding = cfg
+    x, wt, b = _case(n, ci, co, h, w, kh, kw, 200 + sum(cfg[:7]))
+    want = oracle.conv2d(x, wt, b, stride, padding)
+    got = f.conv2d_forward(torch.from_numpy(x).cuda(), torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda(),
+                           stride=stride, padding=padding)
+    torch.cuda.synchronize()
+    assert f.last_path()["path"] == 5, f.last_path()
+    _check(got.cpu().numpy(), want, ci * kh * kw, x, wt, str(cfg))
