@@ -64,9 +64,12 @@ struct ConvParams {
   long long spin_budget;
 };
 
-enum : unsigned int { kStatusConvGather = 0x301, kStatusConvSlab = 0x302 };
+enum : unsigned int { kStatusConvGather = 0x301, kStatusConvSlab = 0x302, kStatusConvSlabFull = 0x303 };
 constexpr int kConvSlabChannels = 32;
 constexpr int kConvSlabHalo = 4;      // zero columns either side of a row (keeps the TMA x coordinate aligned)
+constexpr int kConvSlabStages = 4;    // pipeline stages of the slab form: one per group of gather warps
+constexpr int kConvSlabTmemA = 128;   // first tensor-memory column of its A slots (4 x 32 columns, between the
+                                      // two accumulators, which are at most 128 columns wide in this form)
 constexpr int kConvGatherWarps = 16;
 constexpr int kConvThreads = 32 * (6 + kConvGatherWarps);   // producer, MMA issuer, 4 epilogue warps, gather warps
 constexpr int kConvKPerThread = kBlockK / (kConvGatherWarps / 4);   // k's of a stage row one gather thread fills
@@ -116,7 +119,10 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
   const int lane = threadIdx.x & 31;
 
   const uint32_t stage_b_bytes = static_cast<uint32_t>(p.block_n) * kBlockK * 4;
-  const uint32_t stage_bytes = kStageABytes + stage_b_bytes;
+  // slab form: the A operand goes from the gather warps' registers into tensor memory (32 columns
+  // per stage beside the accumulators), so a stage of shared memory holds the weight tile alone
+  const uint32_t stage_a_bytes = kSlab ? 0u : static_cast<uint32_t>(kStageABytes);
+  const uint32_t stage_bytes = stage_a_bytes + stage_b_bytes;
   // slab form: [stages][slab slot 0][slab slot 1][tap offsets, taps * 32 ints][barriers]
   const uint32_t slab_base = smem_base + p.num_stages * stage_bytes;
   const uint32_t tab_base = slab_base + (kSlab ? 2u * static_cast<uint32_t>(p.slab_bytes) : 0u);
@@ -136,7 +142,9 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.num_stages; ++s) {
-      ptx::mbar_init(full_bar(s), 1 + kConvGatherWarps);   // the weight load's expect_tx + gather warps
+      // the weight load's expect_tx + the gather warps that fill the stage: all sixteen (a quarter of
+      // each row's k's each), or in the slab form the four that own this k-block (whole rows)
+      ptx::mbar_init(full_bar(s), kSlab ? 1 + kConvGatherWarps / 4 : 1 + kConvGatherWarps);
       ptx::mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -218,7 +226,7 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
           }
           ok = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
           if (!ok) break;
-          const uint32_t sb = smem_base + stage * stage_bytes + kStageABytes;
+          const uint32_t sb = smem_base + stage * stage_bytes + stage_a_bytes;
           ptx::mbar_expect_tx(full_bar(stage), stage_b_bytes);
           ptx::tma_load_3d_hint(sb, &tmW, full_bar(stage), kb * kBlockK, n0, 0, pol);
           if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
@@ -245,12 +253,18 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
           if (!ok) break;
           ptx::tc_fence_after_sync();
           const uint32_t sa = smem_base + stage * stage_bytes;
-          const uint32_t sb = sa + kStageABytes;
+          const uint32_t sb = sa + stage_a_bytes;
 #pragma unroll
           for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
-            const uint64_t da = ptx::smem_desc_sw128(sa + ks * 32u, 16u, 1024u);
             const uint64_t db = ptx::smem_desc_sw128(sb + ks * 32u, 16u, 1024u);
-            ptx::mma_tf32_1cta(tmem_d, da, db, idesc, first);
+            if constexpr (kSlab) {
+              // A: 128 lanes x 8 columns of this stage's tensor-memory slot
+              ptx::mma_tf32_1cta_ts(tmem_d, tmem_base + kConvSlabTmemA + stage * kBlockK + ks * kUmmaK, db,
+                                    idesc, first);
+            } else {
+              const uint64_t da = ptx::smem_desc_sw128(sa + ks * 32u, 16u, 1024u);
+              ptx::mma_tf32_1cta(tmem_d, da, db, idesc, first);
+            }
             first = 1u;
           }
           ptx::mma_commit_1cta(empty_bar(stage));
@@ -343,8 +357,10 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
     //    table a small kernel wrote before this one (all lanes read the same entry).
     ptx::grid_dep_wait();
     const int g = warp - kConvGatherWarp0;
-    const int r = (g & 3) * 32 + lane;                            // row of the A stage = position
-    const int part = g >> 2;                                      // which k sub-range of the row
+    // row of the A stage = position.  The slab form writes its rows into tensor memory, where a
+    // warp reaches the 32 lanes of quadrant warp % 4 only
+    const int r = (kSlab ? (warp & 3) : (g & 3)) * 32 + lane;
+    const int part = g >> 2;                                      // which k sub-range of the row (slab form: which k-blocks)
     const long long plane = static_cast<long long>(p.oh) * p.ow;
     const int hw = p.h * p.w;
     const bool taps_fit_32 = p.kh * p.kw <= 32;
@@ -375,6 +391,7 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
       // ------------------------------------------- gather from the slab in shared memory ---
       const int* tab = reinterpret_cast<const int*>(smem_gen + (tab_base - smem_base));
       int chunk_count = 0;                           // chunks consumed: slot and parity of the slab barriers
+      int kb_count = 0;                              // k-blocks passed, over all units: whose turn a stage is
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         const int tp = tile_p(u);
         const int img = tp / p.tiles_pi;
@@ -393,22 +410,41 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
           const int slot = chunk_count & 1;
           int okw = 1;
           if (lane == 0)
-            okw = conv_wait(slab_full_bar(slot), (chunk_count >> 1) & 1u, abort_flag, p, kStatusConvSlab) ? 1 : 0;
+            okw = conv_wait(slab_full_bar(slot), (chunk_count >> 1) & 1u, abort_flag, p, kStatusConvSlabFull) ? 1 : 0;
           if (__shfl_sync(0xffffffffu, okw, 0) == 0) { ok = false; break; }
           const uint32_t base = slab_base + static_cast<uint32_t>(slot) * p.slab_bytes + pos_off;
           for (int t = 0; t < p.taps && kb < p.num_kb; ++t, ++kb) {
-            const int4* t4 = reinterpret_cast<const int4*>(tab + t * kBlockK + part * kConvKPerThread);
-            float e[kConvKPerThread];
+            // A warp fills 32 rows (its tensor-memory lane quadrant) of every fourth k-block
+            // (g >> 2 = k-block count mod 4), all 32 k's of a row per thread, with one tcgen05.st.
+            // Written through shared memory instead, every fill needed a fence.proxy.async, which
+            // took ~900 clocks and held up the MMA issue as well: the tensor pipe stayed at 23 %.
+            if ((kb_count & 3) == part) {
+              // the row's 32 values into registers first: the loads need nothing but the slab
+              const int4* t4 = reinterpret_cast<const int4*>(tab + t * kBlockK);
+              uint32_t e[kBlockK];
 #pragma unroll
-            for (int i = 0; i < kConvKPerThread / 4; ++i) {
-              const int4 o = t4[i];
-              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(e[4 * i]) : "r"(base + o.x));
-              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(e[4 * i + 1]) : "r"(base + o.y));
-              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(e[4 * i + 2]) : "r"(base + o.z));
-              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(e[4 * i + 3]) : "r"(base + o.w));
+              for (int i = 0; i < kBlockK / 4; ++i) {
+                const int4 o = t4[i];
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(e[4 * i]) : "r"(base + o.x));
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(e[4 * i + 1]) : "r"(base + o.y));
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(e[4 * i + 2]) : "r"(base + o.z));
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(e[4 * i + 3]) : "r"(base + o.w));
+              }
+              int okw2 = 1;
+              if (lane == 0)
+                okw2 = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather) ? 1 : 0;
+              if (__shfl_sync(0xffffffffu, okw2, 0) == 0) { ok = false; break; }
+              // the tensor core has read this slot's previous contents (its commit released the stage)
+              ptx::tc_fence_after_sync();
+              ptx::tmem_st_32x32(tmem_base + (static_cast<uint32_t>(r & ~31) << 16) + kConvSlabTmemA +
+                                     static_cast<uint32_t>(stage * kBlockK), e);
+              ptx::tmem_st_wait();                     // in tensor memory before the tensor core is told
+              ptx::tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(full_bar(stage));
             }
-            ok = emit(e);
-            if (!ok) break;
+            ++kb_count;
+            if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
           }
           // the slab has been read (its values went through this warp's stores above): hand it back
           __syncwarp();
@@ -696,9 +732,9 @@ inline size_t conv_smem_bytes(int block_n, int num_stages) {
   return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + block_n * kBlockK * 4) + kBarrierBytes;
 }
 
-// The slab form: the stage ring, two slabs, the tap-offset table, the barriers.
+// The slab form: the stage ring (weight tiles only), two slabs, the tap-offset table, the barriers.
 inline size_t conv_slab_smem_bytes(int block_n, int num_stages, int slab_bytes, int taps) {
-  return 1024 + static_cast<size_t>(num_stages) * (kStageABytes + block_n * kBlockK * 4) +
+  return 1024 + static_cast<size_t>(num_stages) * (block_n * kBlockK * 4) +
          2 * static_cast<size_t>(slab_bytes) + ((static_cast<size_t>(taps) * 128 + 127) & ~static_cast<size_t>(127)) +
          kBarrierBytes;
 }

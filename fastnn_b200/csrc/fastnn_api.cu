@@ -1298,23 +1298,12 @@ static int conv_launch(DeviceState* st, const ConvCall& c, cudaStream_t s) {
   p.dst_h = c.dst_h; p.dst_w = c.dst_w; p.dst_y0 = c.dst_y0; p.dst_x0 = c.dst_x0;
   p.dst_sy = c.dst_sy; p.dst_sx = c.dst_sx;
   p.block_n = c.co >= fnn::kMaxBlockN ? fnn::kMaxBlockN : ceil_div(c.co, 32) * 32;
-  const long long tiles_p = (positions + fnn::kBlockM - 1) / fnn::kBlockM;
-  p.tiles_n = ceil_div(c.co, p.block_n);
-  if (tiles_p * p.tiles_n > 0x7fffffffll) return -1;
-  p.tiles_p = static_cast<int>(tiles_p);
-  p.total_units = static_cast<int>(tiles_p * p.tiles_n);
-  const size_t stage = fnn::kStageABytes + static_cast<size_t>(p.block_n) * fnn::kBlockK * 4;
-  int stages = static_cast<int>((kMaxDynSmem - 1024 - fnn::kBarrierBytes) / stage);
-  p.num_stages = stages > fnn::kMaxStages ? fnn::kMaxStages : stages;
-  p.x = c.input; p.ktab = ktab; p.bias = c.bias; p.out = c.output; p.act = c.act;
-  p.status = st->status; p.spin_budget = st->spin_budget;
-  CUtensorMap tmW;
-  if (!encode_map(&tmW, wsrc, static_cast<uint64_t>(w_ld == k ? k : w_ld), c.co, 1, w_ld * 4ull,
-                  w_ld * 4ull * c.co, fnn::kBlockK, p.block_n))
-    return -1;
   // The slab form (input rows of a tile staged in shared memory by TMA) when the rows can be
   // addressed by a tensor map (16-byte row pitch and base), the kernel overhangs the image by at most
-  // the four halo columns on either side, and two slabs fit beside at least three pipeline stages.
+  // the four halo columns on either side, and two slabs fit beside four pipeline stages.  (Four
+  // stages, no fewer: its four groups of gather warps each take every fourth k-block, and a group
+  // that could run more than one use of a stage ahead of the tensor core would mistake the phase of
+  // the stage's barrier.)
   CUtensorMap tmX;
   bool slab = false;
   const Tunables& tune = tunables();
@@ -1336,9 +1325,12 @@ static int conv_launch(DeviceState* st, const ConvCall& c, cudaStream_t s) {
     const int taps = c.kh * c.kw;
     const long long fixed = 1024 + fnn::kBarrierBytes + ((taps * 128ll + 127) & ~127ll) + 2 * slab_bytes;
     const long long room = static_cast<long long>(kMaxDynSmem) - fixed;
-    if (slab_rows <= 256 && room >= 3 * static_cast<long long>(stage)) {
-      int slab_stages = static_cast<int>(room / static_cast<long long>(stage));
-      if (slab_stages > fnn::kMaxStages) slab_stages = fnn::kMaxStages;
+    // four stages of the weight tile alone (A lives in tensor memory), channel tiles of at most 128
+    // columns (the A slots take the tensor-memory columns between the two accumulators)
+    int slab_bn = p.block_n > 128 ? 128 : p.block_n;
+    const int slab_stages = fnn::kConvSlabStages;
+    if (room < slab_stages * (1ll * slab_bn * fnn::kBlockK * 4)) slab_bn = 0;
+    if (slab_rows <= 256 && slab_bn > 0) {
       const EncodeTiledFn encode = g_encode.load(std::memory_order_acquire);
       cuuint64_t dims[4] = {static_cast<cuuint64_t>(c.w), static_cast<cuuint64_t>(c.h),
                             static_cast<cuuint64_t>(c.ci), static_cast<cuuint64_t>(c.batch)};
@@ -1351,6 +1343,7 @@ static int conv_launch(DeviceState* st, const ConvCall& c, cudaStream_t s) {
                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
         slab = true;
+        p.block_n = slab_bn;
         p.tiles_pi = tiles_pi;
         p.taps = taps;
         p.n_chunks = ceil_div(c.ci, fnn::kConvSlabChannels);
@@ -1358,11 +1351,25 @@ static int conv_launch(DeviceState* st, const ConvCall& c, cudaStream_t s) {
         p.slab_pitch = pitch;
         p.slab_bytes = static_cast<int>(slab_bytes);
         p.num_stages = slab_stages;
-        p.tiles_p = c.batch * tiles_pi;
-        p.total_units = p.tiles_p * p.tiles_n;
       }
     }
   }
+  const long long tiles_p = slab ? 1ll * c.batch * p.tiles_pi : (positions + fnn::kBlockM - 1) / fnn::kBlockM;
+  p.tiles_n = ceil_div(c.co, p.block_n);
+  if (tiles_p * p.tiles_n > 0x7fffffffll) return -1;
+  p.tiles_p = static_cast<int>(tiles_p);
+  p.total_units = static_cast<int>(tiles_p * p.tiles_n);
+  if (!slab) {
+    const size_t stage = fnn::kStageABytes + static_cast<size_t>(p.block_n) * fnn::kBlockK * 4;
+    int stages = static_cast<int>((kMaxDynSmem - 1024 - fnn::kBarrierBytes) / stage);
+    p.num_stages = stages > fnn::kMaxStages ? fnn::kMaxStages : stages;
+  }
+  p.x = c.input; p.ktab = ktab; p.bias = c.bias; p.out = c.output; p.act = c.act;
+  p.status = st->status; p.spin_budget = st->spin_budget;
+  CUtensorMap tmW;
+  if (!encode_map(&tmW, wsrc, static_cast<uint64_t>(w_ld == k ? k : w_ld), c.co, 1, w_ld * 4ull,
+                  w_ld * 4ull * c.co, fnn::kBlockK, p.block_n))
+    return -1;
   const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));

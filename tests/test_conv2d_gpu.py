@@ -109,7 +109,7 @@ def test_conv2d_with_a_seven_by_seven_kernel_and_stride_two(gpu):
     (2, 48, 40, 24, 24, 3, 3, (1, 1), (1, 1)),       # second chunk half out of range (48 = 32 + 16 channels)
     (3, 100, 300, 12, 12, 3, 3, (1, 1), (1, 1)),     # four chunks, three channel tiles, 144 positions per image
     (2, 8, 16, 40, 36, 5, 5, (1, 1), (2, 2)),        # 25 taps, padding 2
-    (2, 3, 32, 12, 64, 7, 7, (1, 1), (3, 3)),        # 49 taps, padding 3 (three of the four halo columns)
+    (2, 3, 32, 8, 32, 7, 7, (1, 1), (3, 3)),         # 49 taps, padding 3 (three of the four halo columns)
     (2, 16, 24, 20, 16, 3, 3, (2, 1), (0, 1)),       # mixed stride and padding
     (5, 32, 64, 8, 8, 3, 3, (1, 1), (1, 1)),         # 64 positions per image: half of every tile is past the image
     (1, 4, 8, 16, 248, 1, 3, (1, 1), (0, 1)),        # the widest row a slab takes (248 + 8 columns), one-row kernel
