@@ -67,9 +67,12 @@ struct ConvParams {
 enum : unsigned int { kStatusConvGather = 0x301, kStatusConvSlab = 0x302, kStatusConvSlabFull = 0x303 };
 constexpr int kConvSlabChannels = 32;
 constexpr int kConvSlabHalo = 4;      // zero columns either side of a row (keeps the TMA x coordinate aligned)
-constexpr int kConvSlabStages = 4;    // pipeline stages of the slab form: one per group of gather warps
-constexpr int kConvSlabTmemA = 128;   // first tensor-memory column of its A slots (4 x 32 columns, between the
-                                      // two accumulators, which are at most 128 columns wide in this form)
+constexpr int kConvSlabMinStages = 4;  // the slab form needs one stage per group of gather warps at least
+// Tensor-memory column of the A slot of stage s: four slots of 32 columns between the two accumulators
+// (which are at most 128 columns wide in this form), four more after the second one.
+__host__ __device__ constexpr uint32_t conv_slab_tmem_a(int s) {
+  return s < 4 ? 128u + 32u * static_cast<uint32_t>(s) : 384u + 32u * static_cast<uint32_t>(s - 4);
+}
 constexpr int kConvGatherWarps = 16;
 constexpr int kConvThreads = 32 * (6 + kConvGatherWarps);   // producer, MMA issuer, 4 epilogue warps, gather warps
 constexpr int kConvKPerThread = kBlockK / (kConvGatherWarps / 4);   // k's of a stage row one gather thread fills
@@ -89,13 +92,16 @@ __device__ __forceinline__ float ldg_if(const float* ptr, uint32_t cond) {
   return v;
 }
 
-// Bounded wait, as in the GEMM kernels.
+// Bounded wait, as in the GEMM kernels.  sleep_ns > 0: the waiter sleeps between probes -- for the
+// roles that wait long and are not on the critical path (22 warps share four schedulers here, and a
+// warp that probes at full rate takes issue slots from the thread that issues the MMAs).
 __device__ __forceinline__ bool conv_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          const ConvParams& p, unsigned int code) {
+                                          const ConvParams& p, unsigned int code, unsigned int sleep_ns = 0) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int it = 0;
   while (true) {
+    if (sleep_ns) __nanosleep(sleep_ns);
     if (ptx::mbar_try_wait(bar, parity)) return true;
     if ((++it & 63) == 0) {
       if (*abort_flag) return false;
@@ -200,7 +206,7 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
       auto issue_slab = [&]() -> bool {
         if (slab_u >= p.total_units) return true;
         const int slot = slab_count & 1;
-        if (!conv_wait(slab_empty_bar(slot), ((slab_count >> 1) & 1u) ^ 1u, abort_flag, p, kStatusConvSlab))
+        if (!conv_wait(slab_empty_bar(slot), ((slab_count >> 1) & 1u) ^ 1u, abort_flag, p, kStatusConvSlab, 64))
           return false;
         const int tp = tile_p(slab_u);
         const int img = tp / p.tiles_pi;
@@ -224,7 +230,7 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
               if (!ok) break;
             }
           }
-          ok = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout);
+          ok = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusProducerTimeout, kSlab ? 32 : 0);
           if (!ok) break;
           const uint32_t sb = smem_base + stage * stage_bytes + stage_a_bytes;
           ptx::mbar_expect_tx(full_bar(stage), stage_b_bytes);
@@ -242,12 +248,41 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      // slab form: state of the current stage
+      const uint64_t s_db0 = ptx::smem_desc_sw128(smem_base + stage_a_bytes, 16u, 1024u);
+      const uint64_t s_db_step = stage_bytes >> 4;
+      uint64_t s_db = s_db0;
+      uint32_t s_full = full_bar(0);
+      uint32_t s_acol = tmem_base + conv_slab_tmem_a(0);
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         ok = conv_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBlockN);
         uint32_t first = 0u;
+        if constexpr (kSlab) {
+          // A from tensor memory.  Everything that depends on the stage alone (barrier addresses, the
+          // weight tile's descriptor, the A slot's column) advances by a constant, so a k-block costs
+          // this thread a dozen instructions.
+          for (int kb = 0; kb < p.num_kb; ++kb) {
+            ok = conv_wait(s_full, phase, abort_flag, p, kStatusMmaTimeout);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
+              ptx::mma_tf32_1cta_ts(tmem_d, s_acol + ks * kUmmaK, s_db + ks * 2u, idesc, first);
+              first = 1u;
+            }
+            ptx::mma_commit_1cta(s_full + 64u);        // the stage's empty barrier
+            if (++stage == p.num_stages) {
+              stage = 0; phase ^= 1u;
+              s_full = full_bar(0); s_db = s_db0; s_acol = tmem_base + conv_slab_tmem_a(0);
+            } else {
+              s_full += 8u; s_db += s_db_step;
+              s_acol += (stage == 4) ? 160u : 32u;     // slots 0-3 at columns 128.., slots 4-7 at 384..
+            }
+          }
+        } else
         for (int kb = 0; kb < p.num_kb; ++kb) {
           ok = conv_wait(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout);
           if (!ok) break;
@@ -259,8 +294,7 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
             const uint64_t db = ptx::smem_desc_sw128(sb + ks * 32u, 16u, 1024u);
             if constexpr (kSlab) {
               // A: 128 lanes x 8 columns of this stage's tensor-memory slot
-              ptx::mma_tf32_1cta_ts(tmem_d, tmem_base + kConvSlabTmemA + stage * kBlockK + ks * kUmmaK, db,
-                                    idesc, first);
+              ptx::mma_tf32_1cta_ts(tmem_d, tmem_base + conv_slab_tmem_a(stage) + ks * kUmmaK, db, idesc, first);
             } else {
               const uint64_t da = ptx::smem_desc_sw128(sa + ks * 32u, 16u, 1024u);
               ptx::mma_tf32_1cta(tmem_d, da, db, idesc, first);
@@ -304,7 +338,7 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
       const long long dplane = static_cast<long long>(p.dst_h) * p.dst_w;           // channel stride
       float* obase = p.out + (img * p.co) * dplane +
                      static_cast<long long>(p.dst_y0 + e_oy * p.dst_sy) * p.dst_w + p.dst_x0 + e_ox * p.dst_sx;
-      ok = conv_wait(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout);
+      ok = conv_wait(tfull_bar(acc), acc_phase, abort_flag, p, kStatusEpilogueTimeout, kSlab ? 256 : 0);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
@@ -410,7 +444,7 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
           const int slot = chunk_count & 1;
           int okw = 1;
           if (lane == 0)
-            okw = conv_wait(slab_full_bar(slot), (chunk_count >> 1) & 1u, abort_flag, p, kStatusConvSlabFull) ? 1 : 0;
+            okw = conv_wait(slab_full_bar(slot), (chunk_count >> 1) & 1u, abort_flag, p, kStatusConvSlabFull, 32) ? 1 : 0;
           if (__shfl_sync(0xffffffffu, okw, 0) == 0) { ok = false; break; }
           const uint32_t base = slab_base + static_cast<uint32_t>(slot) * p.slab_bytes + pos_off;
           for (int t = 0; t < p.taps && kb < p.num_kb; ++t, ++kb) {
@@ -432,12 +466,11 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
               }
               int okw2 = 1;
               if (lane == 0)
-                okw2 = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather) ? 1 : 0;
+                okw2 = conv_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather, 32) ? 1 : 0;
               if (__shfl_sync(0xffffffffu, okw2, 0) == 0) { ok = false; break; }
               // the tensor core has read this slot's previous contents (its commit released the stage)
               ptx::tc_fence_after_sync();
-              ptx::tmem_st_32x32(tmem_base + (static_cast<uint32_t>(r & ~31) << 16) + kConvSlabTmemA +
-                                     static_cast<uint32_t>(stage * kBlockK), e);
+              ptx::tmem_st_32x32(tmem_base + (static_cast<uint32_t>(r & ~31) << 16) + conv_slab_tmem_a(stage), e);
               ptx::tmem_st_wait();                     // in tensor memory before the tensor core is told
               ptx::tc_fence_before_sync();
               __syncwarp();

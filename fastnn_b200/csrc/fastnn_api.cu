@@ -1325,11 +1325,14 @@ static int conv_launch(DeviceState* st, const ConvCall& c, cudaStream_t s) {
     const int taps = c.kh * c.kw;
     const long long fixed = 1024 + fnn::kBarrierBytes + ((taps * 128ll + 127) & ~127ll) + 2 * slab_bytes;
     const long long room = static_cast<long long>(kMaxDynSmem) - fixed;
-    // four stages of the weight tile alone (A lives in tensor memory), channel tiles of at most 128
-    // columns (the A slots take the tensor-memory columns between the two accumulators)
+    // stages of the weight tile alone (A lives in tensor memory): four to eight, as many as fit --
+    // a stage is only 256 clocks of tensor work, and the ring has to cover the latency of a weight
+    // load; channel tiles of at most 128 columns (the A slots take the tensor-memory columns the
+    // accumulators leave)
     int slab_bn = p.block_n > 128 ? 128 : p.block_n;
-    const int slab_stages = fnn::kConvSlabStages;
-    if (room < slab_stages * (1ll * slab_bn * fnn::kBlockK * 4)) slab_bn = 0;
+    long long fit = room / (1ll * slab_bn * fnn::kBlockK * 4);
+    if (fit < fnn::kConvSlabMinStages) slab_bn = 0;
+    const int slab_stages = fit > fnn::kMaxStages ? fnn::kMaxStages : static_cast<int>(fit);
     if (slab_rows <= 256 && slab_bn > 0) {
       const EncodeTiledFn encode = g_encode.load(std::memory_order_acquire);
       cuuint64_t dims[4] = {static_cast<cuuint64_t>(c.w), static_cast<cuuint64_t>(c.h),
