@@ -254,6 +254,7 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
       uint64_t s_db = s_db0;
       uint32_t s_full = full_bar(0);
       uint32_t s_acol = tmem_base + conv_slab_tmem_a(0);
+      uint32_t ready = 0;
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         ok = conv_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout);
         if (!ok) break;
@@ -265,15 +266,15 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
           // weight tile's descriptor, the A slot's column) advances by a constant, so a k-block costs
           // this thread a dozen instructions.
           for (int kb = 0; kb < p.num_kb; ++kb) {
-            ok = conv_wait(s_full, phase, abort_flag, p, kStatusMmaTimeout);
-            if (!ok) break;
-            ptx::tc_fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
-              ptx::mma_tf32_1cta_ts(tmem_d, s_acol + ks * kUmmaK, s_db + ks * 2u, idesc, first);
-              first = 1u;
+            // `ready`: a non-suspending probe of this stage's barrier made one k-block earlier, so its
+            // latency ran under the previous k-block's MMA issue
+            if (!ready) {
+              ok = conv_wait(s_full, phase, abort_flag, p, kStatusMmaTimeout);
+              if (!ok) break;
             }
-            ptx::mma_commit_1cta(s_full + 64u);        // the stage's empty barrier
+            const uint32_t cur_empty = s_full + 64u;
+            const uint32_t cur_acol = s_acol;
+            const uint64_t cur_db = s_db;
             if (++stage == p.num_stages) {
               stage = 0; phase ^= 1u;
               s_full = full_bar(0); s_db = s_db0; s_acol = tmem_base + conv_slab_tmem_a(0);
@@ -281,6 +282,14 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
               s_full += 8u; s_db += s_db_step;
               s_acol += (stage == 4) ? 160u : 32u;     // slots 0-3 at columns 128.., slots 4-7 at 384..
             }
+            ready = ptx::mbar_test_wait(s_full, phase);
+            ptx::tc_fence_after_sync();
+            ptx::mma_tf32_1cta_ts(tmem_d, cur_acol, cur_db, idesc, first);
+            first = 1u;
+#pragma unroll
+            for (int ks = 1; ks < kBlockK / kUmmaK; ++ks)
+              ptx::mma_tf32_1cta_ts(tmem_d, cur_acol + ks * kUmmaK, cur_db + ks * 2u, idesc, 1u);
+            ptx::mma_commit_1cta(cur_empty);
           }
         } else
         for (int kb = 0; kb < p.num_kb; ++kb) {
