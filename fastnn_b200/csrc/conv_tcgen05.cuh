@@ -73,7 +73,8 @@ constexpr int kConvSlabMinStages = 4;  // the slab form needs one stage per grou
 __host__ __device__ constexpr uint32_t conv_slab_tmem_a(int s) {
   return s < 4 ? 128u + 32u * static_cast<uint32_t>(s) : 384u + 32u * static_cast<uint32_t>(s - 4);
 }
-constexpr int kConvGatherWarps = 16;
+constexpr int kConvGatherWarps = 16;     // four groups of four in the slab forms (a group = one warp per lane quadrant)
+static_assert(kConvGatherWarps == 16, "the slab forms take k-blocks in turns of four groups of four warps");
 constexpr int kConvThreads = 32 * (6 + kConvGatherWarps);   // producer, MMA issuer, 4 epilogue warps, gather warps
 constexpr int kConvKPerThread = kBlockK / (kConvGatherWarps / 4);   // k's of a stage row one gather thread fills
 constexpr int kConvGatherWarp0 = 6;
@@ -149,8 +150,9 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.num_stages; ++s) {
       // the weight load's expect_tx + the gather warps that fill the stage: all sixteen (a quarter of
-      // each row's k's each), or in the slab form the four that own this k-block (whole rows)
-      ptx::mbar_init(full_bar(s), kSlab ? 1 + kConvGatherWarps / 4 : 1 + kConvGatherWarps);
+      // each row's k's each), or in the slab form the four (one per tensor-memory lane quadrant) of
+      // the group that owns this k-block
+      ptx::mbar_init(full_bar(s), kSlab ? 1 + 4 : 1 + kConvGatherWarps);
       ptx::mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
