@@ -78,6 +78,15 @@ static_assert(kConvGatherWarps == 16, "the slab forms take k-blocks in turns of 
 constexpr int kConvThreads = 32 * (6 + kConvGatherWarps);   // producer, MMA issuer, 4 epilogue warps, gather warps
 constexpr int kConvKPerThread = kBlockK / (kConvGatherWarps / 4);   // k's of a stage row one gather thread fills
 constexpr int kConvGatherWarp0 = 6;
+// The slab form for channel tiles of at most 64 columns (conv2d_tf32_slab_dual_kernel) has TWO threads
+// that issue MMAs (warps 1 and 22), taking k-blocks in turn, each into a 64-column accumulator of its
+// own; the epilogue adds the two.  One thread cannot issue a tcgen05.mma of M 128, K 8 more often than
+// every ~100-120 clocks whatever its N (measured: 96-121 clocks per instruction at N = 32 ... 128, for
+// 16-64 clocks of tensor work); two threads together reach 60-70 clocks per instruction.  Wider tiles
+// keep one issuing thread: four 128-column accumulators and the A slots do not fit tensor memory, and
+// with a single accumulator set the drain no longer overlaps the next tile (measured slower).
+constexpr int kConvSlabDualThreads = kConvThreads + 32;
+constexpr int kConvSlabMmaWarpB = kConvGatherWarp0 + kConvGatherWarps;
 
 // *ptr when cond != 0, else 0, as ONE predicated load: no branch, and no access when cond is 0
 // (the address may then lie outside the tensor).
@@ -116,7 +125,7 @@ __device__ __forceinline__ bool conv_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-template <bool kSlab>
+template <bool kSlab, bool kDual = false>
 __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const CUtensorMap& tmX,
                                                  const ConvParams& p) {
   extern __shared__ uint8_t smem_raw[];
@@ -156,7 +165,7 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
       ptx::mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
-      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tfull_bar(a), kDual ? 2 : 1);   // two MMA threads: both commit
       ptx::mbar_init(tempty_bar(a), 4);
       if constexpr (kSlab) {
         ptx::mbar_init(slab_full_bar(a), 1);
@@ -239,6 +248,48 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
           ptx::tma_load_3d_hint(sb, &tmW, full_bar(stage), kb * kBlockK, n0, 0, pol);
           if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
         }
+      }
+    }
+  } else if (kDual && (warp == 1 || warp == kConvSlabMmaWarpB)) {
+    // ------------------------------------------------------ the two MMA issuers ---
+    // Thread `who` takes the k-blocks whose running count (over all units) has its parity, into its own
+    // 64-column accumulator of the set; a tile's first k-block of each thread overwrites it.
+    if (lane == 0) {
+      const int who = warp == 1 ? 0 : 1;
+      const uint32_t idesc = ptx::idesc_tf32(kBlockM, p.block_n, 0, 0);
+      const uint64_t db0 = ptx::smem_desc_sw128(smem_base, 16u, 1024u);
+      const uint64_t db_step = stage_bytes >> 4;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      int count = 0;                                                 // k-blocks passed, over all units
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+        ok = conv_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p, kStatusMmaTmemTimeout);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBlockN) + static_cast<uint32_t>(who) * 64u;
+        uint32_t first = 0u;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++count) {
+          if ((count & 1) == who) {
+            ok = conv_wait(full_bar(stage), phase, abort_flag, p, kStatusMmaTimeout);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t acol = tmem_base + conv_slab_tmem_a(stage);
+            const uint64_t db = db0 + static_cast<uint64_t>(stage) * db_step;
+            ptx::mma_tf32_1cta_ts(tmem_d, acol, db, idesc, first);
+            first = 1u;
+#pragma unroll
+            for (int ks = 1; ks < kBlockK / kUmmaK; ++ks)
+              ptx::mma_tf32_1cta_ts(tmem_d, acol + ks * kUmmaK, db + ks * 2u, idesc, 1u);
+            ptx::mma_commit_1cta(empty_bar(stage));
+          }
+          if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::mma_commit_1cta(tfull_bar(acc));          // this thread's part of the tile is complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
@@ -328,6 +379,7 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    int kb_seen = 0;       // two MMA threads: the running k-block count tells which took a tile's first k-block
     for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
       const int n0 = tile_n(u) * p.block_n;
       bool row_ok;
@@ -355,12 +407,30 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
       ptx::tc_fence_after_sync();
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                               static_cast<uint32_t>(acc * kMaxBlockN);
+      // two MMA threads: their two accumulators are added; with a single k-block only the thread whose
+      // turn it was has written one
+      const int first_who = kb_seen & 1;
+      const bool both = p.num_kb >= 2;
+      kb_seen += p.num_kb;
       for (int c = 0; c < p.block_n / 32; ++c) {
         const int co0 = n0 + c * 32;
         if (co0 >= p.co) break;
         uint32_t r[32];
-        ptx::tmem_ld_32x32(taddr0 + c * 32, r);
-        ptx::tmem_ld_wait();
+        if constexpr (kDual) {
+          ptx::tmem_ld_32x32(taddr0 + static_cast<uint32_t>(first_who) * 64u + c * 32, r);
+          if (both) {                                // warp-uniform
+            uint32_t r2[32];
+            ptx::tmem_ld_32x32(taddr0 + static_cast<uint32_t>(first_who ^ 1) * 64u + c * 32, r2);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+          } else {
+            ptx::tmem_ld_wait();
+          }
+        } else {
+          ptx::tmem_ld_32x32(taddr0 + c * 32, r);
+          ptx::tmem_ld_wait();
+        }
         if (co0 + 32 <= p.co) {                      // whole chunk: no per-channel bound checks
           if (p.bias != nullptr) {
 #pragma unroll
@@ -391,6 +461,8 @@ __device__ __forceinline__ void conv2d_tf32_body(const CUtensorMap& tmW, const C
       if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+  } else if (kDual && warp == kConvSlabMmaWarpB) {
+    // (the second MMA thread's warp: handled above)
   } else {
     // ---------------------------------------------------------------- gather ---
     // Sixteen warps: warp g fills rows (g & 3) * 32 + lane, k sub-range (g >> 2) * 8 .. + 8 of the
@@ -571,6 +643,13 @@ __global__ void __launch_bounds__(kConvThreads, 1)
 conv2d_tf32_slab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                         const __grid_constant__ ConvParams p) {
   conv2d_tf32_body<true>(tmW, tmX, p);
+}
+
+// The slab form with two MMA-issuing threads, for channel tiles of at most 64 columns.
+__global__ void __launch_bounds__(kConvSlabDualThreads, 1)
+conv2d_tf32_slab_dual_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                             const __grid_constant__ ConvParams p) {
+  conv2d_tf32_body<true, true>(tmW, tmX, p);
 }
 
 // What the gather needs per k = (ci, ki, kj): the offset of that tap from tap (0, 0) of channel 0

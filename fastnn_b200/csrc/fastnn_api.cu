@@ -988,6 +988,8 @@ extern "C" int fastnn_cuda_init(int device_id) {
                                    static_cast<int>(kMaxDynSmem)));
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_tf32_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
+  FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_tf32_slab_dual_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kMaxDynSmem)));
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::attention_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_wgrad_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1377,7 +1379,9 @@ static int conv_launch(DeviceState* st, const ConvCall& c, cudaStream_t s) {
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(fnn::kConvThreads, 1, 1);
+  // channel tiles of at most 64 columns: the slab form with two MMA-issuing threads
+  const bool dual = slab && p.block_n <= 64;
+  cfg.blockDim = dim3(dual ? fnn::kConvSlabDualThreads : fnn::kConvThreads, 1, 1);
   cfg.dynamicSmemBytes = slab ? fnn::conv_slab_smem_bytes(p.block_n, p.num_stages, p.slab_bytes, p.taps)
                               : fnn::conv_smem_bytes(p.block_n, p.num_stages);
   cfg.stream = s;
@@ -1386,7 +1390,9 @@ static int conv_launch(DeviceState* st, const ConvCall& c, cudaStream_t s) {
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if (slab) {
+  if (dual) {
+    FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::conv2d_tf32_slab_dual_kernel, tmW, tmX, p));
+  } else if (slab) {
     FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::conv2d_tf32_slab_kernel, tmW, tmX, p));
   } else {
     // the global-memory gather reads what depends on k alone from a table written just before
