@@ -768,9 +768,9 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     grid = 2 * clusters;
     const size_t smem = fnn::gemm_pair_smem_bytes(plan.block_n, plan.stages, kb_per_stage);
     if (gather)
-      fnn::gemm_tf32_pair_gather_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, peers, p);
+      fnn::gemm_tf32_pair_gather_kernel<<<grid, fnn::kNumThreadsPair, smem, g.stream>>>(tmA, tmB, tmC, peers, p);
     else
-      fnn::gemm_tf32_pair_kernel<<<grid, fnn::kNumThreads, smem, g.stream>>>(tmA, tmB, tmC, p);
+      fnn::gemm_tf32_pair_kernel<<<grid, fnn::kNumThreadsPair, smem, g.stream>>>(tmA, tmB, tmC, p);
   } else if (gather) {
     grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
     const size_t smem = fnn::gemm_smem_bytes(plan.block_n, plan.stages);
@@ -1031,7 +1031,7 @@ extern "C" int fastnn_cuda_init(int device_id) {
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(2 * prop.multiProcessorCount, 1, 1);
-    cfg.blockDim = dim3(fnn::kNumThreads, 1, 1);
+    cfg.blockDim = dim3(fnn::kNumThreadsPair, 1, 1);
     cfg.dynamicSmemBytes = fnn::gemm_pair_smem_bytes(fnn::kMaxBlockN, stages_for(fnn::kMaxBlockN, true, 1), 1);
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;

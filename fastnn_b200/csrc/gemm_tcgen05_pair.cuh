@@ -35,6 +35,9 @@ __device__ __forceinline__ Unit decode_unit_pair(const GemmParams& p, int u) {
   return decode_unit(p, u);
 }
 
+constexpr int kPairMmaWarpB = 6;                     // second MMA-issuing warp (wide tiles)
+constexpr int kNumThreadsPair = kNumThreads + 32;    // producer, MMA issuer, four epilogue warps, second MMA issuer
+
 // kGather: every finished tile is also stored through p.n_peers extra tensor maps (see PeerMaps).
 template <bool kGather>
 __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
@@ -75,10 +78,10 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.num_stages; ++s) {
       ptx::mbar_init(full_bar(s), 2);          // one arrive.expect_tx from each CTA's producer
-      ptx::mbar_init(empty_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), n_sub);     // one commit per MMA-issuing thread (two for a wide tile)
     }
     for (int a = 0; a < 2; ++a) {
-      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tfull_bar(a), n_sub);
       ptx::mbar_init(tempty_bar(a), 8);        // four epilogue warps of each CTA
     }
     *abort_flag = 0;
@@ -158,9 +161,14 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
         if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------- MMA issuer (leader only) ---
-    if (lane == 0 && rank == 0) {
+  } else if (warp == 1 || warp == kPairMmaWarpB) {
+    // ------------------------------------------------ MMA issuers (leader only) ---
+    // A 256-wide tile has one issuing thread (warp 1).  A wide tile has two: warp 1 issues the MMA
+    // group of columns [0, 256), warp 6 the group of [256, 512), over the same A stage, each into
+    // its own accumulator columns -- one thread issues a tcgen05.mma only every 100-170 clocks, and
+    // eight instructions per k-block from one thread left the tensor pipe 85 % busy.
+    const int my_group = warp == 1 ? 0 : 1;
+    if (lane == 0 && rank == 0 && my_group < n_sub) {
       const uint32_t idesc = ptx::idesc_tf32(kPairBlockM, mma_n, p.a_mn_major, p.b_mn_major);
       const uint64_t a_desc0 = ptx::smem_desc_sw128(
           smem_base, p.a_mn_major ? kChunkBytes : 16u, p.a_mn_major ? 512u : 1024u,
@@ -197,7 +205,8 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
           for (int r = 0; r < nsub; ++r) {
             const uint64_t da = a_desc0 + stage * stage_step + r * sub_step;
             const uint64_t db = b_desc0 + stage * stage_step + r * sub_step;
-            for (int h = 0; h < n_sub; ++h) {         // MMA groups over the same A stage
+            {                                         // this thread's MMA group over the A stage
+              const int h = my_group;
               const uint32_t td = tmem_d + static_cast<uint32_t>(h * mma_n);
               const uint64_t dbh = db + h * half_step;
               ptx::mma_tf32_2cta(td, da, dbh, idesc, accumulate);
@@ -217,7 +226,7 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
         if (++acc == n_acc) { acc = 0; acc_phase ^= 1u; }
       }
     }
-  } else {
+  } else if (warp < kPairMmaWarpB) {
     // -------------------------------------------------------------- epilogue ---
     const int q = warp & 3;
     const uint32_t staging = staging_base + (warp - kEpilogueWarp0) * kStagingBytesPerWarp;
@@ -277,13 +286,13 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
   }
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreadsPair, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmC, const __grid_constant__ GemmParams p) {
   gemm_tf32_pair_body<false>(tmA, tmB, tmC, p, nullptr);
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreadsPair, 1)
 gemm_tf32_pair_gather_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                              const __grid_constant__ CUtensorMap tmC, const __grid_constant__ PeerMaps peers,
                              const __grid_constant__ GemmParams p) {
