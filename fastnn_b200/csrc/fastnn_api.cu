@@ -645,6 +645,10 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
   p.split_k = plan.split_k;
   p.kb_per_split = kbps;
   p.kb_per_stage = kb_per_stage;
+  // two MMA groups (two issuing threads) for the wide pair tile, 512 = 2 x 256; a 256-wide tile as
+  // 2 x 128 measured slower than one group (562-570 against 619-621 TFLOP/s on the fused forward)
+  const int mma_groups = (plan.pair && plan.block_n > fnn::kMaxBlockN) ? 2 : 1;
+  p.mma_groups = mma_groups;
   const long long units = 1ll * g.batch * p.tiles_m * p.tiles_n * plan.split_k;
   if (units > 0x7fffffffll) return -1;
   p.total_units = static_cast<int>(units);
@@ -720,7 +724,7 @@ int launch_tcgen05(DeviceState* st, const GemmArgs& g, const Policy& pol) {
     }
   }
   // B columns one load brings: a CTA's half of one MMA group (a wide tile is two groups of 256)
-  const int b_cols = plan.pair ? (plan.block_n > fnn::kMaxBlockN ? fnn::kMaxBlockN : plan.block_n) / 2
+  const int b_cols = plan.pair ? (plan.block_n / mma_groups) / 2
                                : plan.block_n;
   if (!p.b_mn_major)
     ok = ok && encode_map(&tmB, g.b, g.k, g.n, B, g.ldb * 4ull, sb_bytes, fnn::kBlockK, b_cols);

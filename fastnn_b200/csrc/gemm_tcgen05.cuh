@@ -77,6 +77,7 @@ struct GemmParams {
   int pace_gather;     // gather kernels: spread each tile's stores over this many eighths of the time its
                        // main loop took (0: send every tile at once)
   int kb_per_stage;    // 32-deep k-blocks per pipeline stage (CTA-pair kernel only; else 1)
+  int mma_groups;      // CTA-pair kernel: MMA groups (and issuing threads) per stage: 1 or 2
   int total_units;     // batch * tiles_m * tiles_n * split_k
   int a_mn_major;      // A stored [k, m]
   int b_mn_major;      // B stored [k, n]

@@ -53,10 +53,12 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
   // one MMA group is at most 256 columns wide; a 512-wide tile is two groups over the same A
-  const int n_sub = p.block_n > kMaxBlockN ? 2 : 1;
+  // MMA groups over the same A stage, each with an issuing thread of its own: the two 256-column
+  // halves of a wide tile, or the two 128-column halves of a 256-wide one
+  const int n_sub = p.mma_groups;
   const int mma_n = p.block_n / n_sub;                   // N of one tcgen05.mma
   const int half_n = mma_n >> 1;                         // B columns of one group this CTA loads
-  const int n_acc = n_sub == 2 ? 1 : 2;                  // accumulator sets that fit 512 TMEM columns
+  const int n_acc = p.block_n > kMaxBlockN ? 1 : 2;      // accumulator sets that fit 512 TMEM columns
 
   // A stage holds kb_per_stage consecutive 32-deep k-blocks, each as [A 16 KiB][B half]; one
   // barrier round trip (wait, commit) then covers 4 * kb_per_stage MMAs.
@@ -163,10 +165,10 @@ __device__ __forceinline__ void gemm_tf32_pair_body(const CUtensorMap& tmA, cons
     }
   } else if (warp == 1 || warp == kPairMmaWarpB) {
     // ------------------------------------------------ MMA issuers (leader only) ---
-    // A 256-wide tile has one issuing thread (warp 1).  A wide tile has two: warp 1 issues the MMA
-    // group of columns [0, 256), warp 6 the group of [256, 512), over the same A stage, each into
-    // its own accumulator columns -- one thread issues a tcgen05.mma only every 100-170 clocks, and
-    // eight instructions per k-block from one thread left the tensor pipe 85 % busy.
+    // With two MMA groups there are two issuing threads: warp 1 issues the group of the tile's lower
+    // columns, warp 6 the group of the upper ones, over the same A stage, each into its own
+    // accumulator columns -- one thread issues a tcgen05.mma only every 100-170 clocks, and eight
+    // instructions per k-block from one thread left the tensor pipe 85 % busy.
     const int my_group = warp == 1 ? 0 : 1;
     if (lane == 0 && rank == 0 && my_group < n_sub) {
       const uint32_t idesc = ptx::idesc_tf32(kPairBlockM, mma_n, p.a_mn_major, p.b_mn_major);
