@@ -28,7 +28,13 @@
 // tap mask is needed).  The gather warps then read shared memory instead of L2: per element one
 // add and one load, the tap offsets from a table in shared memory that is the same for every
 // chunk (k = (ci, ki, kj), so 32 channels are exactly kh*kw k-blocks).  Two slab slots take turns;
-// the weight producer loads chunk j + 1 when the main loop reaches chunk j.
+// the weight producer loads chunk j + 1 when the main loop reaches chunk j.  The gathered rows do
+// not pass through shared memory again: a gather thread holds a whole row of 32 k's and writes it
+// with one tcgen05.st into the stage's A slot in TENSOR memory, from where the MMA takes its A
+// operand (a shared-memory A stage needed a fence.proxy.async per fill, ~900 clocks); a stage of
+// shared memory holds the weight tile alone.  The sixteen gather warps form four groups that take
+// every fourth k-block.  For channel tiles of at most 64 columns (conv2d_tf32_slab_dual_kernel)
+// two threads issue the MMAs, taking k-blocks in turn.
 #pragma once
 #include "gemm_tcgen05.cuh"
 
