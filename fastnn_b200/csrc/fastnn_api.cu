@@ -20,6 +20,7 @@
 #include "attention_tcgen05.cuh"
 #include "conv_tcgen05.cuh"
 #include "conv_wgrad_tcgen05.cuh"
+#include "conv_wgrad_slab_tcgen05.cuh"
 
 namespace {
 
@@ -994,6 +995,8 @@ extern "C" int fastnn_cuda_init(int device_id) {
                                    static_cast<int>(kMaxDynSmem)));
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_tf32_slab_dual_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
+  FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_wgrad_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kMaxDynSmem)));
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::attention_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kMaxDynSmem)));
   FNN_CUDA_OK(cudaFuncSetAttribute(fnn::conv2d_wgrad_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1565,6 +1568,132 @@ extern "C" int fastnn_cuda_conv2d_backward_data(const float* grad_output, const 
 // straight into the B stages, the contraction over all positions of all images cut into slices so
 // that every SM has a unit; slices are added in order by the split-K reduce kernel.  Needs
 // out_h * out_w to be a multiple of 4 (16-byte rows of grad_output for TMA).
+// The weight gradient with the gathered operand in tensor memory (conv_wgrad_slab_tcgen05.cuh).
+// Returns 1 when the shape is outside that form's conditions (the caller then takes another form):
+// input rows a tensor map can address (16-byte pitch and base, at most 244 columns), the kernel
+// overhanging the image by at most four columns on either side, output rows of 16-byte pitch, and
+// two slabs beside at least four stages of dY tiles in shared memory.
+static int conv_wgrad_slab(DeviceState* st, const float* input, const float* grad_output, float* grad_weight,
+                           int batch_size, int in_channels, int out_channels, int input_h, int input_w,
+                           int output_h, int output_w, int kernel_h, int kernel_w, int stride_h, int stride_w,
+                           int pad_h, int pad_w, int k, cudaStream_t s) {
+  const Tunables& tune = tunables();
+  if (tune.conv_no_slab) return 1;
+  const int pitch = input_w + 12;            // four halo columns either side + four that keep rows off one bank
+  if ((input_w & 3) != 0 || !aligned16(input) || pitch > 256 || pad_w > fnn::kWgradSlabHalo || stride_w > 4 ||
+      (output_w - 1) * stride_w - pad_w + kernel_w - 1 > input_w - 1 + fnn::kWgradSlabHalo ||
+      (output_w & 3) != 0 || !aligned16(grad_output) || out_channels > (1 << 20))
+    return 1;
+  fnn::WgradSlabParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.batch = batch_size; p.ci = in_channels; p.co = out_channels; p.h = input_h; p.w = input_w;
+  p.kh = kernel_h; p.kw = kernel_w; p.sh = stride_h; p.sw = stride_w; p.ph = pad_h; p.pw = pad_w;
+  p.oh = output_h; p.ow = output_w; p.k_taps = k; p.taps = kernel_h * kernel_w;
+  p.tiles_m = ceil_div(k, fnn::kBlockM);
+  p.block_n = out_channels >= 128 ? 128 : ceil_div(out_channels, 32) * 32;
+  p.tiles_n = ceil_div(out_channels, p.block_n);
+  p.kb_per_row = ceil_div(output_w, fnn::kBlockK);
+  p.slab_ch = (fnn::kBlockM - 1) / p.taps + 2;          // channels 128 consecutive taps can touch
+  if (p.slab_ch > 256) return 1;
+  p.slab_pitch = pitch;
+  const size_t stage = static_cast<size_t>(p.block_n) * fnn::kBlockK * 4;
+  // output rows per slab: as many as keep two slabs beside four stages
+  const long long budget = static_cast<long long>(kMaxDynSmem) - 1024 - fnn::kBarrierBytes - fnn::kWgradSlabTailBytes -
+                           4 * static_cast<long long>(stage);
+  p.g_rows = 0;
+  for (int g : {8, 4, 2, 1}) {
+    const long long rows = 1ll * (g - 1) * stride_h + kernel_h;
+    const long long bytes = 1ll * p.slab_ch * rows * pitch * 4;
+    if (rows <= 256 && 2 * bytes <= budget && bytes <= 48 * 1024) {
+      p.g_rows = g > output_h ? output_h : g;
+      p.slab_rows = static_cast<int>(1ll * (p.g_rows - 1) * stride_h + kernel_h);
+      p.slab_bytes = static_cast<int>(1ll * p.slab_ch * p.slab_rows * pitch * 4);
+      break;
+    }
+  }
+  if (p.g_rows == 0) return 1;
+  p.slabs_per_image = ceil_div(output_h, p.g_rows);
+  if (1ll * batch_size * p.slabs_per_image > 0x7fffffffll) return 1;
+  p.total_slabs = batch_size * p.slabs_per_image;
+  const long long room = static_cast<long long>(kMaxDynSmem) - 1024 - fnn::kBarrierBytes - fnn::kWgradSlabTailBytes -
+                         2ll * p.slab_bytes;
+  long long stages = room / static_cast<long long>(stage);
+  if (stages < 4) return 1;
+  p.num_stages = stages > fnn::kMaxStages ? fnn::kMaxStages : static_cast<int>(stages);
+  long long slices = st->num_sms / (1ll * p.tiles_m * p.tiles_n);
+  if (slices > p.total_slabs) slices = p.total_slabs;
+  if (slices < 1) slices = 1;
+  p.slices = static_cast<int>(slices);
+  const long long units = 1ll * p.tiles_m * p.tiles_n * p.slices;
+  if (units > 0x7fffffffll) return 1;
+  p.total_units = static_cast<int>(units);
+  const size_t part_floats = p.slices > 1 ? static_cast<size_t>(p.slices) * out_channels * k : 0;
+  float* partials = nullptr;
+  if (part_floats > 0 && workspace_reserve(st, st->conv_ws, s, sizeof(float) * part_floats, &partials) != 0) return -1;
+  p.partial = p.slices > 1 ? partials : grad_weight;
+  p.status = st->status; p.spin_budget = st->spin_budget;
+  const EncodeTiledFn encode = g_encode.load(std::memory_order_acquire);
+  if (encode == nullptr) return 1;
+  CUtensorMap tmG, tmX;
+  {
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(output_w), static_cast<cuuint64_t>(output_h),
+                          static_cast<cuuint64_t>(out_channels), static_cast<cuuint64_t>(batch_size)};
+    cuuint64_t strides[3] = {output_w * 4ull, 4ull * output_w * output_h, 4ull * output_w * output_h * out_channels};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(fnn::kBlockK), 1, static_cast<cuuint32_t>(p.block_n), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (strides[2] >= (1ull << 40) ||
+        encode(&tmG, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(grad_output), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return 1;
+  }
+  {
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(input_w), static_cast<cuuint64_t>(input_h),
+                          static_cast<cuuint64_t>(in_channels), static_cast<cuuint64_t>(batch_size)};
+    cuuint64_t strides[3] = {input_w * 4ull, 4ull * input_w * input_h, 4ull * input_w * input_h * in_channels};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(pitch), static_cast<cuuint32_t>(p.slab_rows),
+                         static_cast<cuuint32_t>(p.slab_ch), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (strides[2] >= (1ull << 40) ||
+        encode(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(input), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return 1;
+  }
+  const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(fnn::kWgradSlabThreads, 1, 1);
+  cfg.dynamicSmemBytes = fnn::wgrad_slab_smem_bytes(p.block_n, p.num_stages, p.slab_bytes);
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  FNN_CUDA_OK(cudaLaunchKernelEx(&cfg, fnn::conv2d_wgrad_slab_kernel, tmG, tmX, p));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (p.slices > 1) {
+    const long long total = 1ll * out_channels * k;
+    const bool vec = (k & 3) == 0 && aligned16(grad_weight) && aligned16(partials);
+    long long rblocks = ((vec ? total / 4 : total) + 255) / 256;
+    if (rblocks > 8ll * st->num_sms) rblocks = 8ll * st->num_sms;
+    if (rblocks < 1) rblocks = 1;
+    if (vec)
+      fnn::splitk_reduce_vec4_kernel<<<static_cast<unsigned>(rblocks), 256, 0, s>>>(
+          reinterpret_cast<const float4*>(partials), grad_weight, nullptr, out_channels, k, 1, p.slices, k, total,
+          1.0f, 0.0f, 0);
+    else
+      fnn::splitk_reduce_kernel<<<static_cast<unsigned>(rblocks), 256, 0, s>>>(
+          partials, grad_weight, nullptr, out_channels, k, 1, p.slices, k, total, 1.0f, 0.0f, 0);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
+  FNN_CUDA_OK(cudaGetLastError());
+  t_last = LastCall{11, p.block_n, p.slices, grid};
+  return 0;
+}
+
 static int conv_wgrad_implicit(DeviceState* st, const float* input, const float* grad_output, float* grad_weight,
                                int batch_size, int in_channels, int out_channels, int input_h, int input_w,
                                int output_h, int output_w, int kernel_h, int kernel_w, int stride_h,
@@ -1677,6 +1806,12 @@ extern "C" int fastnn_b200_conv2d_backward_weight(const float* input, const floa
   {
     DeviceState* st0 = current_state();
     if (st0 == nullptr) return -1;
+    if (t_policy.policy != 1) {
+      const int rc = conv_wgrad_slab(st0, input, grad_output, grad_weight, batch_size, in_channels, out_channels,
+                                     input_h, input_w, output_h, output_w, kernel_h, kernel_w, stride_h, stride_w,
+                                     pad_h, pad_w, k, s);
+      if (rc <= 0) return rc;
+    }
     if ((plane & 3) == 0 && aligned16(grad_output) && 1ll * in_channels * input_h * input_w < (1ll << 30) &&
         t_policy.policy != 1)
       return conv_wgrad_implicit(st0, input, grad_output, grad_weight, batch_size, in_channels, out_channels,

@@ -352,7 +352,9 @@ FASTNN_B200_API int fastnn_b200_set_policy(int policy, int block_n, int split_k)
  * 2-CTA, 4 = fused attention, 5 = conv2d, 6 = tcgen05 1-CTA with the K split inside clusters
  * (one launch, no workspace), 7 = a direct (FP32 FMA) convolution kernel, 8 = attention composed
  * from two batched GEMMs and a row softmax, 9 = conv2d with the input rows of every tile staged in
- * shared memory by TMA (5 is then the same kernel gathering from global memory); 0 before any call.
+ * shared memory by TMA (5 is then the same kernel gathering from global memory), 11 = the conv2d weight
+ * gradient with its gathered operand in tensor memory (5 is then the form that gathers from global
+ * memory into shared memory); 0 before any call.
  * Also reports its tile and split choice. */
 FASTNN_B200_API int fastnn_b200_last_path(int* block_n, int* split_k, int* num_ctas);
 

@@ -101,7 +101,7 @@ def test_grad_weight_takes_the_implicit_gemm_and_the_explicit_form_by_plane(gpu)
                                                       pad, pad, None) == 0
         torch.cuda.synchronize()
         lp = f.last_path()
-        assert lp["path"] == want_path or (want_path == 2 and lp["path"] == 1), lp
+        assert lp["path"] == want_path or (want_path == 5 and lp["path"] == 11) or (want_path == 2 and lp["path"] == 1), lp
         if want_path == 5:
             assert lp["split_k"] > 1, "the contraction over 8 x 784 positions is cut into slices"
         _check(gw.cpu().numpy(), want_gw, n * h * w, go, x, f"grad_weight {(n, ci, co, h, w)}")
