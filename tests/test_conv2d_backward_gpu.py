@@ -165,3 +165,41 @@ def test_conv2d_forward_with_more_taps_than_the_gather_encodes(gpu):
     gi, _ = f.conv2d_backward(torch.from_numpy(x).cuda(), torch.from_numpy(wt).cuda(),
                               torch.from_numpy(go).cuda(), padding=(2, 2))
     assert np.abs(gi.cpu().numpy() - want_gi).max() <= 1e-4 * 5 * 64
+
+
+@pytest.mark.parametrize("cfg", [
+    # n, ci, co, h, w, kh, kw, stride, padding -- shapes the tensor-memory form of the weight gradient takes
+    (2, 64, 128, 56, 56, 3, 3, (1, 1), (1, 1)),      # the benchmark layer, two images: 5 tap tiles, the last half full
+    (3, 20, 200, 24, 24, 3, 3, (1, 1), (1, 1)),      # two channel tiles (128 + 72), 180 taps
+    (2, 7, 9, 16, 20, 5, 5, (1, 1), (2, 2)),         # 25 taps per channel, fewer channels than a warp has lanes
+    (2, 16, 24, 32, 32, 3, 3, (2, 2), (1, 1)),       # stride 2: inputs of a k-block two words apart
+    (4, 40, 48, 12, 12, 1, 1, (1, 1), (0, 0)),       # pointwise: one channel per tap
+    (2, 8, 16, 20, 36, 3, 4, (1, 1), (1, 4)),        # output rows of 41 columns: no 16-byte pitch, another form serves it
+    (1, 5, 6, 8, 8, 3, 3, (1, 1), (1, 1)),           # one image, 64 positions: fewer slabs than SMs
+    (2, 32, 32, 16, 64, 3, 3, (1, 1), (1, 1)),       # rows of exactly two k-blocks
+])
+def test_grad_weight_through_tensor_memory(gpu, cfg):
+    """grad_weight with taps as the M dimension and the gathered input rows in tensor memory (path 11)."""
+    import torch
+    f = gpu
+    lib = f.lib()
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    n, ci, co, h, w, kh, kw, stride, padding = cfg
+    x, wt, go = _case(n, ci, co, h, w, kh, kw, stride, padding, 300 + sum(cfg[:7]))
+    oh, ow = go.shape[2], go.shape[3]
+    _, want_gw = oracle.conv2d_backward(x, wt, go, stride, padding)
+    xd, gd = torch.from_numpy(x).cuda(), torch.from_numpy(go).cuda()
+    gw = torch.full(wt.shape, float("nan"), device="cuda")
+    assert lib.fastnn_b200_conv2d_backward_weight(vp(xd), vp(gd), vp(gw), n, ci, co, h, w, oh, ow, kh, kw,
+                                                  stride[0], stride[1], padding[0], padding[1], None) == 0
+    torch.cuda.synchronize()
+    lp = f.last_path()
+    if ow % 4 == 0:
+        assert lp["path"] == 11, lp
+    _check(gw.cpu().numpy(), want_gw, n * oh * ow, go, x, f"grad_weight {cfg}")
+    # the same call again: bit-identical (fixed order of the slices and of the two accumulators)
+    gw2 = torch.full(wt.shape, float("nan"), device="cuda")
+    assert lib.fastnn_b200_conv2d_backward_weight(vp(xd), vp(gd), vp(gw2), n, ci, co, h, w, oh, ow, kh, kw,
+                                                  stride[0], stride[1], padding[0], padding[1], None) == 0
+    assert torch.equal(gw, gw2)
+    assert f.device_status() == 0
