@@ -320,6 +320,14 @@ conv2d_wgrad_slab_kernel(const __grid_constant__ CUtensorMap tmG, const __grid_c
 #pragma unroll
               for (int j = 0; j < kBlockK; ++j)
                 asm volatile("ld.shared.b32 %0, [%1];" : "=r"(e[j]) : "r"(a0 + j * step));
+              // positions past the end of the output row: zeros (their dY columns are zeros too, but a
+              // non-finite input next to the row must not turn the product into NaN)
+              const int n_valid = p.ow - xb * kBlockK;
+              if (n_valid < kBlockK) {                 // warp-uniform
+#pragma unroll
+                for (int j = 0; j < kBlockK; ++j)
+                  if (j >= n_valid) e[j] = 0u;
+              }
               int okw2 = 1;
               if (lane == 0)
                 okw2 = wgs_wait(empty_bar(stage), phase ^ 1u, abort_flag, p, kStatusConvGather, 32) ? 1 : 0;
